@@ -1,0 +1,92 @@
+"""ctypes binding of libnf4b200.so (the C ABI declared in include/nf4b200.h).
+
+There is no fallback: if the library has not been built, or the device is not sm_100, every
+entry point raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libnf4b200.so"
+
+EXPORTS = (
+    "nf4b200_query", "nf4b200_last_error", "nf4b200_device_status", "nf4b200_dequant",
+    "nf4b200_linear_fwd", "nf4b200_linear_bwd_dx", "nf4b200_lora_down", "nf4b200_lora_grad",
+)
+
+F16, BF16, F32 = 0, 1, 2
+
+
+class Nf4Error(RuntimeError):
+    """A non-zero status from the CUDA library."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"nf4b200 error {code}: {message}")
+        self.code = code
+
+
+class Weight(Structure):
+    _fields_ = [
+        ("codes", c_void_p), ("absmax", c_void_p), ("code2", c_void_p), ("absmax2", c_void_p),
+        ("offset", c_void_p), ("code16", c_void_p), ("n_rows", c_int64), ("n_cols", c_int64),
+        ("blocksize", c_int32), ("nested_blocksize", c_int32), ("nested", c_int32),
+        ("reserved", c_int32),
+    ]
+
+
+class Props(Structure):
+    _fields_ = [("cc_major", c_int32), ("cc_minor", c_int32), ("sm_count", c_int32),
+                ("supported", c_int32), ("smem_per_block_optin", c_int64)]
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m hackaton_b200.build` (needs nvcc). "
+            "hackaton_b200 has no CPU or PyTorch fallback for its kernels.")
+    handle = ctypes.CDLL(str(LIB_PATH))
+    handle.nf4b200_last_error.restype = c_char_p
+    handle.nf4b200_last_error.argtypes = []
+    handle.nf4b200_query.argtypes = [c_int, POINTER(Props)]
+    handle.nf4b200_device_status.argtypes = [POINTER(c_int)]
+    handle.nf4b200_dequant.argtypes = [POINTER(Weight), c_void_p, c_int, c_void_p]
+    handle.nf4b200_linear_fwd.argtypes = [POINTER(Weight), c_void_p, c_int64, c_int64, c_void_p,
+                                          c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
+    handle.nf4b200_linear_bwd_dx.argtypes = [POINTER(Weight), c_void_p, c_int64, c_int64, c_void_p,
+                                             c_void_p, c_void_p, c_int64, c_void_p]
+    handle.nf4b200_lora_down.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
+                                         c_int64, c_float, c_void_p, c_void_p]
+    handle.nf4b200_lora_grad.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p,
+                                         c_int64, c_int64, c_void_p]
+    for name in EXPORTS:
+        if name != "nf4b200_last_error":
+            getattr(handle, name).restype = c_int
+    _lib = handle
+    return handle
+
+
+def check(status: int) -> None:
+    if status != 0:
+        raise Nf4Error(status, lib().nf4b200_last_error().decode("utf-8", "replace"))
+
+
+def query(device: int = 0) -> Props:
+    props = Props()
+    check(lib().nf4b200_query(device, ctypes.byref(props)))
+    return props
+
+
+def device_status() -> int:
+    """Reads and clears the device-side status word (synchronises). Raises if it was non-zero."""
+    word = c_int(0)
+    check(lib().nf4b200_device_status(ctypes.byref(word)))
+    return word.value

@@ -1,0 +1,307 @@
+// C-ABI entry points (declared in include/nf4b200.h): argument validation, device checks and
+// dispatch to the kernels. No C++ exception crosses this boundary; errors come back as status
+// codes plus a thread-local message.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/nf4b200.h"
+#include "kernels.h"
+
+namespace {
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+constexpr int MAX_DEVICES = 64;
+
+struct DeviceInfo {
+    bool known = false;
+    int major = 0, minor = 0, sms = 0;
+    size_t smem_optin = 0;
+    int* status_word = nullptr;
+};
+std::mutex g_mutex;
+DeviceInfo g_devices[MAX_DEVICES];
+
+__device__ int g_status_word;  // written by kernels whose bounded wait ran out
+
+// Facts about the current device, looked up once per device.
+int current_device(DeviceInfo** info) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= MAX_DEVICES) return fail(NF4B200_EINVAL, "device index %d", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceInfo& d = g_devices[dev];
+    if (!d.known) {
+        cudaDeviceProp prop;
+        e = cudaGetDeviceProperties(&prop, dev);
+        if (e != cudaSuccess)
+            return fail(NF4B200_ECUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+        d.major = prop.major;
+        d.minor = prop.minor;
+        d.sms = prop.multiProcessorCount;
+        d.smem_optin = prop.sharedMemPerBlockOptin;
+        if (d.major == 10) {
+            void* ptr = nullptr;
+            e = cudaGetSymbolAddress(&ptr, g_status_word);
+            if (e != cudaSuccess)
+                return fail(NF4B200_ECUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            d.status_word = static_cast<int*>(ptr);
+        }
+        d.known = true;
+    }
+    *info = &d;
+    return NF4B200_OK;
+}
+
+int require_sm100(DeviceInfo** info) {
+    int rc = current_device(info);
+    if (rc != NF4B200_OK) return rc;
+    if ((*info)->major != 10)
+        return fail(NF4B200_EARCH,
+                    "nf4b200 kernels are built for sm_100a only; current device is sm_%d%d and "
+                    "there is no fallback path",
+                    (*info)->major, (*info)->minor);
+    return NF4B200_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_weight(const nf4b200_weight* w, bool for_gemm) {
+    if (!w) return fail(NF4B200_EINVAL, "weight descriptor is NULL");
+    if (!w->codes || !w->absmax || !w->code16)
+        return fail(NF4B200_EINVAL, "weight: codes, absmax and code16 must be non-NULL");
+    if (w->n_rows <= 0 || w->n_cols <= 0)
+        return fail(NF4B200_EINVAL, "weight shape %lld x %lld", (long long)w->n_rows,
+                    (long long)w->n_cols);
+    const long long n = (long long)w->n_rows * w->n_cols;
+    if (n % 8 != 0) return fail(NF4B200_EINVAL, "weight element count %lld is not a multiple of 8", n);
+    if (w->blocksize <= 0 || w->blocksize % 8 != 0)
+        return fail(NF4B200_EINVAL, "blocksize %d is not a positive multiple of 8", w->blocksize);
+    if (n % w->blocksize != 0)
+        return fail(NF4B200_EINVAL, "weight element count %lld is not a multiple of blocksize %d", n,
+                    w->blocksize);
+    if ((reinterpret_cast<uintptr_t>(w->codes) & 3u) != 0)
+        return fail(NF4B200_EINVAL, "codes pointer is not 4-byte aligned");
+    if (w->nested) {
+        if (!w->code2 || !w->absmax2 || !w->offset)
+            return fail(NF4B200_EINVAL, "nested weight: code2, absmax2 and offset must be non-NULL");
+        if (w->nested_blocksize <= 0)
+            return fail(NF4B200_EINVAL, "nested_blocksize %d", w->nested_blocksize);
+    }
+    if (for_gemm) {
+        if (w->blocksize != 64)
+            return fail(NF4B200_EINVAL, "fused GEMM needs blocksize 64, got %d", w->blocksize);
+        if (w->n_cols % 64 != 0)
+            return fail(NF4B200_EINVAL, "fused GEMM needs n_cols %% 64 == 0, got %lld",
+                        (long long)w->n_cols);
+        if (!aligned16(w->codes)) return fail(NF4B200_EINVAL, "codes pointer is not 16-byte aligned");
+        if (w->n_rows > 0x7FFFFFFF || w->n_cols > 0x7FFFFFFF)
+            return fail(NF4B200_EINVAL, "weight dimension exceeds 2^31");
+    }
+    return NF4B200_OK;
+}
+
+int check_act(const char* name, const void* p, int64_t m, int64_t ld, int64_t cols) {
+    if (!p) return fail(NF4B200_EINVAL, "%s is NULL", name);
+    if (m <= 0 || m > 0x7FFFFFFF) return fail(NF4B200_EINVAL, "%s: row count %lld", name, (long long)m);
+    if (ld < cols) return fail(NF4B200_EINVAL, "%s: row stride %lld < %lld columns", name,
+                               (long long)ld, (long long)cols);
+    if (ld % 8 != 0) return fail(NF4B200_EINVAL, "%s: row stride %lld is not a multiple of 8", name,
+                                 (long long)ld);
+    if (!aligned16(p)) return fail(NF4B200_EINVAL, "%s is not 16-byte aligned", name);
+    return NF4B200_OK;
+}
+
+void fill_gemm(nf4::GemmArgs& g, const nf4b200_weight* w, int sms) {
+    g.codes = static_cast<const uint8_t*>(w->codes);
+    g.absmax = w->absmax;
+    g.code2 = w->code2;
+    g.absmax2 = w->absmax2;
+    g.offset = w->offset;
+    g.code16 = w->code16;
+    g.n_w = w->n_rows;
+    g.k_w = w->n_cols;
+    g.nested = w->nested ? 1 : 0;
+    g.nested_blocksize = w->nested ? w->nested_blocksize : 1;
+    g.sm_count = sms;
+}
+
+}  // namespace
+
+namespace nf4 {
+
+int* device_status_word() {
+    DeviceInfo* d = nullptr;
+    if (current_device(&d) != NF4B200_OK) return nullptr;
+    return d->status_word;
+}
+
+cudaError_t read_and_clear_device_status(int* out) {
+    int* word = device_status_word();
+    if (!word) return cudaErrorInvalidDevice;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    e = cudaMemcpy(out, word, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    if (*out != 0) e = cudaMemset(word, 0, sizeof(int));
+    return e;
+}
+
+}  // namespace nf4
+
+extern "C" {
+
+const char* nf4b200_last_error(void) { return g_error; }
+
+int nf4b200_query(int device, nf4b200_props* out) {
+    if (!out) return fail(NF4B200_EINVAL, "props pointer is NULL");
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess)
+        return fail(NF4B200_ECUDA, "cudaGetDeviceProperties(%d): %s", device, cudaGetErrorString(e));
+    out->cc_major = prop.major;
+    out->cc_minor = prop.minor;
+    out->sm_count = prop.multiProcessorCount;
+    out->supported = prop.major == 10 ? 1 : 0;
+    out->smem_per_block_optin = (int64_t)prop.sharedMemPerBlockOptin;
+    return NF4B200_OK;
+}
+
+int nf4b200_device_status(int* status_out) {
+    if (!status_out) return fail(NF4B200_EINVAL, "status pointer is NULL");
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    cudaError_t e = nf4::read_and_clear_device_status(status_out);
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "device status: %s", cudaGetErrorString(e));
+    if (*status_out != 0)
+        return fail(NF4B200_EDEVICE, "a kernel gave up a bounded wait (status %d)", *status_out);
+    return NF4B200_OK;
+}
+
+int nf4b200_dequant(const nf4b200_weight* w, void* out, int out_dtype, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    rc = check_weight(w, false);
+    if (rc != NF4B200_OK) return rc;
+    if (!out) return fail(NF4B200_EINVAL, "out is NULL");
+    if (out_dtype < 0 || out_dtype > 2) return fail(NF4B200_EINVAL, "out_dtype %d", out_dtype);
+    if (!aligned16(out)) return fail(NF4B200_EINVAL, "out is not 16-byte aligned");
+    nf4::DequantArgs a;
+    a.codes = w->codes; a.absmax = w->absmax; a.code2 = w->code2; a.absmax2 = w->absmax2;
+    a.offset = w->offset; a.code16 = w->code16; a.out = out;
+    a.n = (long long)w->n_rows * w->n_cols;
+    a.blocksize = w->blocksize;
+    a.nested_blocksize = w->nested ? w->nested_blocksize : 1;
+    a.nested = w->nested ? 1 : 0;
+    a.out_dtype = out_dtype;
+    a.sm_count = d->sms;
+    cudaError_t e = nf4::launch_dequant(a, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "dequant launch: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_t ldx,
+                       const void* bias, const void* xa, const void* lora_b, void* y, int64_t ldy,
+                       void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if ((rc = check_weight(w, true)) != NF4B200_OK) return rc;
+    if ((rc = check_act("x", x, m, ldx, w->n_cols)) != NF4B200_OK) return rc;
+    if (!y) return fail(NF4B200_EINVAL, "y is NULL");
+    if (ldy < w->n_rows) return fail(NF4B200_EINVAL, "y: row stride %lld < %lld columns",
+                                     (long long)ldy, (long long)w->n_rows);
+    if ((xa == nullptr) != (lora_b == nullptr))
+        return fail(NF4B200_EINVAL, "xa and lora_b must both be given or both be NULL");
+    if (xa && (!aligned16(xa) || !aligned16(lora_b)))
+        return fail(NF4B200_EINVAL, "xa / lora_b are not 16-byte aligned");
+    nf4::GemmArgs g;
+    fill_gemm(g, w, d->sms);
+    g.act = static_cast<const __half*>(x); g.m = m; g.ld_act = ldx;
+    g.out = static_cast<__half*>(y); g.ld_out = ldy;
+    g.bias = static_cast<const __half*>(bias);
+    g.ext_a = static_cast<const __half*>(xa);
+    g.ext_b = static_cast<const __half*>(lora_b);
+    g.trans_w = false;
+    const char* why = "";
+    cudaError_t e = nf4::launch_gemm(g, static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess)
+        return fail(NF4B200_ECUDA, "linear_fwd: %s: %s", why, cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_linear_bwd_dx(const nf4b200_weight* w, const void* dy, int64_t m, int64_t lddy,
+                          const void* u, const void* lora_a, void* dx, int64_t lddx, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if ((rc = check_weight(w, true)) != NF4B200_OK) return rc;
+    if ((rc = check_act("dy", dy, m, lddy, w->n_rows)) != NF4B200_OK) return rc;
+    if (!dx) return fail(NF4B200_EINVAL, "dx is NULL");
+    if (lddx < w->n_cols) return fail(NF4B200_EINVAL, "dx: row stride %lld < %lld columns",
+                                      (long long)lddx, (long long)w->n_cols);
+    if ((u == nullptr) != (lora_a == nullptr))
+        return fail(NF4B200_EINVAL, "u and lora_a must both be given or both be NULL");
+    if (u && (!aligned16(u) || !aligned16(lora_a)))
+        return fail(NF4B200_EINVAL, "u / lora_a are not 16-byte aligned");
+    nf4::GemmArgs g;
+    fill_gemm(g, w, d->sms);
+    g.act = static_cast<const __half*>(dy); g.m = m; g.ld_act = lddy;
+    g.out = static_cast<__half*>(dx); g.ld_out = lddx;
+    g.bias = nullptr;
+    g.ext_a = static_cast<const __half*>(u);
+    g.ext_b = static_cast<const __half*>(lora_a);
+    g.trans_w = true;
+    const char* why = "";
+    cudaError_t e = nf4::launch_gemm(g, static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess)
+        return fail(NF4B200_ECUDA, "linear_bwd_dx: %s: %s", why, cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_lora_down(const void* in, int64_t m, int64_t c, int64_t ld_in, const void* p,
+                      int64_t p_stride_r, int64_t p_stride_c, float scaling, void* out,
+                      void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (!in || !p || !out) return fail(NF4B200_EINVAL, "lora_down: NULL pointer");
+    if (m <= 0 || c <= 0 || ld_in < c) return fail(NF4B200_EINVAL, "lora_down: bad shape");
+    if ((reinterpret_cast<uintptr_t>(out) & 3u) != 0)
+        return fail(NF4B200_EINVAL, "lora_down: out is not 4-byte aligned");
+    nf4::LoraDownArgs a{static_cast<const __half*>(in), m, c, ld_in, static_cast<const __half*>(p),
+                        p_stride_r, p_stride_c, scaling, static_cast<__half*>(out)};
+    cudaError_t e = nf4::launch_lora_down(a, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "lora_down launch: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_lora_grad(const void* z, int64_t m, int64_t c, int64_t ld_z, const void* s, float* out,
+                      int64_t o_stride_r, int64_t o_stride_c, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (!z || !s || !out) return fail(NF4B200_EINVAL, "lora_grad: NULL pointer");
+    if (m <= 0 || c <= 0 || ld_z < c) return fail(NF4B200_EINVAL, "lora_grad: bad shape");
+    nf4::LoraGradArgs a{static_cast<const __half*>(z), m, c, ld_z, static_cast<const __half*>(s),
+                        out, o_stride_r, o_stride_c, d->sms};
+    cudaError_t e = nf4::launch_lora_grad(a, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "lora_grad launch: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+}  // extern "C"

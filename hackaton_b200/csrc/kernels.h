@@ -1,0 +1,79 @@
+// Internal launch interface between the C-ABI layer (capi.cu) and the kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nf4 {
+
+struct DequantArgs {
+    const void* codes;
+    const void* absmax;
+    const float* code2;
+    const float* absmax2;
+    const float* offset;
+    const float* code16;
+    void* out;
+    long long n;  // number of weights
+    int blocksize;
+    int nested_blocksize;
+    int nested;
+    int out_dtype;  // 0 fp16, 1 bf16, 2 fp32
+    int sm_count;
+};
+
+cudaError_t launch_dequant(const DequantArgs& a, cudaStream_t stream);
+
+// Fused dequant-GEMM. trans_w == false: out[M, N_w] = act[M, K_w] . W^T (forward).
+// trans_w == true: out[M, K_w] = act[M, N_w] . W (input gradient).
+struct GemmArgs {
+    const uint8_t* codes;
+    const void* absmax;
+    const float* code2;
+    const float* absmax2;
+    const float* offset;
+    const float* code16;
+    long long n_w, k_w;
+    int nested;
+    int nested_blocksize;
+    const __half* act;
+    long long m, ld_act;
+    __half* out;
+    long long ld_out;
+    const __half* bias;   // forward only, may be null
+    const __half* ext_a;  // [M, 16] fp16 rank-16 left factor (xa or u), may be null
+    const __half* ext_b;  // forward: lora_b [N_w, 16]; backward: lora_a [16, K_w]
+    bool trans_w;
+    int sm_count;
+};
+
+// Returns cudaSuccess or the failing CUDA error; `why` receives a short reason on failure.
+cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why);
+
+struct LoraDownArgs {
+    const __half* in;
+    long long m, c, ld_in;
+    const __half* p;
+    long long p_stride_r, p_stride_c;
+    float scaling;
+    __half* out;
+};
+cudaError_t launch_lora_down(const LoraDownArgs& a, cudaStream_t stream);
+
+struct LoraGradArgs {
+    const __half* z;
+    long long m, c, ld_z;
+    const __half* s;
+    float* out;
+    long long o_stride_r, o_stride_c;
+    int sm_count;
+};
+cudaError_t launch_lora_grad(const LoraGradArgs& a, cudaStream_t stream);
+
+// Device-side status word: 0, or a code written by a kernel whose bounded wait ran out.
+int* device_status_word();   // device address of the word for the current device
+cudaError_t read_and_clear_device_status(int* out);
+
+}  // namespace nf4

@@ -1,0 +1,105 @@
+"""Patches that route bitsandbytes' 4-bit matmul and peft's LoRA-on-4-bit forward through the
+B200 kernels: the plug-in boundary of the reference (solution/patches.py:251-277 and
+solution/__init__.py:23-33), for the NF4 path only.
+
+As in the reference, a call the kernels do not cover goes to the function that was there before
+the patch (bitsandbytes' or peft's own code), never to a CPU path of this package.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .lora import RANK, nf4_lora_linear
+from .nf4 import can_dequantize, nf4_linear
+
+
+def _is_4bit_linear(module):
+    """solution/patches.py:12-17."""
+    try:
+        import bitsandbytes as bnb
+    except ImportError:
+        return False
+    return isinstance(module, bnb.nn.Linear4bit)
+
+
+def _eligible(A, state, packed, bias):
+    """The reference's guard (solution/patches.py:266-272) without its two T4-only limits: the
+    minimum weight size (MIN_NF4_WEIGHTS, there to save per-launch CPU time in the contest) and
+    the "more than 4 rows" rule (small batches take the same fused kernel here). Nested states
+    are accepted; the compute dtype must be fp16 and K a multiple of 64."""
+    return (state is not None and isinstance(A, torch.Tensor) and A.is_cuda and A.dim() >= 2
+            and len(getattr(state, "shape", ())) == 2 and A.shape[-1] == state.shape[1]
+            and A.dtype == torch.float16 and getattr(state, "dtype", None) == torch.float16
+            and getattr(state, "blocksize", 0) == 64 and state.shape[1] % 64 == 0
+            and can_dequantize(packed.reshape(-1), state)
+            and (bias is None or bias.dtype == A.dtype))
+
+
+def patch_nf4_matmul():
+    """Replaces `bitsandbytes.matmul_4bit(A, B, quant_state, out=None, bias=None)` (the call every
+    `Linear4bit.forward` makes) by the fused NF4 linear; see solution/patches.py:251-277."""
+    import bitsandbytes as bnb
+
+    original = bnb.matmul_4bit
+    if getattr(original, "_nf4b200", False):
+        return
+
+    def matmul_4bit(A, B, quant_state, out=None, bias=None):
+        if out is None and _eligible(A, quant_state, B, bias):
+            return nf4_linear(A, B, bias, quant_state)
+        return original(A, B, quant_state, out=out, bias=bias)
+
+    matmul_4bit._nf4b200 = True
+    matmul_4bit._original = original
+    bnb.matmul_4bit = matmul_4bit
+
+
+def lora_forward_for(original):
+    """Builds the replacement for peft's `lora.bnb.Linear4bit.forward`. Module attributes used:
+    `base_layer` (a bnb `Linear4bit`: `.weight` with `.quant_state`, `.bias`), `lora_A`,
+    `lora_B`, `lora_dropout`, `scaling` (dicts keyed by adapter name), `active_adapters`,
+    `disable_adapters`, `merged` (names as in the reference's tools/probe.py:127-129)."""
+
+    def forward(self, x, *args, **kwargs):
+        adapters = list(getattr(self, "active_adapters", ()))
+        base = getattr(self, "base_layer", None)
+        weight = getattr(base, "weight", None)
+        state = getattr(weight, "quant_state", None)
+        if (args or kwargs or getattr(self, "disable_adapters", False)
+                or getattr(self, "merged", False) or len(adapters) != 1
+                or adapters[0] not in self.lora_A or weight is None
+                or not _eligible(x, state, weight, getattr(base, "bias", None))):
+            return original(self, x, *args, **kwargs)
+        name = adapters[0]
+        lora_a, lora_b = self.lora_A[name].weight, self.lora_B[name].weight
+        if lora_a.shape[0] != RANK or getattr(self.lora_A[name], "bias", None) is not None \
+                or getattr(self.lora_B[name], "bias", None) is not None:
+            return original(self, x, *args, **kwargs)
+        dropout = self.lora_dropout[name]
+        x_lora = dropout(x) if (dropout.training and getattr(dropout, "p", 0.0) > 0.0) else x
+        return nf4_lora_linear(x, weight, base.bias, state, lora_a, lora_b,
+                               float(self.scaling[name]), x_lora=x_lora)
+
+    forward._nf4b200 = True
+    forward._original = original
+    return forward
+
+
+def patch_peft_lora():
+    """Replaces the forward of peft's LoRA wrapper around 4-bit linears by the fused kernel."""
+    try:
+        from peft.tuners.lora import bnb as peft_bnb
+    except ImportError:
+        return
+    cls = getattr(peft_bnb, "Linear4bit", None)
+    if cls is None or getattr(cls.forward, "_nf4b200", False):
+        return
+    cls.forward = lora_forward_for(cls.forward)
+
+
+def apply():
+    """The entry point the reference's harness calls once before the model is built
+    (solution/__init__.py:23-33), restricted to the NF4 path."""
+    patch_nf4_matmul()
+    patch_peft_lora()

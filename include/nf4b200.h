@@ -1,0 +1,125 @@
+/*
+ * nf4b200 — C ABI of the B200 (sm_100a) NF4 dequant / fused dequant-GEMM / LoRA kernels.
+ *
+ * Plain pointers and sizes only; every pointer is a CUDA device pointer owned by the caller and
+ * borrowed for the duration of the enqueue. `stream` is a cudaStream_t passed as void*. Calls
+ * are asynchronous with respect to the host; they allocate no device memory. All functions
+ * return 0 on success or a negative NF4B200_E* code; nf4b200_last_error() then gives a message
+ * for the calling thread. There is no CPU fallback: on a device that is not compute capability
+ * 10.x every compute entry point returns NF4B200_EARCH.
+ *
+ * "Replaces" comments cite the reference project (mergentlegen/hackaton) by file:line.
+ */
+#ifndef NF4B200_H
+#define NF4B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NF4B200_OK 0
+#define NF4B200_EINVAL (-1)  /* bad argument: shape, alignment, dtype, null pointer */
+#define NF4B200_EARCH (-2)   /* device is not sm_100 */
+#define NF4B200_ECUDA (-3)   /* a CUDA runtime / driver call failed */
+#define NF4B200_EDEVICE (-4) /* a kernel reported a bounded-wait timeout */
+
+enum { NF4B200_F16 = 0, NF4B200_BF16 = 1, NF4B200_F32 = 2 };
+
+/*
+ * One NF4 weight W[n_rows, n_cols] in bitsandbytes layout: the fields of bitsandbytes'
+ * QuantState that the reference reads (solution/nf4.py:55-76, solution/packed.py:71-79).
+ * Flat element i = row * n_cols + col lives in byte i / 2 (even element = high nibble);
+ * `blocksize` consecutive flat elements share one scale.
+ */
+typedef struct nf4b200_weight {
+    const void* codes;      /* uint8 [n_rows * n_cols / 2], 16-byte aligned */
+    const void* absmax;     /* nested != 0: uint8 [n_blocks]; nested == 0: float [n_blocks] */
+    const float* code2;     /* nested: float [256], second-level table; else NULL */
+    const float* absmax2;   /* nested: float [ceil(n_blocks / nested_blocksize)]; else NULL */
+    const float* offset;    /* nested: pointer to one float on the device; else NULL */
+    const float* code16;    /* float [16]: the 4-bit table (quant_state.code) */
+    int64_t n_rows;         /* N, output features */
+    int64_t n_cols;         /* K, input features */
+    int32_t blocksize;      /* weights per first-level scale (64) */
+    int32_t nested_blocksize; /* scales per second-level scale (256) */
+    int32_t nested;         /* 1: double-quantised scales, 0: flat fp32 scales */
+    int32_t reserved;
+} nf4b200_weight;
+
+/* Device / build facts. */
+typedef struct nf4b200_props {
+    int32_t cc_major, cc_minor, sm_count, supported;
+    int64_t smem_per_block_optin;
+} nf4b200_props;
+
+int nf4b200_query(int device, nf4b200_props* out);
+
+/* Message for the last non-zero status returned on this thread ("" if none). */
+const char* nf4b200_last_error(void);
+
+/*
+ * Reads and clears the device-side status word of the current device (synchronises the device).
+ * 0 = no kernel reported a timeout since the last call.
+ */
+int nf4b200_device_status(int* status_out);
+
+/*
+ * Standalone decode: out[n_rows, n_cols] = table[code] * scale, one rounding to out_dtype.
+ * Replaces nf4_dequant_kernel / dequantize_nf4 (solution/nf4.py:28-44, 67-77) and, for nested
+ * weights, the scale pre-pass _flatten_quant_states (solution/packed.py:57-79).
+ * Needs n_rows * n_cols % 8 == 0 and blocksize % 8 == 0 (as solution/nf4.py:61-63).
+ */
+int nf4b200_dequant(const nf4b200_weight* w, void* out, int out_dtype, void* stream);
+
+/*
+ * Forward of the frozen-weight linear, decode fused into the GEMM:
+ *   y[m, n_rows] = x[m, n_cols] . W^T (+ bias) (+ xa[m, rank] . lora_b[n_rows, rank]^T)
+ * fp16 in, fp32 accumulate (tcgen05 / TMEM), fp16 out. Replaces NF4Linear.forward
+ * (solution/nf4.py:87-92): dequantize_nf4 + torch.nn.functional.linear.
+ * x: fp16, row stride ldx elements (ldx % 8 == 0, 16-byte aligned base). y likewise with ldy.
+ * bias: fp16 [n_rows] or NULL. LoRA (rank 16): xa = scaling * x . A^T as fp16 [m, 16]
+ * (see nf4b200_lora_down), lora_b fp16 [n_rows, 16]; pass NULL for both to skip it.
+ * Needs n_cols % 64 == 0, blocksize == 64.
+ */
+int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_t ldx,
+                       const void* bias, const void* xa, const void* lora_b, void* y, int64_t ldy,
+                       void* stream);
+
+/*
+ * Input gradient of the same linear, decode fused:
+ *   dx[m, n_cols] = dy[m, n_rows] . W (+ u[m, rank] . lora_a[rank, n_cols])
+ * Replaces NF4Linear.backward (solution/nf4.py:94-99): a second dequantize_nf4 + torch.matmul.
+ * u = scaling * dy . B as fp16 [m, 16] (nf4b200_lora_down), lora_a fp16 [16, n_cols]; NULL to skip.
+ */
+int nf4b200_linear_bwd_dx(const nf4b200_weight* w, const void* dy, int64_t m, int64_t lddy,
+                          const void* u, const void* lora_a, void* dx, int64_t lddx, void* stream);
+
+/*
+ * Rank-16 projection used by both passes of the LoRA update (peft's lora_A / lora_B linears;
+ * third-party in the reference, configured at README.md:91 and task/task.yaml:18-21):
+ *   out[m, 16] = scaling * in[m, c] . P        (fp16 in, fp32 accumulate, fp16 out)
+ * P[c][j] is read at p[c * p_stride_c + j * p_stride_r]: (p_stride_r, p_stride_c) = (c, 1) for
+ * a row-major [16, c] matrix (lora_A, forward), (1, 16) for a row-major [c, 16] matrix (lora_B,
+ * backward).
+ */
+int nf4b200_lora_down(const void* in, int64_t m, int64_t c, int64_t ld_in, const void* p,
+                      int64_t p_stride_r, int64_t p_stride_c, float scaling, void* out,
+                      void* stream);
+
+/*
+ * Rank-16 weight gradients (contraction over the m rows, fp32 accumulate, fp32 out):
+ *   out[c][j] (at out + c * o_stride_c + j * o_stride_r) = sum_m z[m, c] * s[m, j]
+ * dA[16, K] = u^T . x  -> z = x, s = u, strides (o_stride_r, o_stride_c) = (K, 1);
+ * dB[N, 16] = dy^T . xa -> z = dy, s = xa, strides (1, 16).
+ * `out` must be zeroed by the caller (partial sums are added atomically).
+ */
+int nf4b200_lora_grad(const void* z, int64_t m, int64_t c, int64_t ld_z, const void* s,
+                      float* out, int64_t o_stride_r, int64_t o_stride_c, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NF4B200_H */

@@ -1,0 +1,152 @@
+"""Plain numpy / torch-CPU restatement of the reference's NF4 hot path (test infrastructure).
+
+Every function names the reference lines it follows. Parity status is stated in the package
+docstring (oracle/__init__.py): the flat decode and the linear are pinned by golden vectors made
+with the reference's own code; the nested-absmax decode and LoRA are "parity unpinned".
+
+Byte and nibble layout (solution/nf4.py:7-14, 33-44): flat element i of the row-major weight sits
+in byte i // 2; the even element is the HIGH nibble, the odd one the LOW nibble; `blocksize`
+consecutive flat elements share one scale. value = table[code] * scale in fp32, rounded once to
+the output dtype.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+
+# --------------------------------------------------------------------------------------------
+# decode
+# --------------------------------------------------------------------------------------------
+
+def flatten_absmax(absmax_u8, code2, absmax2, offset, nested_blocksize=256):
+    """Two-level scales -> flat fp32 scales.
+
+    Follows solution/packed.py:74-77 and solution/test_nf4.py:23-26: a blockwise 8-bit decode
+    (`code2[u8] * absmax2[i // nested_blocksize]`, one fp32 multiply) followed by an in-place
+    fp32 `+= offset` (a second, separately rounded fp32 op; never a fused multiply-add).
+    """
+    absmax_u8 = np.asarray(absmax_u8, dtype=np.uint8).reshape(-1)
+    code2 = np.asarray(code2, dtype=np.float32).reshape(-1)
+    absmax2 = np.asarray(absmax2, dtype=np.float32).reshape(-1)
+    idx = np.arange(absmax_u8.size, dtype=np.int64) // nested_blocksize
+    prod = (code2[absmax_u8] * absmax2[idx]).astype(np.float32)
+    return (prod + np.float32(offset)).astype(np.float32)
+
+
+def nibbles(packed):
+    """Packed bytes -> 4-bit codes in flat element order (high nibble first, nf4.py:8,34,40)."""
+    packed = np.asarray(packed, dtype=np.uint8).reshape(-1)
+    out = np.empty(packed.size * 2, dtype=np.uint8)
+    out[0::2] = packed >> 4
+    out[1::2] = packed & 15
+    return out
+
+
+def dequant_flat(packed, absmax_f32, code16, shape, blocksize=64, dtype=torch.float16):
+    """Decode with flat fp32 scales: solution/nf4.py:33-44 (one fp32 multiply, one rounding).
+
+    Returns a torch CPU tensor of `shape` and `dtype` (fp16, bf16 or fp32).
+    """
+    n = int(np.prod(shape))
+    codes = nibbles(packed)[:n]
+    table = np.asarray(code16, dtype=np.float32).reshape(-1)
+    scale = np.asarray(absmax_f32, dtype=np.float32).reshape(-1)
+    block = np.arange(n, dtype=np.int64) // blocksize
+    value = (table[codes] * scale[block]).astype(np.float32)
+    out = torch.from_numpy(value).to(dtype)  # round-to-nearest-even, one rounding
+    return out.reshape(tuple(shape))
+
+
+def dequant_nested(packed, absmax_u8, code2, absmax2, offset, code16, shape, blocksize=64,
+                   nested_blocksize=256, dtype=torch.float16):
+    """Double-quantised layout decoded in one go: flatten_absmax, then dequant_flat."""
+    flat = flatten_absmax(absmax_u8, code2, absmax2, offset, nested_blocksize)
+    return dequant_flat(packed, flat, code16, shape, blocksize, dtype)
+
+
+# --------------------------------------------------------------------------------------------
+# linear (solution/nf4.py:80-102) and LoRA (peft's `Linear.forward`, configured at
+# README.md:91 / task/task.yaml:18-21 of the reference; not in its tree)
+# --------------------------------------------------------------------------------------------
+
+def linear_fwd(x, weight, bias=None):
+    """Y = X Wᵀ (+ bias), fp32 accumulate, result in x's dtype (nf4.py:87-92)."""
+    y = x.float() @ weight.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype)
+
+
+def linear_bwd(grad_y, weight):
+    """dX = dY W, fp32 accumulate (nf4.py:94-99)."""
+    return (grad_y.float() @ weight.float()).to(grad_y.dtype)
+
+
+def bias_grad(grad_y, dtype):
+    """dbias = dY summed over rows (nf4.py:100-101)."""
+    return grad_y.reshape(-1, grad_y.shape[-1]).float().sum(0).to(dtype)
+
+
+def lora_fwd(x, weight, lora_a, lora_b, scaling, bias=None):
+    """Y = X Wᵀ (+ bias) + scaling * (X Aᵀ) Bᵀ with the low-rank product kept in fp32.
+
+    A is [r, K], B is [N, r]. Returns (Y, XA) where XA = X Aᵀ in fp32 (the tensor a fused kernel
+    hands to the backward pass).
+    """
+    xa = x.float() @ lora_a.float().t()
+    y = x.float() @ weight.float().t() + scaling * (xa @ lora_b.float().t())
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype), xa
+
+
+def lora_bwd(grad_y, x, weight, lora_a, lora_b, scaling):
+    """Gradients of lora_fwd w.r.t. X, A and B (W frozen), fp32 accumulate.
+
+    dX = dY W + scaling * (dY B) A;  dA = scaling * (dY B)ᵀ X;  dB = scaling * dYᵀ (X Aᵀ).
+    """
+    gy, xf = grad_y.float(), x.float()
+    a, b = lora_a.float(), lora_b.float()
+    gyb = gy @ b                                  # [M, r]
+    dx = gy @ weight.float() + scaling * (gyb @ a)
+    da = scaling * (gyb.t() @ xf)                 # [r, K]
+    db = scaling * (gy.t() @ (xf @ a.t()))        # [N, r]
+    return dx.to(grad_y.dtype), da, db
+
+
+def max_rel_err(got, want):
+    """max |got - want| / max |want| : the error measure of the fp16 tolerance (<= 1e-2)."""
+    got, want = got.float(), want.float()
+    denom = want.abs().max().clamp_min(1e-30)
+    return float((got - want).abs().max() / denom)
+
+
+# --------------------------------------------------------------------------------------------
+# threaded variant for the timed CPU baseline
+# --------------------------------------------------------------------------------------------
+
+def dequant_torch(packed, absmax, code16, shape, blocksize=64, dtype=torch.float16, code2=None,
+                  absmax2=None, offset=None, nested_blocksize=256):
+    """Same arithmetic as dequant_flat / dequant_nested written with torch CPU ops, so that it
+    uses all host threads: the reference's plain-PyTorch decode path timed as the CPU baseline
+    (its decode, solution/nf4.py:33-44, followed by F.linear / matmul, :87-99)."""
+    packed = torch.as_tensor(packed).reshape(-1)
+    n = 1
+    for d in shape:
+        n *= int(d)
+    table = torch.as_tensor(code16, dtype=torch.float32)
+    if code2 is not None:
+        q = torch.as_tensor(absmax).reshape(-1).long()
+        idx = torch.arange(q.numel()) // nested_blocksize
+        scale = torch.as_tensor(code2, dtype=torch.float32)[q] * \
+            torch.as_tensor(absmax2, dtype=torch.float32)[idx]
+        scale = scale + torch.as_tensor(offset, dtype=torch.float32)
+    else:
+        scale = torch.as_tensor(absmax, dtype=torch.float32).reshape(-1)
+    hi = table[(packed >> 4).long()]
+    lo = table[(packed & 15).long()]
+    value = torch.stack((hi, lo), dim=1).reshape(-1)[:n]
+    value = (value.view(-1, blocksize) * scale[:, None]).reshape(-1)
+    return value.to(dtype).reshape(tuple(shape))

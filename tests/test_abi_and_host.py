@@ -1,0 +1,105 @@
+"""CPU: the C-ABI library builds, loads and exports every symbol include/nf4b200.h declares;
+host-side guards and patches behave like the reference's (no compute calls here)."""
+
+import ctypes
+import re
+import sys
+import types
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture(scope="module")
+def library():
+    from hackaton_b200.build import build_library
+
+    return ctypes.CDLL(str(build_library()))
+
+
+def declared_functions():
+    text = (ROOT / "include" / "nf4b200.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nf4b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported(library):
+    names = declared_functions()
+    assert len(names) >= 8
+    for name in names:
+        assert hasattr(library, name), f"{name} declared in nf4b200.h but not exported"
+
+
+def test_binding_covers_the_header():
+    from hackaton_b200 import _lib
+
+    assert sorted(_lib.EXPORTS) == declared_functions()
+
+
+def test_struct_layout_matches_header():
+    from hackaton_b200 import _lib
+
+    assert ctypes.sizeof(_lib.Weight) == 6 * 8 + 2 * 8 + 4 * 4
+    assert ctypes.sizeof(_lib.Props) == 4 * 4 + 8
+
+
+def test_no_gpu_means_error_not_fallback(library):
+    """Without a CUDA device every compute entry point reports an error status."""
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    from hackaton_b200 import _lib
+
+    w = _lib.Weight()
+    rc = _lib.lib().nf4b200_dequant(ctypes.byref(w), None, 0, None)
+    assert rc != 0
+    assert _lib.lib().nf4b200_last_error()
+
+
+def test_can_dequantize_guards():
+    from hackaton_b200 import can_dequantize
+    from tests.util import synthetic_weight
+
+    packed, state = synthetic_weight(8, 64, True)
+    assert not can_dequantize(packed, state)           # CPU tensors: never eligible
+    assert not can_dequantize("not a tensor", state)
+
+
+def test_product_does_not_import_the_oracle():
+    for path in (ROOT / "hackaton_b200").rglob("*.py"):
+        text = path.read_text()
+        assert "oracle" not in re.sub(r'""".*?"""', "", text, flags=re.S), path
+
+
+def test_matmul_patch_falls_through_to_original(monkeypatch):
+    """solution/patches.py:266-275: whatever the kernels do not cover goes to the function that
+    was installed before (here a fake bitsandbytes)."""
+    calls = []
+    fake = types.ModuleType("bitsandbytes")
+    fake.matmul_4bit = lambda A, B, quant_state, out=None, bias=None: calls.append("orig") or "orig"
+    fake.nn = types.SimpleNamespace(Linear4bit=type("Linear4bit", (), {}))
+    monkeypatch.setitem(sys.modules, "bitsandbytes", fake)
+    from hackaton_b200 import patches
+
+    patches.patch_nf4_matmul()
+    patched = fake.matmul_4bit
+    assert patched._nf4b200
+    patches.patch_nf4_matmul()                      # idempotent
+    assert fake.matmul_4bit is patched
+    x = torch.zeros(8, 64, dtype=torch.float16)     # CPU tensor -> not eligible
+    assert fake.matmul_4bit(x, torch.zeros(1, 8, dtype=torch.uint8), None) == "orig"
+    assert calls == ["orig"]
+    assert patches._is_4bit_linear(fake.nn.Linear4bit())
+    assert not patches._is_4bit_linear(object())
+
+
+def test_lora_patch_falls_through_to_original():
+    from hackaton_b200 import patches
+
+    seen = []
+    forward = patches.lora_forward_for(lambda self, x, *a, **k: seen.append(1) or "orig")
+    module = types.SimpleNamespace(active_adapters=["default"], disable_adapters=True,
+                                   merged=False, base_layer=None, lora_A={}, lora_B={})
+    assert forward(module, torch.zeros(2, 64)) == "orig" and seen == [1]

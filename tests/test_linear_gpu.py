@@ -1,0 +1,121 @@
+"""GPU: the fused dequant-GEMM (forward x.Wᵀ, backward dy.W) through the C ABI against the CPU
+oracle, at fp16 tolerance: max |err| / max |ref| <= 1e-2 (the bound the task states), and the
+reference's own rtol = atol = 2e-3 (solution/test_nf4.py:63-64) where K is small enough for it."""
+
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from hackaton_b200.quantize import QuantState
+from oracle import nf4_oracle
+from tests.util import oracle_weight, synthetic_weight
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+TOL = 1e-2
+
+
+def rel(got, want):
+    return nf4_oracle.max_rel_err(got.cpu(), want)
+
+
+def run_case(m, n, k, nested, bias, seed=0):
+    from hackaton_b200 import nf4_linear
+
+    packed, state = synthetic_weight(n, k, nested, seed=seed, device="cuda")
+    w = oracle_weight(packed, state)
+    g = torch.Generator().manual_seed(seed + 1)
+    x = torch.randn(m, k, generator=g).half()
+    dy = torch.randn(m, n, generator=g).half()
+    b = (torch.randn(n, generator=g) * 0.1).half() if bias else None
+    xg = x.cuda().requires_grad_()
+    y = nf4_linear(xg, packed.t(), None if b is None else b.cuda(), state)
+    y.backward(dy.cuda())
+    torch.cuda.synchronize()
+    return rel(y, nf4_oracle.linear_fwd(x, w, b)), rel(xg.grad, nf4_oracle.linear_bwd(dy, w))
+
+
+# (M, N, K): the reference's test shape, tile-aligned and ragged ones, single rows, N < tile
+CASES = [(300, 512, 1536), (256, 256, 64), (128, 256, 128), (1, 256, 64), (4, 1536, 1536),
+         (77, 100 * 8, 192), (513, 264, 320), (2048, 256, 1536), (130, 8, 64)]
+
+
+@pytest.mark.parametrize("m,n,k", CASES)
+@pytest.mark.parametrize("nested", [True, False])
+def test_linear_forward_backward_vs_oracle(cuda_lib, m, n, k, nested):
+    ef, eb = run_case(m, n, k, nested, bias=(n % 16 == 0), seed=m + n + k)
+    assert ef <= TOL, f"forward max rel err {ef}"
+    assert eb <= TOL, f"backward max rel err {eb}"
+    cuda_lib.device_status()
+
+
+def test_config0_q_proj(cuda_lib):
+    """BASELINE config 0: W[1536,1536], X[2048,1536]."""
+    ef, eb = run_case(2048, 1536, 1536, True, bias=False, seed=0)
+    assert ef <= TOL and eb <= TOL, (ef, eb)
+
+
+def test_mlp_shapes(cuda_lib):
+    """gate/up (8960 <- 1536) and down (1536 <- 8960) at a reduced token count."""
+    for n, k in [(8960, 1536), (1536, 8960)]:
+        ef, eb = run_case(384, n, k, True, bias=False, seed=n)
+        assert ef <= TOL and eb <= TOL, (n, k, ef, eb)
+
+
+def test_matches_reference_golden_linear(cuda_lib):
+    from hackaton_b200 import nf4_linear
+
+    g = np.load(GOLDEN / "linear_small.npz")
+    state = QuantState(absmax=torch.from_numpy(g["absmax"]).cuda(),
+                       code=torch.from_numpy(g["table"]).cuda(), shape=(96, 192))
+    x = torch.from_numpy(g["x"]).cuda().requires_grad_()
+    out = nf4_linear(x, torch.from_numpy(g["packed"]).cuda().view(-1, 1).t(),
+                     torch.from_numpy(g["bias"]).cuda(), state)
+    out.backward(torch.from_numpy(g["grad"]).cuda())
+    torch.testing.assert_close(out.detach().cpu(), torch.from_numpy(g["out"]), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(x.grad.cpu(), torch.from_numpy(g["grad_x"]), rtol=2e-3, atol=2e-3)
+
+
+def test_leading_dims_and_strided_rows(cuda_lib):
+    from hackaton_b200 import nf4_linear
+
+    packed, state = synthetic_weight(256, 128, True, seed=4, device="cuda")
+    w = oracle_weight(packed, state)
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(3, 50, 256, generator=g).half()
+    xs = x.cuda()[..., :128]  # row stride 256, 128 columns used
+    y = nf4_linear(xs, packed, None, state)
+    assert y.shape == (3, 50, 256)
+    assert rel(y.reshape(-1, 256), nf4_oracle.linear_fwd(x[..., :128].reshape(-1, 128), w)) <= TOL
+
+
+def test_linearity_at_full_size(cuda_lib):
+    """Size-independent property at the full 8960x1536 shape with M = 2048: f(a + b) = f(a) + f(b)
+    up to fp16 rounding, and the bias gradient equals the column sums of dy."""
+    from hackaton_b200 import nf4_linear
+
+    packed, state = synthetic_weight(8960, 1536, True, seed=3, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(1)
+    a = torch.randn(2048, 1536, generator=g, device="cuda").half()
+    b = torch.randn(2048, 1536, generator=g, device="cuda").half()
+    ya, yb, yab = (nf4_linear(t, packed, None, state).float() for t in (a, b, (a + b)))
+    assert float((yab - ya - yb).abs().max() / yab.abs().max()) <= TOL
+    bias = torch.zeros(8960, device="cuda", dtype=torch.float16, requires_grad=True)
+    dy = torch.randn(2048, 8960, generator=g, device="cuda").half()
+    nf4_linear(a, packed, bias, state).backward(dy)
+    torch.testing.assert_close(bias.grad.float(), dy.float().sum(0), rtol=2e-2, atol=2e-1)
+
+
+def test_bad_arguments_raise(cuda_lib):
+    from hackaton_b200 import nf4_linear
+
+    packed, state = synthetic_weight(64, 128, True, seed=4, device="cuda")
+    with pytest.raises(TypeError):
+        nf4_linear(torch.randn(4, 128, device="cuda"), packed, None, state)  # fp32 input
+    with pytest.raises(ValueError):
+        nf4_linear(torch.randn(4, 64, device="cuda").half(), packed, None, state)  # wrong K
+    packed2, state2 = synthetic_weight(64, 96, False, seed=4, device="cuda")  # K % 64 != 0
+    with pytest.raises(cuda_lib.Nf4Error):
+        nf4_linear(torch.randn(4, 96, device="cuda").half(), packed2, None, state2)

@@ -1,0 +1,120 @@
+"""CPU: the oracle against the golden vectors made with the reference's own code
+(tests/golden/make_golden.py), and the C restatement against the numpy one."""
+
+import ctypes
+import hashlib
+import json
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nf4_oracle
+from tests.util import random_case, synthetic_weight, oracle_weight
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+DTYPES = {0: torch.float16, 1: torch.bfloat16, 2: torch.float32}
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def to_numpy(t):
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().view(np.uint16)
+    return t.numpy()
+
+
+@pytest.mark.parametrize("name", list("abcde"))
+def test_flat_decode_matches_reference_kernel(name):
+    g = np.load(GOLDEN / "decode_small.npz")
+    rows, cols, bs, dt = (int(v) for v in g[f"{name}_meta"])
+    out = nf4_oracle.dequant_flat(g[f"{name}_packed"], g[f"{name}_absmax"], g["table"],
+                                  (rows, cols), bs, DTYPES[dt])
+    assert np.array_equal(to_numpy(out), g[f"{name}_out"])
+
+
+@pytest.mark.parametrize("shape", ["256x1536", "1536x1536", "1536x8960"])
+def test_flat_decode_digest_full_size(shape):
+    d = json.loads((GOLDEN / "decode_digests.json").read_text())[shape]
+    rows, cols = (int(v) for v in shape.split("x"))
+    packed, absmax = random_case(d["seed"], rows, cols)
+    assert sha(packed) == d["packed_sha256"] and sha(absmax) == d["absmax_sha256"], \
+        "numpy's seeded stream changed: regenerate tests/golden"
+    from hackaton_b200.quantize import NF4_TABLE
+    out = nf4_oracle.dequant_flat(packed, absmax, np.asarray(NF4_TABLE, np.float32), (rows, cols))
+    assert sha(out.numpy()) == d["out_sha256"]
+
+
+def test_linear_matches_reference_autograd_function():
+    g = np.load(GOLDEN / "linear_small.npz")
+    w = nf4_oracle.dequant_flat(g["packed"], g["absmax"], g["table"], (96, 192))
+    x, grad, bias = (torch.from_numpy(g[k]) for k in ("x", "grad", "bias"))
+    out = nf4_oracle.linear_fwd(x, w, bias)
+    gx = nf4_oracle.linear_bwd(grad, w)
+    torch.testing.assert_close(out, torch.from_numpy(g["out"]), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(gx, torch.from_numpy(g["grad_x"]), rtol=2e-3, atol=2e-3)
+
+
+def test_nested_scales_are_two_roundings():
+    rng = np.random.default_rng(3)
+    q = rng.integers(0, 256, size=1000, dtype=np.uint8)
+    code2 = np.sort(rng.uniform(-1, 1, 256)).astype(np.float32)
+    absmax2 = rng.uniform(0.01, 0.1, 4).astype(np.float32)
+    flat = nf4_oracle.flatten_absmax(q, code2, absmax2, 0.0371, 256)
+    want = (code2[q] * absmax2[np.arange(1000) // 256]).astype(np.float32) + np.float32(0.0371)
+    assert flat.dtype == np.float32 and np.array_equal(flat, want)
+
+
+@pytest.fixture(scope="module")
+def c_oracle():
+    folder = Path(__file__).resolve().parents[1] / "oracle"
+    subprocess.run(["make", "-C", str(folder), "libnf4_oracle.so"], check=True,
+                   stdout=subprocess.DEVNULL)
+    return ctypes.CDLL(str(folder / "libnf4_oracle.so"))
+
+
+@pytest.mark.parametrize("nested", [False, True])
+def test_c_restatement_equals_numpy(c_oracle, nested):
+    packed, state = synthetic_weight(96, 320, nested, seed=5)
+    want = oracle_weight(packed, state).numpy().view(np.uint16)
+    n = 96 * 320
+    out = np.empty(n, dtype=np.uint16)
+    p = packed.numpy().reshape(-1)
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    code16 = state.code.numpy()
+    if nested:
+        a, c2, a2 = state.absmax.numpy(), state.state2.code.numpy(), state.state2.absmax.numpy()
+        c_oracle.oracle_dequant_nested_f16(ptr(p), ptr(a), ptr(c2), ptr(a2),
+                                           ctypes.c_float(float(state.offset)), ptr(code16),
+                                           ctypes.c_int64(n), 64, 256, ptr(out))
+    else:
+        a = state.absmax.numpy()
+        c_oracle.oracle_dequant_flat_f16(ptr(p), ptr(a), ptr(code16), ctypes.c_int64(n), 64,
+                                         ptr(out))
+    assert np.array_equal(out, want.reshape(-1))
+
+
+def test_quantiser_round_trip_error_is_small():
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(64, 256, generator=g) * 0.02).half()
+    for nested in (False, True):
+        from hackaton_b200.quantize import quantize_nf4
+        packed, state = quantize_nf4(w, compress_statistics=nested)
+        assert packed.shape == (64 * 256 // 2, 1) and packed.dtype == torch.uint8
+        back = oracle_weight(packed, state)
+        err = (back.float() - w.float()).abs().max() / w.float().abs().max()
+        assert err < 0.2
+
+
+@pytest.mark.parametrize("nested", [False, True])
+def test_threaded_variant_equals_numpy(nested):
+    packed, state = synthetic_weight(96, 320, nested, seed=6)
+    kw = {}
+    if nested:
+        kw = dict(code2=state.state2.code, absmax2=state.state2.absmax, offset=state.offset)
+    got = nf4_oracle.dequant_torch(packed, state.absmax, state.code, (96, 320), **kw)
+    assert torch.equal(got.view(torch.int16), oracle_weight(packed, state).view(torch.int16))
