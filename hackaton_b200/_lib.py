@@ -7,7 +7,8 @@ entry point raises.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from ctypes import (POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t,
+                    c_void_p)
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libnf4b200.so"
@@ -15,6 +16,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libnf4b200.so"
 EXPORTS = (
     "nf4b200_query", "nf4b200_last_error", "nf4b200_device_status", "nf4b200_dequant",
     "nf4b200_linear_fwd", "nf4b200_linear_bwd_dx", "nf4b200_lora_down", "nf4b200_lora_grad",
+    "nf4b200_workspace_bytes",
 )
 
 F16, BF16, F32 = 0, 1, 2
@@ -60,16 +62,20 @@ def lib() -> ctypes.CDLL:
     handle.nf4b200_device_status.argtypes = [POINTER(c_int)]
     handle.nf4b200_dequant.argtypes = [POINTER(Weight), c_void_p, c_int, c_void_p]
     handle.nf4b200_linear_fwd.argtypes = [POINTER(Weight), c_void_p, c_int64, c_int64, c_void_p,
-                                          c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
+                                          c_void_p, c_void_p, c_void_p, c_int64, c_void_p,
+                                          c_size_t, c_void_p]
     handle.nf4b200_linear_bwd_dx.argtypes = [POINTER(Weight), c_void_p, c_int64, c_int64, c_void_p,
-                                             c_void_p, c_void_p, c_int64, c_void_p]
+                                             c_void_p, c_void_p, c_int64, c_void_p, c_size_t,
+                                             c_void_p]
+    handle.nf4b200_workspace_bytes.argtypes = [c_int64, c_int64, c_int64, c_int, POINTER(c_int64)]
     handle.nf4b200_lora_down.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
                                          c_int64, c_float, c_void_p, c_void_p]
     handle.nf4b200_lora_grad.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                          c_int64, c_int64, c_void_p]
     for name in EXPORTS:
-        if name != "nf4b200_last_error":
+        if name not in ("nf4b200_last_error", "nf4b200_workspace_bytes"):
             getattr(handle, name).restype = c_int
+    handle.nf4b200_workspace_bytes.restype = c_int64
     _lib = handle
     return handle
 

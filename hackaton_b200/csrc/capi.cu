@@ -138,6 +138,14 @@ void fill_gemm(nf4::GemmArgs& g, const nf4b200_weight* w, int sms) {
     g.sm_count = sms;
 }
 
+int set_workspace(nf4::GemmArgs& g, void* workspace, size_t bytes) {
+    if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+        return fail(NF4B200_EINVAL, "workspace is not 256-byte aligned");
+    g.workspace = workspace;
+    g.workspace_bytes = workspace ? bytes : 0;
+    return NF4B200_OK;
+}
+
 }  // namespace
 
 namespace nf4 {
@@ -216,7 +224,7 @@ int nf4b200_dequant(const nf4b200_weight* w, void* out, int out_dtype, void* str
 
 int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_t ldx,
                        const void* bias, const void* xa, const void* lora_b, void* y, int64_t ldy,
-                       void* stream) {
+                       void* workspace, size_t workspace_bytes, void* stream) {
     DeviceInfo* d = nullptr;
     int rc = require_sm100(&d);
     if (rc != NF4B200_OK) return rc;
@@ -237,6 +245,7 @@ int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_
     g.ext_a = static_cast<const __half*>(xa);
     g.ext_b = static_cast<const __half*>(lora_b);
     g.trans_w = false;
+    if ((rc = set_workspace(g, workspace, workspace_bytes)) != NF4B200_OK) return rc;
     const char* why = "";
     cudaError_t e = nf4::launch_gemm(g, static_cast<cudaStream_t>(stream), &why);
     if (e != cudaSuccess)
@@ -245,7 +254,8 @@ int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_
 }
 
 int nf4b200_linear_bwd_dx(const nf4b200_weight* w, const void* dy, int64_t m, int64_t lddy,
-                          const void* u, const void* lora_a, void* dx, int64_t lddx, void* stream) {
+                          const void* u, const void* lora_a, void* dx, int64_t lddx,
+                          void* workspace, size_t workspace_bytes, void* stream) {
     DeviceInfo* d = nullptr;
     int rc = require_sm100(&d);
     if (rc != NF4B200_OK) return rc;
@@ -266,11 +276,25 @@ int nf4b200_linear_bwd_dx(const nf4b200_weight* w, const void* dy, int64_t m, in
     g.ext_a = static_cast<const __half*>(u);
     g.ext_b = static_cast<const __half*>(lora_a);
     g.trans_w = true;
+    if ((rc = set_workspace(g, workspace, workspace_bytes)) != NF4B200_OK) return rc;
     const char* why = "";
     cudaError_t e = nf4::launch_gemm(g, static_cast<cudaStream_t>(stream), &why);
     if (e != cudaSuccess)
         return fail(NF4B200_ECUDA, "linear_bwd_dx: %s: %s", why, cudaGetErrorString(e));
     return NF4B200_OK;
+}
+
+int64_t nf4b200_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int backward,
+                                int64_t* counter_bytes_out) {
+    if (counter_bytes_out) *counter_bytes_out = 0;
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (n_rows <= 0 || n_cols <= 0 || m <= 0)
+        return fail(NF4B200_EINVAL, "workspace_bytes: bad shape");
+    const nf4::GemmPlan pl = nf4::plan_gemm(m, n_rows, n_cols, backward != 0, d->sms);
+    if (counter_bytes_out) *counter_bytes_out = (int64_t)pl.counter_bytes;
+    return (int64_t)(pl.counter_bytes + pl.partial_bytes);
 }
 
 int nf4b200_lora_down(const void* in, int64_t m, int64_t c, int64_t ld_in, const void* p,

@@ -47,7 +47,21 @@ struct GemmArgs {
     const __half* ext_b;  // forward: lora_b [N_w, 16]; backward: lora_a [16, K_w]
     bool trans_w;
     int sm_count;
+    void* workspace;          // split-K scratch (counters, then fp32 partial tiles); may be null
+    size_t workspace_bytes;
 };
+
+constexpr size_t GEMM_COUNTER_BYTES = 4096;  // split-K arrival counters at the workspace head
+
+// Tiling and split-K plan of one GEMM call.
+struct GemmPlan {
+    int nacc;          // 128-row accumulators per CTA (1 or 2)
+    int m_tiles, n_tiles;
+    int splits;        // CTAs sharing one tile along K
+    int kb_per_split;  // 64-deep k-blocks per CTA
+    size_t counter_bytes, partial_bytes;  // workspace layout: counters first, then partials
+};
+GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int sm_count);
 
 // Returns cudaSuccess or the failing CUDA error; `why` receives a short reason on failure.
 cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why);

@@ -118,6 +118,33 @@ def _stream_ptr(device):
     return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
 
 
+_ws_need = {}      # (device, n_rows, n_cols, m, backward) -> bytes of split-K scratch
+_ws_buffers = {}   # (device, stream) -> uint8 tensor; its counter prefix is zero between calls
+
+
+def _workspace(device, n_rows, n_cols, m, backward):
+    """Split-K scratch for one GEMM call on the current stream: (pointer, bytes) or (None, 0).
+    One buffer per (device, stream), grown on demand and zeroed when it is created: the kernels
+    leave its counters at zero, so it is never cleared again. Calls on the same stream run one
+    after the other and can share it; other streams get their own."""
+    key = (device.index, n_rows, n_cols, m, backward)
+    need = _ws_need.get(key)
+    if need is None:
+        with torch.cuda.device(device):
+            need = int(_lib.lib().nf4b200_workspace_bytes(n_rows, n_cols, m, int(backward), None))
+        if need < 0:
+            _lib.check(need)
+        _ws_need[key] = need
+    if need == 0:
+        return None, 0
+    skey = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _ws_buffers.get(skey)
+    if buf is None or buf.numel() < need:
+        buf = torch.zeros(max(need, 1 << 22), dtype=torch.uint8, device=device)
+        _ws_buffers[skey] = buf
+    return buf.data_ptr(), buf.numel()
+
+
 def _require(packed, state):
     if not can_dequantize(packed, state):
         raise ValueError(
@@ -163,12 +190,13 @@ def linear_forward(x, packed, bias, state, xa=None, lora_b=None):
         return y.reshape(*x.shape[:-1], ref.rows)
     if bias is not None:
         bias = bias.to(torch.float16).contiguous()
+    ws, ws_bytes = _workspace(x.device, ref.rows, ref.cols, m, False)
     with torch.cuda.device(x.device):
         _lib.check(_lib.lib().nf4b200_linear_fwd(
             ctypes.byref(ref.struct), x2.data_ptr(), m, x2.stride(0),
             None if bias is None else bias.data_ptr(),
             None if xa is None else xa.data_ptr(), None if lora_b is None else lora_b.data_ptr(),
-            y.data_ptr(), y.stride(0), _stream_ptr(x.device)))
+            y.data_ptr(), y.stride(0), ws, ws_bytes, _stream_ptr(x.device)))
     return y.reshape(*x.shape[:-1], ref.rows)
 
 
@@ -184,11 +212,12 @@ def linear_backward_dx(grad_output, packed, state, u=None, lora_a=None):
     dx = torch.empty((m, ref.cols), dtype=torch.float16, device=grad_output.device)
     if m == 0:
         return dx.reshape(*grad_output.shape[:-1], ref.cols)
+    ws, ws_bytes = _workspace(grad_output.device, ref.rows, ref.cols, m, True)
     with torch.cuda.device(grad_output.device):
         _lib.check(_lib.lib().nf4b200_linear_bwd_dx(
             ctypes.byref(ref.struct), g2.data_ptr(), m, g2.stride(0),
             None if u is None else u.data_ptr(), None if lora_a is None else lora_a.data_ptr(),
-            dx.data_ptr(), dx.stride(0), _stream_ptr(grad_output.device)))
+            dx.data_ptr(), dx.stride(0), ws, ws_bytes, _stream_ptr(grad_output.device)))
     return dx.reshape(*grad_output.shape[:-1], ref.cols)
 
 

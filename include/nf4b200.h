@@ -83,10 +83,13 @@ int nf4b200_dequant(const nf4b200_weight* w, void* out, int out_dtype, void* str
  * bias: fp16 [n_rows] or NULL. LoRA (rank 16): xa = scaling * x . A^T as fp16 [m, 16]
  * (see nf4b200_lora_down), lora_b fp16 [n_rows, 16]; pass NULL for both to skip it.
  * Needs n_cols % 64 == 0, blocksize == 64.
+ * workspace: split-K scratch of at least nf4b200_workspace_bytes(...) bytes, 256-byte aligned, or
+ * NULL (then one CTA walks the whole K range of its tile: correct, slower on shapes with few
+ * tiles). See nf4b200_workspace_bytes for its rules.
  */
 int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_t ldx,
                        const void* bias, const void* xa, const void* lora_b, void* y, int64_t ldy,
-                       void* stream);
+                       void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * Input gradient of the same linear, decode fused:
@@ -95,7 +98,21 @@ int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_
  * u = scaling * dy . B as fp16 [m, 16] (nf4b200_lora_down), lora_a fp16 [16, n_cols]; NULL to skip.
  */
 int nf4b200_linear_bwd_dx(const nf4b200_weight* w, const void* dy, int64_t m, int64_t lddy,
-                          const void* u, const void* lora_a, void* dx, int64_t lddx, void* stream);
+                          const void* u, const void* lora_a, void* dx, int64_t lddx,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Bytes of split-K scratch that nf4b200_linear_fwd (backward == 0) or nf4b200_linear_bwd_dx
+ * (backward == 1) can use for a weight [n_rows, n_cols] and m rows on the current device; 0 when
+ * the shape has enough tiles to fill the GPU without splitting. The scratch starts with a
+ * fixed-size area of 32-bit arrival counters (`*counter_bytes_out` bytes, the same for every
+ * shape): those bytes must be zero before the first use; the kernels leave them zero, so one
+ * buffer serves any number of calls, of any shapes, without clearing. Calls that may overlap on the GPU (different streams) need separate
+ * buffers. The reference has no counterpart: it lets cuBLAS pick its own workspace
+ * (solution/nf4.py:92,99).
+ */
+int64_t nf4b200_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int backward,
+                                int64_t* counter_bytes_out);
 
 /*
  * Rank-16 projection used by both passes of the LoRA update (peft's lora_A / lora_B linears;

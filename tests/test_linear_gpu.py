@@ -119,3 +119,33 @@ def test_bad_arguments_raise(cuda_lib):
     packed2, state2 = synthetic_weight(64, 96, False, seed=4, device="cuda")  # K % 64 != 0
     with pytest.raises(cuda_lib.Nf4Error):
         nf4_linear(torch.randn(4, 96, device="cuda").half(), packed2, None, state2)
+
+
+def test_split_k_equals_single_pass_and_is_deterministic(cuda_lib, monkeypatch):
+    """Shapes with few output tiles split the K range over several CTAs through the fp32
+    scratch; without scratch one CTA walks the whole range. Same numbers either way (up to fp32
+    summation order), bit-identical from run to run, and the scratch needs no clearing between
+    calls."""
+    from hackaton_b200 import nf4 as nf4_mod
+
+    n, k, m = 1536, 8960, 300      # down_proj: 2 x 6 tiles, 140 k-blocks
+    packed, state = synthetic_weight(n, k, True, seed=8, device="cuda")
+    need = cuda_lib.lib().nf4b200_workspace_bytes(n, k, m, 0, None)
+    assert need > 0
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(m, k, generator=g, device="cuda").half()
+    bias = torch.randn(n, generator=g, device="cuda").half()
+    dy = torch.randn(m, n, generator=g, device="cuda").half()
+    y1 = nf4_mod.linear_forward(x, packed, bias, state)
+    y2 = nf4_mod.linear_forward(x, packed, bias, state)
+    d1 = nf4_mod.linear_backward_dx(dy, packed, state)
+    d2 = nf4_mod.linear_backward_dx(dy, packed, state)
+    assert torch.equal(y1, y2) and torch.equal(d1, d2)
+    monkeypatch.setattr(nf4_mod, "_workspace", lambda *a, **kw: (None, 0))
+    y0 = nf4_mod.linear_forward(x, packed, bias, state)
+    d0 = nf4_mod.linear_backward_dx(dy, packed, state)
+    assert float((y1.float() - y0.float()).abs().max() / y0.float().abs().max()) < 2e-3
+    assert float((d1.float() - d0.float()).abs().max() / d0.float().abs().max()) < 2e-3
+    w = oracle_weight(packed, state)
+    assert rel(y1, nf4_oracle.linear_fwd(x.cpu(), w, bias.cpu())) <= TOL
+    cuda_lib.device_status()
