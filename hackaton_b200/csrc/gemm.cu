@@ -5,29 +5,32 @@
 // replacing the reference's "decode the whole weight to fp16 in HBM, then cuBLAS"
 // (solution/nf4.py:87-92 forward, 94-99 backward). W never exists in HBM as fp16 here.
 //
-// One CTA computes a (128*NACC) x 256 output tile over a range of 64-deep k-blocks. Roles:
+// Persistent kernel: one CTA per SM walks a list of work units; a unit is one (128*NACC) x 256
+// output tile over a slice of the 64-deep k-blocks. Roles:
 //   warps 0..15  producers: read the packed-code tile from shared memory, fetch the block scales
 //                (u8 absmax -> second-level table -> * absmax2 + offset, prefetched one k-block
 //                ahead), expand codes through a register-resident fp16 table (byte permutes, no
 //                shared-memory lookups) and write the fp16 weight tile in the 128-byte-swizzled
-//                layout the MMA descriptor expects. After the main loop the same warps run the
-//                epilogue (tcgen05.ld -> fp16 -> global, or fp32 partials for split-K).
+//                layout the MMA descriptor expects. At the end of a unit the same warps drain the
+//                accumulators (tcgen05.ld), transpose them through shared memory and store
+//                whole 128-byte lines.
 //   warp 16      TMA: activation tiles (128-byte swizzle) and the code tile of each k-block into
-//                a STAGES-deep ring of shared memory.
+//                a STAGES-deep ring of shared memory; it runs ahead into the next unit while the
+//                producers are still in the epilogue of the current one.
 //   warp 17      allocates TMEM; one lane issues tcgen05.mma (M=128, N=256, K=16) and commits
-//                each k-block to the ring's "empty" barrier.
+//                each k-block to the ring's "empty" barrier and each unit to "accumulators full".
 // The weight tile is always stored as rows of n_w holding 64 consecutive k_w (128 bytes, chunk
 // index XOR row%8). Forward reads it as a K-major B operand; backward as an MN-major one.
 // With NACC = 2 both accumulators (two 128-row halves of the token tile) reuse each decoded
 // weight tile, halving the decode work per flop.
 //
-// Split-K: when a problem has fewer tiles than SMs, gridDim.z CTAs share one tile, each over a
-// slice of the k-blocks. They park fp32 partial tiles in a caller-provided workspace; the CTA
+// Split-K: when a problem has fewer tiles than SMs, several units share one tile, each over a
+// slice of the k-blocks. They park fp32 partial tiles in a caller-provided workspace; the unit
 // that arrives last (a per-tile counter) adds the slices in a fixed order, applies the bias and
 // writes fp16. The counters return to zero, so the workspace is reusable without clearing.
 //
 // The rank-16 LoRA term rides along as one extra K=16 MMA step after the main loop ("K
-// extension", done by split 0): its two small operands are copied by the producers into the
+// extension", done by slice 0): its two small operands are copied by the producers into the
 // ring slot in the unswizzled core-matrix layout.
 //
 // Every barrier wait is bounded (ptx.cuh); on a timeout the CTA records a status code, lets its
@@ -36,6 +39,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "decode.cuh"
@@ -63,12 +67,13 @@ struct GemmParams {
     const __half* ext_b;
     __half* out;
     int* status;
-    float* ws_partials;      // split-K: [tile][split][128*NACC][BN] fp32
+    float* ws_partials;      // split-K: [tile][slice][128*NACC][BN] fp32
     unsigned int* ws_count;  // split-K: one arrival counter per tile, zero between launches
     long long ld_out;
     int m, n_w, k_w;
     int nested, nested_shift, nested_blocksize;
-    int kb_per_split;
+    int m_tiles, n_tiles, splits, kb_per_split;
+    int debug;               // bit 0: producers skip the decode (timing experiments only)
 };
 
 template <int NACC, int STAGES>
@@ -99,8 +104,13 @@ __device__ __forceinline__ void named_bar_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
-// Adds the bias (if any), rounds eight fp32 values to fp16 and stores them at dst (columns
-// col .. col+7 of a row that is n_out wide): one 16-byte store when allowed, else element-wise.
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Rounds eight fp32 values (+ bias) to fp16 and stores them at dst (columns col .. col+7 of a row
+// that is n_out wide): one 16-byte store when allowed, else element-wise.
 __device__ __forceinline__ void store8(__half* dst, float (&v)[8], int col, int n_out, bool vec_ok,
                                        const __half* bias) {
     if (bias != nullptr) {
@@ -110,11 +120,8 @@ __device__ __forceinline__ void store8(__half* dst, float (&v)[8], int col, int 
     }
     if (vec_ok && col + 8 <= n_out) {
         uint4 o;
-        __half2 h;
-        h = __floats2half2_rn(v[0], v[1]); o.x = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2half2_rn(v[2], v[3]); o.y = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2half2_rn(v[4], v[5]); o.z = *reinterpret_cast<uint32_t*>(&h);
-        h = __floats2half2_rn(v[6], v[7]); o.w = *reinterpret_cast<uint32_t*>(&h);
+        o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]);
+        o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
         *reinterpret_cast<uint4*>(dst) = o;
     } else {
 #pragma unroll
@@ -123,14 +130,53 @@ __device__ __forceinline__ void store8(__half* dst, float (&v)[8], int col, int 
     }
 }
 
+// Optional phase timestamps for tuning (NF4B200_DEBUG bit 1): producer thread 0 of each CTA records
+// %globaltimer at fixed points of its first TRACE_UNITS units.
+constexpr int TRACE_CTAS = 160, TRACE_UNITS = 4, TRACE_STAMPS = 8;
+__device__ unsigned long long g_trace[TRACE_CTAS * TRACE_UNITS * TRACE_STAMPS];
+
+#define NF4_TRACE(slot)                                                                       \
+    do {                                                                                      \
+        if ((p.debug & 2) && threadIdx.x == 0 && blockIdx.x < TRACE_CTAS &&                   \
+            unit_iter < TRACE_UNITS)                                                          \
+            g_trace[(blockIdx.x * TRACE_UNITS + unit_iter) * TRACE_STAMPS + (slot)] =         \
+                globaltimer_ns();                                                             \
+    } while (0)
+
+// One work unit of the persistent loop.
+struct Unit {
+    int m0, n0;         // tile origin (token row, output column)
+    int kb_begin, nkb;  // slice of k-blocks
+    int n_iter;         // nkb (+1 when this unit also runs the K extension)
+    unsigned tile_id, slice;
+};
+
+__device__ __forceinline__ Unit make_unit(int u, const GemmParams& p, int rows_per_tile,
+                                          int nkb_total) {
+    Unit w;
+    w.tile_id = (unsigned)(u / p.splits);
+    w.slice = (unsigned)(u % p.splits);
+    const int mt = (int)(w.tile_id % (unsigned)p.m_tiles), nt = (int)(w.tile_id / (unsigned)p.m_tiles);
+    w.m0 = mt * rows_per_tile;
+    w.n0 = nt * BN;
+    w.kb_begin = (int)w.slice * p.kb_per_split;
+    const int kb_end = min(w.kb_begin + p.kb_per_split, nkb_total);
+    w.nkb = kb_end - w.kb_begin;
+    w.n_iter = w.nkb + ((p.ext_a != nullptr && w.slice == 0) ? 1 : 0);
+    return w;
+}
+
 template <int NACC, bool TRANS_W, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                 const __grid_constant__ CUtensorMap tm_codes, const GemmParams p) {
     using L = SmemLayout<NACC, STAGES>;
     static_assert(BN * 2 == PRODUCER_THREADS, "one 16-byte code chunk per producer thread");
+    static_assert(STAGES >= 2, "the epilogue stages through the first two weight slots");
     constexpr uint32_t TMEM_COLS = NACC * BN;
     static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
+    constexpr int ROWS_PER_TILE = 128 * NACC;
+    constexpr size_t TILE_ELEMS = (size_t)ROWS_PER_TILE * BN;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -141,25 +187,20 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
     auto bar_full_tma = [&](int s) { return bar_base + 8u * s; };
     auto bar_full_w = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto bar_empty = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
-    const uint32_t bar_accum = bar_base + 8u * (3 * STAGES);
+    const uint32_t bar_tmem_full = bar_base + 8u * (3 * STAGES);
+    const uint32_t bar_tmem_empty = bar_base + 8u * (3 * STAGES + 1);
     volatile uint32_t* tmem_slot =
-        reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 1));
+        reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 2));
     volatile int* abort_flag =
-        reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 1) + 4);
+        reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 2) + 4);
     volatile int* last_flag =
-        reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 1) + 8);
+        reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 2) + 8);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * (128 * NACC);
-    const int n0 = blockIdx.y * BN;          // first output column of this tile
     const int kc = TRANS_W ? p.n_w : p.k_w;  // contraction length
     const int nkb_total = (kc + BK - 1) / BK;
-    const int kb_begin = blockIdx.z * p.kb_per_split;
-    const int kb_end = min(kb_begin + p.kb_per_split, nkb_total);
-    const int nkb = kb_end - kb_begin;       // k-blocks of this CTA (>= 1)
-    const bool has_ext = p.ext_a != nullptr && blockIdx.z == 0;
-    const int n_iter = nkb + (has_ext ? 1 : 0);
+    const int total_units = p.m_tiles * p.n_tiles * p.splits;
     const int blocks_per_row = p.k_w >> 6;
 
     if (threadIdx.x == 0) {
@@ -168,7 +209,8 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
             mbar_init(bar_full_w(s), PRODUCER_THREADS);
             mbar_init(bar_empty(s), 1);
         }
-        mbar_init(bar_accum, 1);
+        mbar_init(bar_tmem_full, 1);
+        mbar_init(bar_tmem_empty, PRODUCER_THREADS);
         *abort_flag = 0;
         *last_flag = 0;
         fence_barrier_init();
@@ -192,25 +234,29 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
     if (warp == TMA_WARP) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            for (int it = 0; it < n_iter; ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                const uint32_t sa = smem_base + (uint32_t)s * L::STAGE_BYTES;
-                if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag)) { fail = 1; break; }
-                if (it < nkb) {
-                    const int kb = kb_begin + it;
-                    mbar_arrive_expect_tx(bar_full_tma(s), L::A_BYTES + L::C_BYTES);
+            uint32_t g = 0;  // ring position, running across units
+            for (int u = blockIdx.x; u < total_units && !fail; u += gridDim.x) {
+                const Unit w = make_unit(u, p, ROWS_PER_TILE, nkb_total);
+                for (int it = 0; it < w.n_iter; ++it, ++g) {
+                    const int s = (int)(g % STAGES);
+                    const uint32_t ph = (g / STAGES) & 1u;
+                    const uint32_t sa = smem_base + (uint32_t)s * L::STAGE_BYTES;
+                    if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag)) { fail = 1; break; }
+                    if (it < w.nkb) {
+                        const int kb = w.kb_begin + it;
+                        mbar_arrive_expect_tx(bar_full_tma(s), L::A_BYTES + L::C_BYTES);
 #pragma unroll
-                    for (int a = 0; a < NACC; ++a)
-                        tma_load_2d(sa + a * (128 * BK * 2), &tm_act, kb * BK, m0 + a * 128,
-                                    bar_full_tma(s));
-                    const uint32_t sc = sa + L::A_BYTES + L::W_BYTES;
-                    if (TRANS_W)
-                        tma_load_2d(sc, &tm_codes, n0 / 2, kb * BK, bar_full_tma(s));
-                    else
-                        tma_load_2d(sc, &tm_codes, kb * (BK / 2), n0, bar_full_tma(s));
-                } else {
-                    mbar_arrive(bar_full_tma(s));  // extension step: operands come from producers
+                        for (int a = 0; a < NACC; ++a)
+                            tma_load_2d(sa + a * (128 * BK * 2), &tm_act, kb * BK, w.m0 + a * 128,
+                                        bar_full_tma(s));
+                        const uint32_t sc = sa + L::A_BYTES + L::W_BYTES;
+                        if (TRANS_W)
+                            tma_load_2d(sc, &tm_codes, w.n0 / 2, kb * BK, bar_full_tma(s));
+                        else
+                            tma_load_2d(sc, &tm_codes, kb * (BK / 2), w.n0, bar_full_tma(s));
+                    } else {
+                        mbar_arrive(bar_full_tma(s));  // extension step: producers bring operands
+                    }
                 }
             }
         }
@@ -218,47 +264,57 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_f16(BN, 0u, TRANS_W ? 1u : 0u);
-            for (int it = 0; it < n_iter; ++it) {
-                const int s = it % STAGES;
-                const uint32_t ph = (it / STAGES) & 1;
-                const uint32_t sa = smem_base + (uint32_t)s * L::STAGE_BYTES;
-                const uint32_t sw = sa + L::A_BYTES;
-                if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 2; break; }
-                if (!mbar_wait(bar_full_w(s), ph, abort_flag)) { fail = 3; break; }
+            uint32_t g = 0;
+            uint32_t unit_iter = 0;
+            for (int u = blockIdx.x; u < total_units && !fail; u += gridDim.x, ++unit_iter) {
+                const Unit w = make_unit(u, p, ROWS_PER_TILE, nkb_total);
+                // the accumulators of the previous unit must have been drained
+                if (!mbar_wait(bar_tmem_empty, (unit_iter & 1u) ^ 1u, abort_flag)) { fail = 6; break; }
                 tc_fence_after_sync();
-                if (it < nkb) {
-                    const uint64_t bdesc0 = TRANS_W ? make_smem_desc(sw, 64 * 128, 1024, LAYOUT_SW128)
-                                                    : make_smem_desc(sw, 16, 1024, LAYOUT_SW128);
+                for (int it = 0; it < w.n_iter; ++it, ++g) {
+                    const int s = (int)(g % STAGES);
+                    const uint32_t ph = (g / STAGES) & 1u;
+                    const uint32_t sa = smem_base + (uint32_t)s * L::STAGE_BYTES;
+                    const uint32_t sw = sa + L::A_BYTES;
+                    if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 2; break; }
+                    if (!mbar_wait(bar_full_w(s), ph, abort_flag)) { fail = 3; break; }
+                    tc_fence_after_sync();
+                    if (it < w.nkb) {
+                        const uint64_t bdesc0 = TRANS_W
+                            ? make_smem_desc(sw, 64 * 128, 1024, LAYOUT_SW128)
+                            : make_smem_desc(sw, 16, 1024, LAYOUT_SW128);
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k) {
-                        const uint64_t bdesc =
-                            bdesc0 + (uint64_t)(TRANS_W ? (16 * 128) >> 4 : 32 >> 4) * k;
+                        for (int k = 0; k < BK / 16; ++k) {
+                            const uint64_t bdesc =
+                                bdesc0 + (uint64_t)(TRANS_W ? (16 * 128) >> 4 : 32 >> 4) * k;
+#pragma unroll
+                            for (int a = 0; a < NACC; ++a) {
+                                const uint64_t adesc =
+                                    make_smem_desc(sa + a * (128 * BK * 2), 16, 1024, LAYOUT_SW128) +
+                                    (uint64_t)(32 >> 4) * k;
+                                umma_f16(tmem_base + a * BN, adesc, bdesc, idesc,
+                                         (it > 0 || k > 0) ? 1u : 0u);
+                            }
+                        }
+                    } else {
+                        // K extension: unswizzled core-matrix operands (layout type 0).
+                        // A: [row/8][k-half][row%8][16 B]  -> LBO 128, SBO 256 (K-major).
+                        // B forward:  same form over n_w rows (K-major).
+                        // B backward: [r/8][k_w/8][r%8][16 B] -> LBO BN*16, SBO 128 (MN-major).
+                        const uint64_t bdesc = TRANS_W
+                            ? make_smem_desc(sw, BN * 16, 128, LAYOUT_NONE)
+                            : make_smem_desc(sw, 128, 256, LAYOUT_NONE);
 #pragma unroll
                         for (int a = 0; a < NACC; ++a) {
                             const uint64_t adesc =
-                                make_smem_desc(sa + a * (128 * BK * 2), 16, 1024, LAYOUT_SW128) +
-                                (uint64_t)(32 >> 4) * k;
-                            umma_f16(tmem_base + a * BN, adesc, bdesc, idesc,
-                                     (it > 0 || k > 0) ? 1u : 0u);
+                                make_smem_desc(sa + a * (128 * BK * 2), 128, 256, LAYOUT_NONE);
+                            umma_f16(tmem_base + a * BN, adesc, bdesc, idesc, it > 0 ? 1u : 0u);
                         }
                     }
-                } else {
-                    // K extension: unswizzled core-matrix operands (layout type 0).
-                    // A: [row/8][k-half][row%8][16 B]  -> LBO 128, SBO 256 (K-major).
-                    // B forward:  same form over n_w rows (K-major).
-                    // B backward: [r/8][k_w/8][r%8][16 B] -> LBO BN*16, SBO 128 (MN-major).
-                    const uint64_t bdesc = TRANS_W ? make_smem_desc(sw, BN * 16, 128, LAYOUT_NONE)
-                                                   : make_smem_desc(sw, 128, 256, LAYOUT_NONE);
-#pragma unroll
-                    for (int a = 0; a < NACC; ++a) {
-                        const uint64_t adesc =
-                            make_smem_desc(sa + a * (128 * BK * 2), 128, 256, LAYOUT_NONE);
-                        umma_f16(tmem_base + a * BN, adesc, bdesc, idesc, it > 0 ? 1u : 0u);
-                    }
+                    umma_commit(bar_empty(s));
                 }
-                umma_commit(bar_empty(s));
+                if (!fail) umma_commit(bar_tmem_full);
             }
-            if (!fail) umma_commit(bar_accum);
         }
     } else {
         // ------------------------------------------------------------------ decode producers
@@ -271,6 +327,8 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
             lut = make_reg_lut(bits);
         }
         const float offset = p.nested ? *p.offset : 0.f;
+        const uint8_t* absmax_u8 = static_cast<const uint8_t*>(p.absmax);
+        const float* absmax_f32 = static_cast<const float*>(p.absmax);
 
         // Chunk geometry. Forward: the code tile is [256 rows][32 B]; chunk c covers row c/2,
         // half c%2 of the 64-wide k-block. Backward: the tile is [64 rows][128 B], 128-byte
@@ -300,55 +358,64 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                 dst_off[i] = smem_base + L::A_BYTES + dst + (uint32_t)(((chunk0 + i) ^ (row & 7)) << 4);
             src_off += smem_base + L::A_BYTES + L::W_BYTES;
         }
+        // epilogue geometry: TMEM lane quadrant, column share, private 4 KB staging area inside
+        // the weight slots of ring stages 0 and 1 (free while the accumulators are drained)
+        const int q = warp & 3;
+        const int grp = warp >> 2;
+        constexpr int CHUNKS_PER_GRP = NACC * (BN / 32) / 4;
+        const uint32_t staging = smem_base + (uint32_t)(warp >> 3) * L::STAGE_BYTES + L::A_BYTES +
+                                 (uint32_t)(warp & 7) * 4096u;
+        const int n_out = TRANS_W ? p.k_w : p.n_w;
+        const bool split = p.splits > 1;
+        const bool vec_ok = (p.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
 
-        // First-level scale index of this thread's chunk in k-block kb (32-bit: n_blocks < 2^31).
-        //   forward : block (n0 + row) * bpr + kb            valid while n0 + row < N_w
-        //   backward: block (kb*64 + row) * bpr + kw / 64    valid while kb*64 + row < N_w, kw < K_w
-        uint32_t blk;
-        uint32_t blk_step;
-        bool col_ok;
-        if (!TRANS_W) {
-            blk = (uint32_t)(n0 + row) * (uint32_t)blocks_per_row + (uint32_t)kb_begin;
-            blk_step = 1u;
-            col_ok = n0 + row < p.n_w;
-        } else {
-            const int kw = n0 + col * 32;
-            blk = (uint32_t)(kb_begin * BK + row) * (uint32_t)blocks_per_row + (uint32_t)(kw >> 6);
-            blk_step = (uint32_t)BK * (uint32_t)blocks_per_row;
-            col_ok = kw < p.k_w;
-        }
-        const uint8_t* absmax_u8 = static_cast<const uint8_t*>(p.absmax);
-        const float* absmax_f32 = static_cast<const float*>(p.absmax);
+        uint32_t g = 0;
+        uint32_t unit_iter = 0;
+        for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++unit_iter) {
+            const Unit w = make_unit(u, p, ROWS_PER_TILE, nkb_total);
+            NF4_TRACE(0);
 
-        uint32_t raw_q = 0;   // u8 code (nested) or fp32 bits (flat) of the current k-block
-        float raw_a2 = 0.f;   // second-level scale
-        bool raw_ok = false;
-        auto fetch_scale = [&](int it) {
-            bool ok = col_ok;
-            if (TRANS_W) ok = ok && ((kb_begin + it) * BK + row < p.n_w);
-            raw_ok = ok;
-            if (ok) {
-                if (p.nested) {
-                    raw_q = __ldg(absmax_u8 + blk);
-                    const uint32_t b2 = p.nested_shift >= 0 ? (blk >> p.nested_shift)
-                                                            : (blk / (uint32_t)p.nested_blocksize);
-                    raw_a2 = __ldg(p.absmax2 + b2);
-                } else {
-                    raw_q = __float_as_uint(__ldg(absmax_f32 + blk));
-                }
+            // First-level scale index of this thread's chunk (32-bit: n_blocks < 2^31).
+            //   forward : block (n0 + row) * bpr + kb          valid while n0 + row < N_w
+            //   backward: block (kb*64 + row) * bpr + kw / 64  valid while kb*64 + row < N_w, kw < K_w
+            uint32_t blk, blk_step;
+            bool col_ok;
+            if (!TRANS_W) {
+                blk = (uint32_t)(w.n0 + row) * (uint32_t)blocks_per_row + (uint32_t)w.kb_begin;
+                blk_step = 1u;
+                col_ok = w.n0 + row < p.n_w;
+            } else {
+                const int kw = w.n0 + col * 32;
+                blk = (uint32_t)(w.kb_begin * BK + row) * (uint32_t)blocks_per_row + (uint32_t)(kw >> 6);
+                blk_step = (uint32_t)BK * (uint32_t)blocks_per_row;
+                col_ok = kw < p.k_w;
             }
-            blk += blk_step;
-        };
-        if (nkb > 0) fetch_scale(0);
+            uint32_t raw_q = 0;   // u8 code (nested) or fp32 bits (flat) of the coming k-block
+            float raw_a2 = 0.f;   // its second-level scale
+            bool raw_ok = false;
+            auto fetch_scale = [&](int it) {
+                bool ok = col_ok;
+                if (TRANS_W) ok = ok && ((w.kb_begin + it) * BK + row < p.n_w);
+                raw_ok = ok;
+                if (ok) {
+                    if (p.nested) {
+                        raw_q = __ldg(absmax_u8 + blk);
+                        const uint32_t b2 = p.nested_shift >= 0
+                            ? (blk >> p.nested_shift) : (blk / (uint32_t)p.nested_blocksize);
+                        raw_a2 = __ldg(p.absmax2 + b2);
+                    } else {
+                        raw_q = __float_as_uint(__ldg(absmax_f32 + blk));
+                    }
+                }
+                blk += blk_step;
+            };
+            if (!fail) fetch_scale(0);
 
-        uint32_t ph = 0;
-        for (int it0 = 0; it0 < n_iter && !fail; it0 += STAGES, ph ^= 1u) {
-#pragma unroll
-            for (int s = 0; s < STAGES; ++s) {
-                const int it = it0 + s;
-                if (it >= n_iter) break;
+            for (int it = 0; it < w.n_iter && !fail; ++it, ++g) {
+                const int s = (int)(g % STAGES);
+                const uint32_t ph = (g / STAGES) & 1u;
                 const uint32_t stage_off = (uint32_t)s * L::STAGE_BYTES;
-                if (it < nkb) {
+                if (it < w.nkb) {
                     float sc;
                     if (!raw_ok)
                         sc = 0.f;  // rows / columns outside the weight contribute zeros
@@ -357,13 +424,30 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                     else
                         sc = __uint_as_float(raw_q);
                     const __half2 scale2 = __float2half2_rn(sc);
-                    if (it + 1 < nkb) fetch_scale(it + 1);
+                    if (it + 1 < w.nkb) fetch_scale(it + 1);
                     if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 4; break; }
-                    const uint4 cw = lds128(src_off + stage_off);
-                    sts128(dst_off[0] + stage_off, decode_word_reg(cw.x, lut, scale2));
-                    sts128(dst_off[1] + stage_off, decode_word_reg(cw.y, lut, scale2));
-                    sts128(dst_off[2] + stage_off, decode_word_reg(cw.z, lut, scale2));
-                    sts128(dst_off[3] + stage_off, decode_word_reg(cw.w, lut, scale2));
+                    if (!(p.debug & 1)) {
+                        const uint4 cw = lds128(src_off + stage_off);
+                        if (p.debug & 4) {         // experiment: shared-memory traffic without the ALU work
+                            sts128(dst_off[0] + stage_off, cw);
+                            sts128(dst_off[1] + stage_off, cw);
+                            sts128(dst_off[2] + stage_off, cw);
+                            sts128(dst_off[3] + stage_off, cw);
+                        } else if (p.debug & 8) {  // experiment: ALU work with a single store
+                            const uint4 a = decode_word_reg(cw.x, lut, scale2);
+                            const uint4 b = decode_word_reg(cw.y, lut, scale2);
+                            const uint4 c = decode_word_reg(cw.z, lut, scale2);
+                            const uint4 d = decode_word_reg(cw.w, lut, scale2);
+                            sts128(dst_off[0] + stage_off,
+                                   make_uint4(a.x ^ b.x ^ c.x ^ d.x, a.y ^ b.y ^ c.y ^ d.y,
+                                              a.z ^ b.z ^ c.z ^ d.z, a.w ^ b.w ^ c.w ^ d.w));
+                        } else {
+                            sts128(dst_off[0] + stage_off, decode_word_reg(cw.x, lut, scale2));
+                            sts128(dst_off[1] + stage_off, decode_word_reg(cw.y, lut, scale2));
+                            sts128(dst_off[2] + stage_off, decode_word_reg(cw.z, lut, scale2));
+                            sts128(dst_off[3] + stage_off, decode_word_reg(cw.w, lut, scale2));
+                        }
+                    }
                 } else {
                     // K extension operands, unswizzled core-matrix layout (see the MMA branch).
                     if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 4; break; }
@@ -371,9 +455,9 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                     const uint32_t wbase = abase + L::A_BYTES;
                     const uint4 zero = make_uint4(0, 0, 0, 0);
                     // ext_a rows m0 .. m0 + 128*NACC: two 16-byte halves per row
-                    for (int c = pt; c < 128 * NACC * 2; c += PRODUCER_THREADS) {
+                    for (int c = pt; c < ROWS_PER_TILE * 2; c += PRODUCER_THREADS) {
                         const int r_all = c >> 1, half = c & 1;
-                        const long long gm = (long long)m0 + r_all;
+                        const long long gm = (long long)w.m0 + r_all;
                         uint4 v = zero;
                         if (gm < p.m)
                             v = __ldg(reinterpret_cast<const uint4*>(p.ext_a + gm * 16) + half);
@@ -384,130 +468,208 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                     if (!TRANS_W) {
                         for (int c = pt; c < BN * 2; c += PRODUCER_THREADS) {
                             const int r = c >> 1, half = c & 1;
-                            const long long gn = (long long)n0 + r;
+                            const long long gn = (long long)w.n0 + r;
                             uint4 v = zero;
                             if (gn < p.n_w)
                                 v = __ldg(reinterpret_cast<const uint4*>(p.ext_b + gn * 16) + half);
                             sts128(wbase + (r >> 3) * 256 + half * 128 + (r & 7) * 16, v);
                         }
                     } else {
-                        // lora_a [16, K_w]: chunk (r, g) = 8 consecutive k_w of rank row r
+                        // lora_a [16, K_w]: chunk (r, gq) = 8 consecutive k_w of rank row r
                         for (int c = pt; c < 16 * (BN / 8); c += PRODUCER_THREADS) {
-                            const int r = c / (BN / 8), g = c % (BN / 8);
-                            const long long kw = (long long)n0 + g * 8;
+                            const int r = c / (BN / 8), gq = c % (BN / 8);
+                            const long long kw = (long long)w.n0 + gq * 8;
                             uint4 v = zero;
                             if (kw < p.k_w)
                                 v = __ldg(reinterpret_cast<const uint4*>(
                                     p.ext_b + (long long)r * p.k_w + kw));
-                            sts128(wbase + (r >> 3) * (BN * 16) + g * 128 + (r & 7) * 16, v);
+                            sts128(wbase + (r >> 3) * (BN * 16) + gq * 128 + (r & 7) * 16, v);
                         }
                     }
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(bar_full_w(s));
             }
-        }
 
-        // ------------------------------------------------------------------ epilogue
-        if (!fail) {
-            if (!mbar_wait(bar_accum, 0u, abort_flag)) fail = 5;
-        }
-        const int n_out = TRANS_W ? p.k_w : p.n_w;
-        const bool split = gridDim.z > 1;
-        const bool vec_ok = (p.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
-        const unsigned tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-        constexpr size_t TILE_ELEMS = (size_t)128 * NACC * BN;
-        if (!fail) {
-            tc_fence_after_sync();
-            const int q = warp & 3;     // TMEM lane quadrant this warp may read
-            const int grp = warp >> 2;  // 0..3: which share of the column chunks
-            constexpr int CHUNKS_PER_GRP = NACC * (BN / 32) / 4;
-            float* part = split ? p.ws_partials + ((size_t)tile_id * gridDim.z + blockIdx.z) * TILE_ELEMS
-                                : nullptr;
+            // -------------------------------------------------------------- epilogue of the unit
+            NF4_TRACE(1);
+            if (!fail) {
+                if (!mbar_wait(bar_tmem_full, unit_iter & 1u, abort_flag)) fail = 5;
+            }
+            NF4_TRACE(2);
+            if (!fail) {
+                tc_fence_after_sync();
+                const int lrow = lane;                      // row of this lane inside its quadrant
+                const int rd_row = lane >> 3, rd_chunk = lane & 7;
+                if (!split) {
+                    // two 32-column chunks -> one [32 rows x 64 cols] fp16 box, written out as
+                    // whole 128-byte lines
 #pragma unroll 1
-            for (int t = grp * CHUNKS_PER_GRP; t < (grp + 1) * CHUNKS_PER_GRP; ++t) {
-                const int acc = t / (BN / 32), ch = t % (BN / 32);
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + ch * 32, r);
-                tmem_ld_wait();
-                const int trow = acc * 128 + q * 32 + lane;  // row within the tile
-                const long long grow = (long long)m0 + trow;
-                const int col0 = n0 + ch * 32;
-                if (split) {
-                    float4* dst = reinterpret_cast<float4*>(part + (size_t)trow * BN + ch * 32);
+                    for (int b = 0; b < CHUNKS_PER_GRP / 2; ++b) {
+                        const int t0 = grp * CHUNKS_PER_GRP + 2 * b;
+                        const int acc = t0 / (BN / 32), ch0 = t0 % (BN / 32);
 #pragma unroll
-                    for (int g = 0; g < 8; ++g)
-                        __stcg(dst + g, make_float4(__uint_as_float(r[4 * g]),
-                                                    __uint_as_float(r[4 * g + 1]),
-                                                    __uint_as_float(r[4 * g + 2]),
-                                                    __uint_as_float(r[4 * g + 3])));
-                } else if (grow < p.m && col0 < n_out) {
-                    __half* dst = p.out + grow * p.ld_out + col0;
+                        for (int h = 0; h < 2; ++h) {
+                            uint32_t r[32];
+                            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN +
+                                              (ch0 + h) * 32, r);
+                            tmem_ld_wait();
+                            if (!TRANS_W && p.bias != nullptr) {
+                                const int cb = w.n0 + (ch0 + h) * 32;
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        float v[8];
+                                for (int e = 0; e < 32; ++e)
+                                    if (cb + e < n_out)
+                                        r[e] = __float_as_uint(__uint_as_float(r[e]) +
+                                                               __half2float(p.bias[cb + e]));
+                            }
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[g * 8 + e]);
-                        store8(dst + g * 8, v, col0 + g * 8, n_out, vec_ok,
-                               TRANS_W ? nullptr : p.bias);
-                    }
-                }
-            }
-        }
-        if (split) {
-            // Last-arriver reduction. Every thread publishes its partials, the 512 epilogue
-            // threads meet (whether or not a wait timed out, so the barrier always fills), one of
-            // them takes a ticket; the CTA holding the last ticket sums the slices in order.
-            __threadfence();
-            named_bar_sync(1, PRODUCER_THREADS);
-            if (threadIdx.x == 0) {
-                int last = 0;
-                if (!*abort_flag) {
-                    const unsigned ticket = atomicAdd(p.ws_count + tile_id, 1u);
-                    last = (ticket == gridDim.z - 1) ? 1 : 0;
-                }
-                *last_flag = last;
-            }
-            named_bar_sync(1, PRODUCER_THREADS);
-            if (*last_flag) {
-                __threadfence();
-                const float* base = p.ws_partials + (size_t)tile_id * gridDim.z * TILE_ELEMS;
-                constexpr int UNITS = 128 * NACC * (BN / 8);  // 8-column groups in the tile
-                const unsigned nz = gridDim.z;
-                for (int u = threadIdx.x; u < UNITS; u += PRODUCER_THREADS) {
-                    const int trow = u / (BN / 8), c8 = u % (BN / 8);
-                    const long long grow = (long long)m0 + trow;
-                    const int col = n0 + c8 * 8;
-                    if (grow >= p.m || col >= n_out) continue;
-                    const float4* src0 =
-                        reinterpret_cast<const float4*>(base + (size_t)trow * BN + c8 * 8);
-                    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                    // slices are added in index order (deterministic); loads go out four slices
-                    // at a time so that their latencies overlap
-                    for (unsigned z0 = 0; z0 < nz; z0 += 4) {
-                        float4 a[4], b[4];
-#pragma unroll
-                        for (unsigned j = 0; j < 4; ++j) {
-                            if (z0 + j < nz) {
-                                const float4* src = src0 + (size_t)(z0 + j) * (TILE_ELEMS / 4);
-                                a[j] = __ldcg(src);
-                                b[j] = __ldcg(src + 1);
-                            } else {
-                                a[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                                b[j] = a[j];
+                            for (int i = 0; i < 4; ++i) {
+                                uint4 o;
+                                o.x = pack_half2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+                                o.y = pack_half2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                                o.z = pack_half2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                                o.w = pack_half2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                                sts128(staging + lrow * 128 + (((h * 4 + i) ^ (lrow & 7)) << 4), o);
                             }
                         }
+                        if (b == CHUNKS_PER_GRP / 2 - 1) {
+                            // every accumulator value of this thread is in registers / staging
+                            tc_fence_before_sync();
+                            mbar_arrive(bar_tmem_empty);
+                        }
+                        __syncwarp();
 #pragma unroll
-                        for (unsigned j = 0; j < 4; ++j) {
-                            v[0] += a[j].x; v[1] += a[j].y; v[2] += a[j].z; v[3] += a[j].w;
-                            v[4] += b[j].x; v[5] += b[j].y; v[6] += b[j].z; v[7] += b[j].w;
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = i * 4 + rd_row;
+                            const uint4 v = lds128(staging + rr * 128 + ((rd_chunk ^ (rr & 7)) << 4));
+                            const long long grow = (long long)w.m0 + acc * 128 + q * 32 + rr;
+                            const int colg = w.n0 + ch0 * 32 + rd_chunk * 8;
+                            if (grow < p.m && colg < n_out) {
+                                __half* dst = p.out + grow * p.ld_out + colg;
+                                if (vec_ok && colg + 8 <= n_out) {
+                                    *reinterpret_cast<uint4*>(dst) = v;
+                                } else {
+                                    const __half* hv = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e)
+                                        if (colg + e < n_out) dst[e] = hv[e];
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    }
+                } else {
+                    // fp32 partial tile of this slice: one [32 rows x 32 cols] box per chunk
+                    float* part = p.ws_partials + ((size_t)w.tile_id * p.splits + w.slice) * TILE_ELEMS;
+#pragma unroll 1
+                    for (int t = grp * CHUNKS_PER_GRP; t < (grp + 1) * CHUNKS_PER_GRP; ++t) {
+                        const int acc = t / (BN / 32), ch = t % (BN / 32);
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + ch * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            sts128(staging + lrow * 128 + ((i ^ (lrow & 7)) << 4),
+                                   make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]));
+                        if (t == (grp + 1) * CHUNKS_PER_GRP - 1) {
+                            tc_fence_before_sync();
+                            mbar_arrive(bar_tmem_empty);
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = i * 4 + rd_row;
+                            const uint4 v = lds128(staging + rr * 128 + ((rd_chunk ^ (rr & 7)) << 4));
+                            const int trow = acc * 128 + q * 32 + rr;
+                            __stcg(reinterpret_cast<uint4*>(part + (size_t)trow * BN + ch * 32 +
+                                                            rd_chunk * 4), v);
+                        }
+                        __syncwarp();
+                    }
+                }
+            }
+            NF4_TRACE(3);
+            if (split) {
+                // Last-arriver reduction. Every thread publishes its partials, the 512 epilogue
+                // threads meet (whether or not a wait timed out, so the barrier always fills), one
+                // of them takes a ticket; the unit holding the last ticket sums the slices in order.
+                __threadfence();
+                named_bar_sync(1, PRODUCER_THREADS);
+                if (threadIdx.x == 0) {
+                    int last = 0;
+                    if (!*abort_flag) {
+                        const unsigned ticket = atomicAdd(p.ws_count + w.tile_id, 1u);
+                        last = (ticket == (unsigned)p.splits - 1u) ? 1 : 0;
+                    }
+                    *last_flag = last;
+                }
+                named_bar_sync(1, PRODUCER_THREADS);
+                NF4_TRACE(4);
+                if (*last_flag) {
+                    __threadfence();
+                    const float* base = p.ws_partials + (size_t)w.tile_id * p.splits * TILE_ELEMS;
+                    constexpr int UNITS = ROWS_PER_TILE * (BN / 8);  // 8-column groups in the tile
+                    const unsigned nz = (unsigned)p.splits;
+                    // Two 8-column groups per thread and up to four slices are in flight at a
+                    // time (16 independent 16-byte loads), so the L2 latency is paid once per
+                    // round, not once per load; slices are added in index order (deterministic).
+                    static_assert(UNITS % (2 * PRODUCER_THREADS) == 0, "two groups per thread");
+                    for (int uu = threadIdx.x; uu < UNITS; uu += 2 * PRODUCER_THREADS) {
+                        float v[2][8];
+                        const float4* src0[2];
+#pragma unroll
+                        for (int hgrp = 0; hgrp < 2; ++hgrp) {
+                            const int ug = uu + hgrp * PRODUCER_THREADS;
+                            src0[hgrp] = reinterpret_cast<const float4*>(
+                                base + (size_t)(ug / (BN / 8)) * BN + (ug % (BN / 8)) * 8);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[hgrp][e] = 0.f;
+                        }
+                        for (unsigned z0 = 0; z0 < nz; z0 += 4) {
+                            float4 a[2][4], bq[2][4];
+#pragma unroll
+                            for (int hgrp = 0; hgrp < 2; ++hgrp)
+#pragma unroll
+                                for (unsigned j = 0; j < 4; ++j) {
+                                    if (z0 + j < nz) {
+                                        const float4* src =
+                                            src0[hgrp] + (size_t)(z0 + j) * (TILE_ELEMS / 4);
+                                        a[hgrp][j] = __ldcg(src);
+                                        bq[hgrp][j] = __ldcg(src + 1);
+                                    } else {
+                                        a[hgrp][j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                        bq[hgrp][j] = a[hgrp][j];
+                                    }
+                                }
+#pragma unroll
+                            for (int hgrp = 0; hgrp < 2; ++hgrp)
+#pragma unroll
+                                for (unsigned j = 0; j < 4; ++j) {
+                                    v[hgrp][0] += a[hgrp][j].x; v[hgrp][1] += a[hgrp][j].y;
+                                    v[hgrp][2] += a[hgrp][j].z; v[hgrp][3] += a[hgrp][j].w;
+                                    v[hgrp][4] += bq[hgrp][j].x; v[hgrp][5] += bq[hgrp][j].y;
+                                    v[hgrp][6] += bq[hgrp][j].z; v[hgrp][7] += bq[hgrp][j].w;
+                                }
+                        }
+#pragma unroll
+                        for (int hgrp = 0; hgrp < 2; ++hgrp) {
+                            const int ug = uu + hgrp * PRODUCER_THREADS;
+                            const int trow = ug / (BN / 8), c8 = ug % (BN / 8);
+                            const long long grow = (long long)w.m0 + trow;
+                            const int colg = w.n0 + c8 * 8;
+                            if (grow < p.m && colg < n_out)
+                                store8(p.out + grow * p.ld_out + colg, v[hgrp], colg, n_out, vec_ok,
+                                       TRANS_W ? nullptr : p.bias);
                         }
                     }
-                    store8(p.out + grow * p.ld_out + col, v, col, n_out, vec_ok,
-                           TRANS_W ? nullptr : p.bias);
+                    if (threadIdx.x == 0) p.ws_count[w.tile_id] = 0u;  // ready for the next launch
                 }
-                if (threadIdx.x == 0) p.ws_count[tile_id] = 0u;  // ready for the next launch
             }
+            NF4_TRACE(5);
+            // the staging areas live in weight slots: nobody may decode the next unit into them
+            // before every warp has read its staging back
+            named_bar_sync(1, PRODUCER_THREADS);
+            NF4_TRACE(6);
         }
     }
 
@@ -591,6 +753,15 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
     return pl;
 }
 
+static int debug_flags() {
+    static int flags = -1;
+    if (flags < 0) {
+        const char* e = std::getenv("NF4B200_DEBUG");
+        flags = e ? std::atoi(e) : 0;
+    }
+    return flags;
+}
+
 template <int NACC, bool TRANS_W, int STAGES>
 static cudaError_t launch_cfg(const GemmArgs& a, const GemmPlan& pl, cudaStream_t stream,
                               const char** why) {
@@ -627,20 +798,24 @@ static cudaError_t launch_cfg(const GemmArgs& a, const GemmPlan& pl, cudaStream_
         p.nested_shift = s;
     }
     if (p.status == nullptr) { *why = "device status word"; return cudaErrorInvalidValue; }
-    int splits = pl.splits;
+    p.m_tiles = pl.m_tiles;
+    p.n_tiles = pl.n_tiles;
+    p.splits = pl.splits;
     p.kb_per_split = pl.kb_per_split;
     p.ws_count = nullptr;
     p.ws_partials = nullptr;
-    if (splits > 1) {
+    p.debug = debug_flags();
+    if (p.splits > 1) {
         if (a.workspace == nullptr || a.workspace_bytes < pl.counter_bytes + pl.partial_bytes) {
-            splits = 1;  // no scratch given: one CTA per tile walks the whole K range
+            p.splits = 1;  // no scratch given: one unit per tile walks the whole K range
             p.kb_per_split = (int)((kc + BK - 1) / BK);
         } else {
             p.ws_count = static_cast<unsigned int*>(a.workspace);
             p.ws_partials = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + pl.counter_bytes);
         }
     }
-    dim3 grid((unsigned)pl.m_tiles, (unsigned)pl.n_tiles, (unsigned)splits);
+    const long long units = (long long)p.m_tiles * p.n_tiles * p.splits;
+    const unsigned grid = (unsigned)(units < a.sm_count ? units : a.sm_count);
     kernel<<<grid, GEMM_THREADS, L::DYNAMIC_BYTES, stream>>>(tm_act, tm_codes, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) *why = "kernel launch";
@@ -659,3 +834,13 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why
 }
 
 }  // namespace nf4
+
+// Tuning aid, not part of the public ABI: copies the phase timestamps to the host.
+extern "C" int nf4dbg_read_trace(unsigned long long* dst, int max_entries) {
+    const int n = nf4::TRACE_CTAS * nf4::TRACE_UNITS * nf4::TRACE_STAMPS;
+    if (max_entries < n) return -1;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+    if (cudaMemcpyFromSymbol(dst, nf4::g_trace, sizeof(unsigned long long) * n) != cudaSuccess)
+        return -3;
+    return n;
+}

@@ -171,6 +171,106 @@ __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---------------------------------------------------------------------------------- CTA pairs
+// Helpers for kernels launched as clusters of two CTAs that drive one tcgen05.mma.cta_group::2.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// Address, in the cluster's shared window, of `local_addr` inside CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t local_addr, uint32_t rank) {
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+    return a;
+}
+
+// Arrive (release at cluster scope) on a barrier given by its cluster-window address.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done;
+}
+
+// Bounded wait that acquires at cluster scope (for barriers the peer CTA arrives on).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    unsigned long long t0 = 0;
+    uint32_t polls = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if ((++polls & 31u) == 0u) {
+            if (*abort_flag) return false;
+            unsigned long long now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > WAIT_TIMEOUT_NS) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// All threads of both CTAs meet (used once after set-up and once before tear-down).
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst),
+                 "r"(ncols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+
+// D[tmem of both CTAs] (+)= A * B with M = 256 split over the pair; issued by one thread of the
+// leader CTA. Descriptors hold shared-memory offsets that are valid in both CTAs.
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                              uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives on the barrier at offset `bar` in every CTA of `cta_mask` once the pair's MMAs issued so
+// far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 "
+        "[%0], %1;" ::"r"(bar), "h"(cta_mask)
+        : "memory");
+}
+
 // ---------------------------------------------------------------------------------- descriptors
 // Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets (all
 // >> 4), descriptor version 1 (bits 46-47), layout type in bits 61-63.
@@ -184,13 +284,14 @@ __host__ __device__ constexpr uint64_t make_smem_desc(uint32_t smem_addr, uint32
            ((uint64_t)layout << 61);
 }
 
-// Instruction descriptor for kind::f16 with fp16 A/B, fp32 accumulate, M = 128.
+// Instruction descriptor for kind::f16 with fp16 A/B, fp32 accumulate; M = 128 for one CTA, 256 for
+// a CTA pair.
 // b_mn_major = 1 when the B tile is stored with its N dimension contiguous.
 __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t n, uint32_t a_mn_major,
-                                                      uint32_t b_mn_major) {
+                                                      uint32_t b_mn_major, uint32_t m = 128u) {
     return (1u << 4)                 // accumulator format: fp32
            | (0u << 7) | (0u << 10)  // A, B format: fp16
-           | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+           | (a_mn_major << 15) | (b_mn_major << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 }  // namespace nf4
