@@ -67,7 +67,7 @@ def lib() -> ctypes.CDLL:
     handle.nf4b200_linear_bwd_dx.argtypes = [POINTER(Weight), c_void_p, c_int64, c_int64, c_void_p,
                                              c_void_p, c_void_p, c_int64, c_void_p, c_size_t,
                                              c_void_p]
-    handle.nf4b200_workspace_bytes.argtypes = [c_int64, c_int64, c_int64, c_int, POINTER(c_int64)]
+    handle.nf4b200_workspace_bytes.argtypes = [c_int64, c_int64, c_int64, c_int]
     handle.nf4b200_lora_down.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
                                          c_int64, c_float, c_void_p, c_void_p]
     handle.nf4b200_lora_grad.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p,

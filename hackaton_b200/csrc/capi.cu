@@ -284,17 +284,14 @@ int nf4b200_linear_bwd_dx(const nf4b200_weight* w, const void* dy, int64_t m, in
     return NF4B200_OK;
 }
 
-int64_t nf4b200_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int backward,
-                                int64_t* counter_bytes_out) {
-    if (counter_bytes_out) *counter_bytes_out = 0;
+int64_t nf4b200_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int backward) {
     DeviceInfo* d = nullptr;
     int rc = require_sm100(&d);
     if (rc != NF4B200_OK) return rc;
     if (n_rows <= 0 || n_cols <= 0 || m <= 0)
         return fail(NF4B200_EINVAL, "workspace_bytes: bad shape");
     const nf4::GemmPlan pl = nf4::plan_gemm(m, n_rows, n_cols, backward != 0, d->sms);
-    if (counter_bytes_out) *counter_bytes_out = (int64_t)pl.counter_bytes;
-    return (int64_t)(pl.counter_bytes + pl.partial_bytes);
+    return (int64_t)pl.ws_bytes;
 }
 
 int nf4b200_lora_down(const void* in, int64_t m, int64_t c, int64_t ld_in, const void* p,

@@ -5,29 +5,38 @@
 // replacing the reference's "decode the whole weight to fp16 in HBM, then cuBLAS"
 // (solution/nf4.py:87-92 forward, 94-99 backward). W never exists in HBM as fp16 here.
 //
-// Persistent kernel: one CTA per SM walks a list of work units; a unit is one (128*NACC) x 256
-// output tile over a slice of the 64-deep k-blocks. Roles:
-//   warps 0..15  producers: read the packed-code tile from shared memory, fetch the block scales
-//                (u8 absmax -> second-level table -> * absmax2 + offset, prefetched one k-block
+// Persistent kernel. With CG = 2 the grid is a set of CTA pairs (clusters of two, one CTA per SM)
+// driving tcgen05.mma.cta_group::2: a work unit is a (256*NACC) x 256 output tile over a slice of
+// the 64-deep k-blocks; each CTA holds 128*NACC of its rows (activations in shared memory,
+// accumulators in its own TMEM) and decodes only half of the weight tile, which the tensor cores
+// of both SMs then read. With CG = 1 (token counts up to 128) a single CTA owns a 128 x 256 tile.
+// Roles inside a CTA (18 warps):
+//   warps 0..15  producers: read packed codes from shared memory, fetch the block scales (u8
+//                absmax -> second-level table -> * absmax2 + offset, prefetched one k-block
 //                ahead), expand codes through a register-resident fp16 table (byte permutes, no
 //                shared-memory lookups) and write the fp16 weight tile in the 128-byte-swizzled
 //                layout the MMA descriptor expects. At the end of a unit the same warps drain the
-//                accumulators (tcgen05.ld), transpose them through shared memory and store
-//                whole 128-byte lines.
-//   warp 16      TMA: activation tiles (128-byte swizzle) and the code tile of each k-block into
-//                a STAGES-deep ring of shared memory; it runs ahead into the next unit while the
+//                accumulators (tcgen05.ld), transpose them through shared memory and store whole
+//                128-byte lines.
+//   warp 16      TMA: this CTA's activation tiles (128-byte swizzle) and code tile of each
+//                k-block into a STAGES-deep ring; it runs ahead into the next unit while the
 //                producers are still in the epilogue of the current one.
-//   warp 17      allocates TMEM; one lane issues tcgen05.mma (M=128, N=256, K=16) and commits
-//                each k-block to the ring's "empty" barrier and each unit to "accumulators full".
+//   warp 17      allocates TMEM; in the leader CTA one lane issues the MMAs (N = 256, K = 16) and
+//                commits each k-block to the ring's "empty" barriers and each unit to
+//                "accumulators full" (multicast to both CTAs of a pair).
 // The weight tile is always stored as rows of n_w holding 64 consecutive k_w (128 bytes, chunk
 // index XOR row%8). Forward reads it as a K-major B operand; backward as an MN-major one.
-// With NACC = 2 both accumulators (two 128-row halves of the token tile) reuse each decoded
-// weight tile, halving the decode work per flop.
+// With NACC = 2 two accumulators (two token sub-tiles) reuse each decoded weight tile.
 //
-// Split-K: when a problem has fewer tiles than SMs, several units share one tile, each over a
-// slice of the k-blocks. They park fp32 partial tiles in a caller-provided workspace; the unit
-// that arrives last (a per-tile counter) adds the slices in a fixed order, applies the bias and
-// writes fp16. The counters return to zero, so the workspace is reusable without clearing.
+// Synchronisation across a pair: the producers of both CTAs arrive (one lane per warp, release at
+// cluster scope) on the leader's "weights ready" barrier; the peer's producers only get there
+// after their own TMA barrier fired, so that one barrier also vouches for the peer's activation
+// tile. Accumulator hand-back ("TMEM drained") works the same way.
+//
+// Split-K: when a problem has fewer tiles than the GPU has CTA slots, several units share a tile,
+// each over a slice of the k-blocks, and write fp32 partial sums as plain row-major planes
+// [slice][M][ldp] into caller-provided scratch; splitk_reduce_kernel then adds the planes in
+// slice order (deterministic), applies the bias and writes fp16.
 //
 // The rank-16 LoRA term rides along as one extra K=16 MMA step after the main loop ("K
 // extension", done by slice 0): its two small operands are copied by the producers into the
@@ -67,31 +76,40 @@ struct GemmParams {
     const __half* ext_b;
     __half* out;
     int* status;
-    float* ws_partials;      // split-K: [tile][slice][128*NACC][BN] fp32
-    unsigned int* ws_count;  // split-K: one arrival counter per tile, zero between launches
-    long long ld_out;
+    float* ws;               // split-K: fp32 planes [slice][m][ldp]
+    long long ld_out, ldp;
     int m, n_w, k_w;
     int nested, nested_shift, nested_blocksize;
     int m_tiles, n_tiles, splits, kb_per_split;
-    int debug;               // bit 0: producers skip the decode (timing experiments only)
+    int debug;               // bit 0: producers skip the decode, bit 1: phase trace (tuning only)
 };
 
-template <int NACC, int STAGES>
+template <int CG, int NACC, int STAGES>
 struct SmemLayout {
+    static constexpr int NB = BN / CG;                 // weight-tile columns decoded by one CTA
     static constexpr int A_BYTES = NACC * 128 * BK * 2;
-    static constexpr int W_BYTES = BN * BK * 2;
-    static constexpr int C_BYTES = BN * BK / 2;
+    static constexpr int W_BYTES = NB * BK * 2;
+    static constexpr int C_BYTES = NB * BK / 2;
     static constexpr int STAGE_BYTES = A_BYTES + W_BYTES + C_BYTES;
     static constexpr int TABLE2_OFF = STAGES * STAGE_BYTES;
     static constexpr int BAR_OFF = TABLE2_OFF + 1024;
     static constexpr int TOTAL = BAR_OFF + 256;
     static constexpr int DYNAMIC_BYTES = TOTAL + 1024;  // slack for 1024-byte alignment
+    static constexpr int WARPS_PER_W_SLOT = W_BYTES / 4096;  // 4 KB epilogue staging per warp
+    static_assert(STAGES * WARPS_PER_W_SLOT >= PRODUCER_WARPS, "staging needs more weight slots");
+    static_assert(DYNAMIC_BYTES <= 232448, "exceeds the 227 KB of shared memory per CTA");
 };
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
     return v;
 }
 
@@ -109,27 +127,6 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// Rounds eight fp32 values (+ bias) to fp16 and stores them at dst (columns col .. col+7 of a row
-// that is n_out wide): one 16-byte store when allowed, else element-wise.
-__device__ __forceinline__ void store8(__half* dst, float (&v)[8], int col, int n_out, bool vec_ok,
-                                       const __half* bias) {
-    if (bias != nullptr) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e)
-            if (col + e < n_out) v[e] += __half2float(bias[col + e]);
-    }
-    if (vec_ok && col + 8 <= n_out) {
-        uint4 o;
-        o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]);
-        o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
-        *reinterpret_cast<uint4*>(dst) = o;
-    } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e)
-            if (col + e < n_out) dst[e] = __float2half_rn(v[e]);
-    }
-}
-
 // Optional phase timestamps for tuning (NF4B200_DEBUG bit 1): producer thread 0 of each CTA records
 // %globaltimer at fixed points of its first TRACE_UNITS units.
 constexpr int TRACE_CTAS = 160, TRACE_UNITS = 4, TRACE_STAMPS = 8;
@@ -143,40 +140,50 @@ __device__ unsigned long long g_trace[TRACE_CTAS * TRACE_UNITS * TRACE_STAMPS];
                 globaltimer_ns();                                                             \
     } while (0)
 
+// Second tuning aid: per-k-block event times of the first pair's first unit.
+constexpr int TRACE2_EVENTS = 6, TRACE2_ITERS = 64;
+__device__ unsigned long long g_trace2[2 * TRACE2_EVENTS * TRACE2_ITERS];
+#define NF4_TRACE2(ev, it_)                                                                    \
+    do {                                                                                       \
+        if ((p.debug & 2) && blockIdx.x < 2 && unit_iter2 == 0 && (it_) < TRACE2_ITERS)         \
+            g_trace2[(blockIdx.x * TRACE2_EVENTS + (ev)) * TRACE2_ITERS + (it_)] = globaltimer_ns(); \
+    } while (0)
+
 // One work unit of the persistent loop.
 struct Unit {
     int m0, n0;         // tile origin (token row, output column)
     int kb_begin, nkb;  // slice of k-blocks
     int n_iter;         // nkb (+1 when this unit also runs the K extension)
-    unsigned tile_id, slice;
+    int slice;
 };
 
 __device__ __forceinline__ Unit make_unit(int u, const GemmParams& p, int rows_per_tile,
                                           int nkb_total) {
     Unit w;
-    w.tile_id = (unsigned)(u / p.splits);
-    w.slice = (unsigned)(u % p.splits);
-    const int mt = (int)(w.tile_id % (unsigned)p.m_tiles), nt = (int)(w.tile_id / (unsigned)p.m_tiles);
+    const int tile = u / p.splits;
+    w.slice = u % p.splits;
+    const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
     w.m0 = mt * rows_per_tile;
     w.n0 = nt * BN;
-    w.kb_begin = (int)w.slice * p.kb_per_split;
+    w.kb_begin = w.slice * p.kb_per_split;
     const int kb_end = min(w.kb_begin + p.kb_per_split, nkb_total);
     w.nkb = kb_end - w.kb_begin;
     w.n_iter = w.nkb + ((p.ext_a != nullptr && w.slice == 0) ? 1 : 0);
     return w;
 }
 
-template <int NACC, bool TRANS_W, int STAGES>
+template <int CG, int NACC, bool TRANS_W, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                 const __grid_constant__ CUtensorMap tm_codes, const GemmParams p) {
-    using L = SmemLayout<NACC, STAGES>;
-    static_assert(BN * 2 == PRODUCER_THREADS, "one 16-byte code chunk per producer thread");
-    static_assert(STAGES >= 2, "the epilogue stages through the first two weight slots");
+    using L = SmemLayout<CG, NACC, STAGES>;
+    constexpr int NB = L::NB;
+    constexpr int WORDS = 4 / CG;  // 32-bit code words (8 weights each) per producer thread
+    static_assert(NB * BK / 8 == PRODUCER_THREADS * WORDS, "producer work split");
     constexpr uint32_t TMEM_COLS = NACC * BN;
     static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
-    constexpr int ROWS_PER_TILE = 128 * NACC;
-    constexpr size_t TILE_ELEMS = (size_t)ROWS_PER_TILE * BN;
+    constexpr int ROWS_PER_TILE = 128 * CG * NACC;  // token rows of a unit (whole pair)
+    constexpr uint32_t ARRIVALS = CG * PRODUCER_WARPS;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -193,11 +200,12 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
         reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 2));
     volatile int* abort_flag =
         reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 2) + 4);
-    volatile int* last_flag =
-        reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 2) + 8);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;  // 0 = leader of the pair
+    const int pair = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int n_pairs = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
     const int kc = TRANS_W ? p.n_w : p.k_w;  // contraction length
     const int nkb_total = (kc + BK - 1) / BK;
     const int total_units = p.m_tiles * p.n_tiles * p.splits;
@@ -206,13 +214,12 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full_tma(s), 1);
-            mbar_init(bar_full_w(s), PRODUCER_THREADS);
+            mbar_init(bar_full_w(s), ARRIVALS);
             mbar_init(bar_empty(s), 1);
         }
         mbar_init(bar_tmem_full, 1);
-        mbar_init(bar_tmem_empty, PRODUCER_THREADS);
+        mbar_init(bar_tmem_empty, ARRIVALS);
         *abort_flag = 0;
-        *last_flag = 0;
         fence_barrier_init();
     }
     if (warp == TMA_WARP && lane == 0) {
@@ -220,14 +227,25 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
         tma_prefetch_desc(&tm_codes);
     }
     if (warp == MMA_WARP) {
-        tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
-        tmem_relinquish();
+        if (CG == 2) {
+            tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+            tmem_relinquish();
+        }
     }
     if (p.nested && threadIdx.x < 256) table2[threadIdx.x] = p.code2[threadIdx.x];
     tc_fence_before_sync();
     __syncthreads();
+    if (CG == 2) cluster_sync_all();  // the peer's barriers and TMEM exist before anyone uses them
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+
+    // barriers that both CTAs arrive on live in the leader; everyone reaches them through the
+    // cluster window
+    const uint32_t lead_full_w0 = CG == 2 ? mapa_shared(bar_full_w(0), 0u) : bar_full_w(0);
+    const uint32_t lead_tmem_empty = CG == 2 ? mapa_shared(bar_tmem_empty, 0u) : bar_tmem_empty;
 
     int fail = 0;
 
@@ -235,25 +253,30 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t g = 0;  // ring position, running across units
-            for (int u = blockIdx.x; u < total_units && !fail; u += gridDim.x) {
+            uint32_t unit_iter2 = 0;
+            for (int u = pair; u < total_units && !fail; u += n_pairs, ++unit_iter2) {
                 const Unit w = make_unit(u, p, ROWS_PER_TILE, nkb_total);
                 for (int it = 0; it < w.n_iter; ++it, ++g) {
                     const int s = (int)(g % STAGES);
                     const uint32_t ph = (g / STAGES) & 1u;
                     const uint32_t sa = smem_base + (uint32_t)s * L::STAGE_BYTES;
-                    if (!mbar_wait(bar_empty(s), ph ^ 1u, abort_flag)) { fail = 1; break; }
+                    const bool free_slot = CG == 2 ? mbar_wait_cluster(bar_empty(s), ph ^ 1u, abort_flag)
+                                                   : mbar_wait(bar_empty(s), ph ^ 1u, abort_flag);
+                    if (!free_slot) { fail = 1; break; }
+                    NF4_TRACE2(0, it);
                     if (it < w.nkb) {
                         const int kb = w.kb_begin + it;
                         mbar_arrive_expect_tx(bar_full_tma(s), L::A_BYTES + L::C_BYTES);
 #pragma unroll
                         for (int a = 0; a < NACC; ++a)
-                            tma_load_2d(sa + a * (128 * BK * 2), &tm_act, kb * BK, w.m0 + a * 128,
-                                        bar_full_tma(s));
+                            tma_load_2d(sa + a * (128 * BK * 2), &tm_act, kb * BK,
+                                        w.m0 + a * (128 * CG) + (int)rank * 128, bar_full_tma(s));
                         const uint32_t sc = sa + L::A_BYTES + L::W_BYTES;
+                        const int nb0 = w.n0 + (int)rank * NB;
                         if (TRANS_W)
-                            tma_load_2d(sc, &tm_codes, w.n0 / 2, kb * BK, bar_full_tma(s));
+                            tma_load_2d(sc, &tm_codes, nb0 / 2, kb * BK, bar_full_tma(s));
                         else
-                            tma_load_2d(sc, &tm_codes, kb * (BK / 2), w.n0, bar_full_tma(s));
+                            tma_load_2d(sc, &tm_codes, kb * (BK / 2), nb0, bar_full_tma(s));
                     } else {
                         mbar_arrive(bar_full_tma(s));  // extension step: producers bring operands
                     }
@@ -261,23 +284,37 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
             }
         }
     } else if (warp == MMA_WARP) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_f16(BN, 0u, TRANS_W ? 1u : 0u);
+        // ------------------------------------------------------------------ MMA issuer (leader)
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_f16(BN, 0u, TRANS_W ? 1u : 0u, 128u * CG);
             uint32_t g = 0;
             uint32_t unit_iter = 0;
-            for (int u = blockIdx.x; u < total_units && !fail; u += gridDim.x, ++unit_iter) {
+            long long wait_tma = 0, wait_w = 0;  // tuning: cycles the issuer spent on each barrier
+            for (int u = pair; u < total_units && !fail; u += n_pairs, ++unit_iter) {
                 const Unit w = make_unit(u, p, ROWS_PER_TILE, nkb_total);
-                // the accumulators of the previous unit must have been drained
-                if (!mbar_wait(bar_tmem_empty, (unit_iter & 1u) ^ 1u, abort_flag)) { fail = 6; break; }
+                // the accumulators of the previous unit must have been drained (in both CTAs)
+                if (!mbar_wait_cluster(bar_tmem_empty, (unit_iter & 1u) ^ 1u, abort_flag)) {
+                    fail = 6;
+                    break;
+                }
                 tc_fence_after_sync();
                 for (int it = 0; it < w.n_iter; ++it, ++g) {
                     const int s = (int)(g % STAGES);
                     const uint32_t ph = (g / STAGES) & 1u;
                     const uint32_t sa = smem_base + (uint32_t)s * L::STAGE_BYTES;
                     const uint32_t sw = sa + L::A_BYTES;
+                    const uint32_t unit_iter2 = unit_iter;
+                    const long long c0 = (p.debug & 2) ? clock64() : 0;
                     if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 2; break; }
-                    if (!mbar_wait(bar_full_w(s), ph, abort_flag)) { fail = 3; break; }
+                    NF4_TRACE2(3, it);
+                    const long long c1 = (p.debug & 2) ? clock64() : 0;
+                    if (!mbar_wait_cluster(bar_full_w(s), ph, abort_flag)) { fail = 3; break; }
+                    NF4_TRACE2(4, it);
+                    if (p.debug & 2) {
+                        const long long c2 = clock64();
+                        wait_tma += c1 - c0;
+                        wait_w += c2 - c1;
+                    }
                     tc_fence_after_sync();
                     if (it < w.nkb) {
                         const uint64_t bdesc0 = TRANS_W
@@ -292,33 +329,46 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                                 const uint64_t adesc =
                                     make_smem_desc(sa + a * (128 * BK * 2), 16, 1024, LAYOUT_SW128) +
                                     (uint64_t)(32 >> 4) * k;
-                                umma_f16(tmem_base + a * BN, adesc, bdesc, idesc,
-                                         (it > 0 || k > 0) ? 1u : 0u);
+                                const uint32_t accum = (it > 0 || k > 0) ? 1u : 0u;
+                                if (CG == 2) umma_f16_pair(tmem_base + a * BN, adesc, bdesc, idesc, accum);
+                                else         umma_f16(tmem_base + a * BN, adesc, bdesc, idesc, accum);
                             }
                         }
                     } else {
                         // K extension: unswizzled core-matrix operands (layout type 0).
                         // A: [row/8][k-half][row%8][16 B]  -> LBO 128, SBO 256 (K-major).
-                        // B forward:  same form over n_w rows (K-major).
-                        // B backward: [r/8][k_w/8][r%8][16 B] -> LBO BN*16, SBO 128 (MN-major).
+                        // B forward:  same form over this CTA's NB n_w rows (K-major).
+                        // B backward: [r/8][k_w/8][r%8][16 B] -> LBO NB*16, SBO 128 (MN-major).
                         const uint64_t bdesc = TRANS_W
-                            ? make_smem_desc(sw, BN * 16, 128, LAYOUT_NONE)
+                            ? make_smem_desc(sw, NB * 16, 128, LAYOUT_NONE)
                             : make_smem_desc(sw, 128, 256, LAYOUT_NONE);
 #pragma unroll
                         for (int a = 0; a < NACC; ++a) {
                             const uint64_t adesc =
                                 make_smem_desc(sa + a * (128 * BK * 2), 128, 256, LAYOUT_NONE);
-                            umma_f16(tmem_base + a * BN, adesc, bdesc, idesc, it > 0 ? 1u : 0u);
+                            const uint32_t accum = it > 0 ? 1u : 0u;
+                            if (CG == 2) umma_f16_pair(tmem_base + a * BN, adesc, bdesc, idesc, accum);
+                            else         umma_f16(tmem_base + a * BN, adesc, bdesc, idesc, accum);
                         }
                     }
-                    umma_commit(bar_empty(s));
+                    if (CG == 2) umma_commit_pair(bar_empty(s), (uint16_t)3);
+                    else         umma_commit(bar_empty(s));
+                    NF4_TRACE2(5, it);
                 }
-                if (!fail) umma_commit(bar_tmem_full);
+                if (!fail) {
+                    if (CG == 2) umma_commit_pair(bar_tmem_full, (uint16_t)3);
+                    else         umma_commit(bar_tmem_full);
+                }
+                if ((p.debug & 2) && blockIdx.x < TRACE_CTAS && unit_iter == 0) {
+                    g_trace[(blockIdx.x * TRACE_UNITS) * TRACE_STAMPS + 5] = (unsigned long long)wait_tma;
+                    g_trace[(blockIdx.x * TRACE_UNITS) * TRACE_STAMPS + 6] = (unsigned long long)wait_w;
+                    g_trace[(blockIdx.x * TRACE_UNITS) * TRACE_STAMPS + 7] = (unsigned long long)clock64();
+                }
             }
         }
     } else {
         // ------------------------------------------------------------------ decode producers
-        const int pt = threadIdx.x;  // 0..511: one 16-byte code chunk (32 weights) per k-block
+        const int pt = threadIdx.x;  // 0..511: WORDS code words (8 weights each) per k-block
         RegLut lut;
         {
             uint16_t bits[16];
@@ -330,62 +380,71 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
         const uint8_t* absmax_u8 = static_cast<const uint8_t*>(p.absmax);
         const float* absmax_f32 = static_cast<const float*>(p.absmax);
 
-        // Chunk geometry. Forward: the code tile is [256 rows][32 B]; chunk c covers row c/2,
-        // half c%2 of the 64-wide k-block. Backward: the tile is [64 rows][128 B], 128-byte
-        // swizzled by TMA; 8 consecutive lanes take 8 different rows of one chunk column so that
-        // both the swizzled reads and the swizzled writes are bank-conflict free.
-        int row, col;
-        uint32_t src_off, dst_off[4];
+        // Piece geometry (a piece = the 4*WORDS code bytes of one thread).
+        // Forward: the code tile is [NB rows][32 B], pieces in memory order.
+        // Backward: the tile is [64 rows][NB/2 B], swizzled by TMA (128-byte pattern for 128-byte
+        // rows, 64-byte pattern for 64-byte rows); 8 consecutive lanes take 8 different rows of
+        // one piece column, so the swizzled reads and the swizzled writes are bank-conflict free.
+        int row, klocal;  // row of the tile; first k_w column (backward) / first k (forward)
+        uint32_t src_off, dst_off[WORDS];
         {
             uint32_t dst;
             int chunk0;
             if (!TRANS_W) {
-                row = pt >> 1;
-                col = pt & 1;
-                src_off = (uint32_t)pt * 16u;
+                constexpr int PPR = 8 / WORDS;  // pieces per row
+                row = pt / PPR;
+                const int part = pt % PPR;
+                klocal = part * 8 * WORDS;
+                src_off = (uint32_t)pt * (4u * WORDS);
                 dst = (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
-                chunk0 = col * 4;
+                chunk0 = part * WORDS;
             } else {
                 row = ((pt >> 6) << 3) | (pt & 7);
-                col = (pt >> 3) & 7;
-                src_off = (uint32_t)row * 128u + (uint32_t)((col ^ (row & 7)) << 4);
-                dst = (uint32_t)(col >> 1) * 8192u + (uint32_t)(row >> 3) * 1024u +
+                const int e = (pt >> 3) & 7;
+                klocal = e * 8 * WORDS;
+                if (CG == 1)
+                    src_off = (uint32_t)row * 128u + (uint32_t)((e ^ (row & 7)) << 4);
+                else
+                    src_off = (uint32_t)row * 64u +
+                              (uint32_t)((((e >> 1) ^ ((row >> 1) & 3)) << 4) + (e & 1) * 8);
+                dst = (uint32_t)(klocal >> 6) * 8192u + (uint32_t)(row >> 3) * 1024u +
                       (uint32_t)(row & 7) * 128u;
-                chunk0 = (col & 1) * 4;
+                chunk0 = (klocal & 63) >> 3;
             }
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < WORDS; ++i)
                 dst_off[i] = smem_base + L::A_BYTES + dst + (uint32_t)(((chunk0 + i) ^ (row & 7)) << 4);
             src_off += smem_base + L::A_BYTES + L::W_BYTES;
         }
         // epilogue geometry: TMEM lane quadrant, column share, private 4 KB staging area inside
-        // the weight slots of ring stages 0 and 1 (free while the accumulators are drained)
+        // the weight slots of the ring (free while the accumulators are drained)
         const int q = warp & 3;
         const int grp = warp >> 2;
         constexpr int CHUNKS_PER_GRP = NACC * (BN / 32) / 4;
-        const uint32_t staging = smem_base + (uint32_t)(warp >> 3) * L::STAGE_BYTES + L::A_BYTES +
-                                 (uint32_t)(warp & 7) * 4096u;
+        const uint32_t staging = smem_base + (uint32_t)(warp / L::WARPS_PER_W_SLOT) * L::STAGE_BYTES +
+                                 L::A_BYTES + (uint32_t)(warp % L::WARPS_PER_W_SLOT) * 4096u;
         const int n_out = TRANS_W ? p.k_w : p.n_w;
         const bool split = p.splits > 1;
         const bool vec_ok = (p.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
 
         uint32_t g = 0;
         uint32_t unit_iter = 0;
-        for (int u = blockIdx.x; u < total_units; u += gridDim.x, ++unit_iter) {
+        for (int u = pair; u < total_units; u += n_pairs, ++unit_iter) {
             const Unit w = make_unit(u, p, ROWS_PER_TILE, nkb_total);
             NF4_TRACE(0);
+            const int nb0 = w.n0 + (int)rank * NB;  // first weight-tile column of this CTA
 
-            // First-level scale index of this thread's chunk (32-bit: n_blocks < 2^31).
-            //   forward : block (n0 + row) * bpr + kb          valid while n0 + row < N_w
-            //   backward: block (kb*64 + row) * bpr + kw / 64  valid while kb*64 + row < N_w, kw < K_w
+            // First-level scale index of this thread's piece (32-bit: n_blocks < 2^31).
+            //   forward : block (nb0 + row) * bpr + kb          valid while nb0 + row < N_w
+            //   backward: block (kb*64 + row) * bpr + kw / 64   valid while kb*64 + row < N_w, kw < K_w
             uint32_t blk, blk_step;
             bool col_ok;
             if (!TRANS_W) {
-                blk = (uint32_t)(w.n0 + row) * (uint32_t)blocks_per_row + (uint32_t)w.kb_begin;
+                blk = (uint32_t)(nb0 + row) * (uint32_t)blocks_per_row + (uint32_t)w.kb_begin;
                 blk_step = 1u;
-                col_ok = w.n0 + row < p.n_w;
+                col_ok = nb0 + row < p.n_w;
             } else {
-                const int kw = w.n0 + col * 32;
+                const int kw = nb0 + klocal;
                 blk = (uint32_t)(w.kb_begin * BK + row) * (uint32_t)blocks_per_row + (uint32_t)(kw >> 6);
                 blk_step = (uint32_t)BK * (uint32_t)blocks_per_row;
                 col_ok = kw < p.k_w;
@@ -426,26 +485,18 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                     const __half2 scale2 = __float2half2_rn(sc);
                     if (it + 1 < w.nkb) fetch_scale(it + 1);
                     if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 4; break; }
+                    if (threadIdx.x == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(1, it); }
                     if (!(p.debug & 1)) {
-                        const uint4 cw = lds128(src_off + stage_off);
-                        if (p.debug & 4) {         // experiment: shared-memory traffic without the ALU work
-                            sts128(dst_off[0] + stage_off, cw);
-                            sts128(dst_off[1] + stage_off, cw);
-                            sts128(dst_off[2] + stage_off, cw);
-                            sts128(dst_off[3] + stage_off, cw);
-                        } else if (p.debug & 8) {  // experiment: ALU work with a single store
-                            const uint4 a = decode_word_reg(cw.x, lut, scale2);
-                            const uint4 b = decode_word_reg(cw.y, lut, scale2);
-                            const uint4 c = decode_word_reg(cw.z, lut, scale2);
-                            const uint4 d = decode_word_reg(cw.w, lut, scale2);
-                            sts128(dst_off[0] + stage_off,
-                                   make_uint4(a.x ^ b.x ^ c.x ^ d.x, a.y ^ b.y ^ c.y ^ d.y,
-                                              a.z ^ b.z ^ c.z ^ d.z, a.w ^ b.w ^ c.w ^ d.w));
-                        } else {
+                        if (WORDS == 4) {
+                            const uint4 cw = lds128(src_off + stage_off);
                             sts128(dst_off[0] + stage_off, decode_word_reg(cw.x, lut, scale2));
                             sts128(dst_off[1] + stage_off, decode_word_reg(cw.y, lut, scale2));
-                            sts128(dst_off[2] + stage_off, decode_word_reg(cw.z, lut, scale2));
-                            sts128(dst_off[3] + stage_off, decode_word_reg(cw.w, lut, scale2));
+                            sts128(dst_off[WORDS - 2] + stage_off, decode_word_reg(cw.z, lut, scale2));
+                            sts128(dst_off[WORDS - 1] + stage_off, decode_word_reg(cw.w, lut, scale2));
+                        } else {
+                            const uint2 cw = lds64(src_off + stage_off);
+                            sts128(dst_off[0] + stage_off, decode_word_reg(cw.x, lut, scale2));
+                            sts128(dst_off[1] + stage_off, decode_word_reg(cw.y, lut, scale2));
                         }
                     }
                 } else {
@@ -454,21 +505,21 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                     const uint32_t abase = smem_base + stage_off;
                     const uint32_t wbase = abase + L::A_BYTES;
                     const uint4 zero = make_uint4(0, 0, 0, 0);
-                    // ext_a rows m0 .. m0 + 128*NACC: two 16-byte halves per row
-                    for (int c = pt; c < ROWS_PER_TILE * 2; c += PRODUCER_THREADS) {
+                    // this CTA's ext_a rows: two 16-byte halves per row
+                    for (int c = pt; c < 128 * NACC * 2; c += PRODUCER_THREADS) {
                         const int r_all = c >> 1, half = c & 1;
-                        const long long gm = (long long)w.m0 + r_all;
+                        const int acc = r_all >> 7, r = r_all & 127;
+                        const long long gm = (long long)w.m0 + acc * (128 * CG) + (int)rank * 128 + r;
                         uint4 v = zero;
                         if (gm < p.m)
                             v = __ldg(reinterpret_cast<const uint4*>(p.ext_a + gm * 16) + half);
-                        const int acc = r_all >> 7, r = r_all & 127;
                         sts128(abase + acc * (128 * BK * 2) + (r >> 3) * 256 + half * 128 +
                                    (r & 7) * 16, v);
                     }
                     if (!TRANS_W) {
-                        for (int c = pt; c < BN * 2; c += PRODUCER_THREADS) {
+                        for (int c = pt; c < NB * 2; c += PRODUCER_THREADS) {
                             const int r = c >> 1, half = c & 1;
-                            const long long gn = (long long)w.n0 + r;
+                            const long long gn = (long long)nb0 + r;
                             uint4 v = zero;
                             if (gn < p.n_w)
                                 v = __ldg(reinterpret_cast<const uint4*>(p.ext_b + gn * 16) + half);
@@ -476,19 +527,25 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                         }
                     } else {
                         // lora_a [16, K_w]: chunk (r, gq) = 8 consecutive k_w of rank row r
-                        for (int c = pt; c < 16 * (BN / 8); c += PRODUCER_THREADS) {
-                            const int r = c / (BN / 8), gq = c % (BN / 8);
-                            const long long kw = (long long)w.n0 + gq * 8;
+                        for (int c = pt; c < 16 * (NB / 8); c += PRODUCER_THREADS) {
+                            const int r = c / (NB / 8), gq = c % (NB / 8);
+                            const long long kw = (long long)nb0 + gq * 8;
                             uint4 v = zero;
                             if (kw < p.k_w)
                                 v = __ldg(reinterpret_cast<const uint4*>(
                                     p.ext_b + (long long)r * p.k_w + kw));
-                            sts128(wbase + (r >> 3) * (BN * 16) + gq * 128 + (r & 7) * 16, v);
+                            sts128(wbase + (r >> 3) * (NB * 16) + gq * 128 + (r & 7) * 16, v);
                         }
                     }
                 }
+                // publish: every lane fences its writes towards the async proxy, one lane arrives
                 fence_proxy_async_smem();
-                mbar_arrive(bar_full_w(s));
+                __syncwarp();
+                if (lane == 0) {
+                    if (CG == 2) mbar_arrive_cluster(lead_full_w0 + 8u * s);
+                    else         mbar_arrive(bar_full_w(s));
+                }
+                if (threadIdx.x == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(2, it); }
             }
 
             // -------------------------------------------------------------- epilogue of the unit
@@ -499,8 +556,17 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
             NF4_TRACE(2);
             if (!fail) {
                 tc_fence_after_sync();
-                const int lrow = lane;                      // row of this lane inside its quadrant
+                const int lrow = lane;  // row of this lane inside its quadrant
                 const int rd_row = lane >> 3, rd_chunk = lane & 7;
+                auto release_tmem = [&]() {
+                    // every accumulator value of this warp is in registers / staging
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (CG == 2) mbar_arrive_cluster(lead_tmem_empty);
+                        else         mbar_arrive(bar_tmem_empty);
+                    }
+                };
                 if (!split) {
                     // two 32-column chunks -> one [32 rows x 64 cols] fp16 box, written out as
                     // whole 128-byte lines
@@ -532,17 +598,15 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                                 sts128(staging + lrow * 128 + (((h * 4 + i) ^ (lrow & 7)) << 4), o);
                             }
                         }
-                        if (b == CHUNKS_PER_GRP / 2 - 1) {
-                            // every accumulator value of this thread is in registers / staging
-                            tc_fence_before_sync();
-                            mbar_arrive(bar_tmem_empty);
-                        }
+                        if (b == CHUNKS_PER_GRP / 2 - 1) release_tmem();
                         __syncwarp();
+                        const long long grow0 =
+                            (long long)w.m0 + acc * (128 * CG) + (int)rank * 128 + q * 32;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int rr = i * 4 + rd_row;
                             const uint4 v = lds128(staging + rr * 128 + ((rd_chunk ^ (rr & 7)) << 4));
-                            const long long grow = (long long)w.m0 + acc * 128 + q * 32 + rr;
+                            const long long grow = grow0 + rr;
                             const int colg = w.n0 + ch0 * 32 + rd_chunk * 8;
                             if (grow < p.m && colg < n_out) {
                                 __half* dst = p.out + grow * p.ld_out + colg;
@@ -559,8 +623,9 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                         __syncwarp();
                     }
                 } else {
-                    // fp32 partial tile of this slice: one [32 rows x 32 cols] box per chunk
-                    float* part = p.ws_partials + ((size_t)w.tile_id * p.splits + w.slice) * TILE_ELEMS;
+                    // fp32 partial sums of this slice: one [32 rows x 32 cols] box per chunk into
+                    // the slice's row-major plane
+                    float* plane = p.ws + (size_t)w.slice * ((size_t)p.m * (size_t)p.ldp);
 #pragma unroll 1
                     for (int t = grp * CHUNKS_PER_GRP; t < (grp + 1) * CHUNKS_PER_GRP; ++t) {
                         const int acc = t / (BN / 32), ch = t % (BN / 32);
@@ -571,105 +636,36 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                         for (int i = 0; i < 8; ++i)
                             sts128(staging + lrow * 128 + ((i ^ (lrow & 7)) << 4),
                                    make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]));
-                        if (t == (grp + 1) * CHUNKS_PER_GRP - 1) {
-                            tc_fence_before_sync();
-                            mbar_arrive(bar_tmem_empty);
-                        }
+                        if (t == (grp + 1) * CHUNKS_PER_GRP - 1) release_tmem();
                         __syncwarp();
+                        const long long grow0 =
+                            (long long)w.m0 + acc * (128 * CG) + (int)rank * 128 + q * 32;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int rr = i * 4 + rd_row;
                             const uint4 v = lds128(staging + rr * 128 + ((rd_chunk ^ (rr & 7)) << 4));
-                            const int trow = acc * 128 + q * 32 + rr;
-                            __stcg(reinterpret_cast<uint4*>(part + (size_t)trow * BN + ch * 32 +
-                                                            rd_chunk * 4), v);
+                            const long long grow = grow0 + rr;
+                            const int colg = w.n0 + ch * 32 + rd_chunk * 4;
+                            if (grow < p.m && colg < n_out) {
+                                float* dst = plane + grow * p.ldp + colg;  // ldp % 4 == 0
+                                if (colg + 4 <= n_out) {
+                                    __stcg(reinterpret_cast<uint4*>(dst), v);
+                                } else {
+                                    const float* fv = reinterpret_cast<const float*>(&v);
+                                    for (int e = 0; e < 4; ++e)
+                                        if (colg + e < n_out) dst[e] = fv[e];
+                                }
+                            }
                         }
                         __syncwarp();
                     }
                 }
             }
             NF4_TRACE(3);
-            if (split) {
-                // Last-arriver reduction. Every thread publishes its partials, the 512 epilogue
-                // threads meet (whether or not a wait timed out, so the barrier always fills), one
-                // of them takes a ticket; the unit holding the last ticket sums the slices in order.
-                __threadfence();
-                named_bar_sync(1, PRODUCER_THREADS);
-                if (threadIdx.x == 0) {
-                    int last = 0;
-                    if (!*abort_flag) {
-                        const unsigned ticket = atomicAdd(p.ws_count + w.tile_id, 1u);
-                        last = (ticket == (unsigned)p.splits - 1u) ? 1 : 0;
-                    }
-                    *last_flag = last;
-                }
-                named_bar_sync(1, PRODUCER_THREADS);
-                NF4_TRACE(4);
-                if (*last_flag) {
-                    __threadfence();
-                    const float* base = p.ws_partials + (size_t)w.tile_id * p.splits * TILE_ELEMS;
-                    constexpr int UNITS = ROWS_PER_TILE * (BN / 8);  // 8-column groups in the tile
-                    const unsigned nz = (unsigned)p.splits;
-                    // Two 8-column groups per thread and up to four slices are in flight at a
-                    // time (16 independent 16-byte loads), so the L2 latency is paid once per
-                    // round, not once per load; slices are added in index order (deterministic).
-                    static_assert(UNITS % (2 * PRODUCER_THREADS) == 0, "two groups per thread");
-                    for (int uu = threadIdx.x; uu < UNITS; uu += 2 * PRODUCER_THREADS) {
-                        float v[2][8];
-                        const float4* src0[2];
-#pragma unroll
-                        for (int hgrp = 0; hgrp < 2; ++hgrp) {
-                            const int ug = uu + hgrp * PRODUCER_THREADS;
-                            src0[hgrp] = reinterpret_cast<const float4*>(
-                                base + (size_t)(ug / (BN / 8)) * BN + (ug % (BN / 8)) * 8);
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) v[hgrp][e] = 0.f;
-                        }
-                        for (unsigned z0 = 0; z0 < nz; z0 += 4) {
-                            float4 a[2][4], bq[2][4];
-#pragma unroll
-                            for (int hgrp = 0; hgrp < 2; ++hgrp)
-#pragma unroll
-                                for (unsigned j = 0; j < 4; ++j) {
-                                    if (z0 + j < nz) {
-                                        const float4* src =
-                                            src0[hgrp] + (size_t)(z0 + j) * (TILE_ELEMS / 4);
-                                        a[hgrp][j] = __ldcg(src);
-                                        bq[hgrp][j] = __ldcg(src + 1);
-                                    } else {
-                                        a[hgrp][j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                                        bq[hgrp][j] = a[hgrp][j];
-                                    }
-                                }
-#pragma unroll
-                            for (int hgrp = 0; hgrp < 2; ++hgrp)
-#pragma unroll
-                                for (unsigned j = 0; j < 4; ++j) {
-                                    v[hgrp][0] += a[hgrp][j].x; v[hgrp][1] += a[hgrp][j].y;
-                                    v[hgrp][2] += a[hgrp][j].z; v[hgrp][3] += a[hgrp][j].w;
-                                    v[hgrp][4] += bq[hgrp][j].x; v[hgrp][5] += bq[hgrp][j].y;
-                                    v[hgrp][6] += bq[hgrp][j].z; v[hgrp][7] += bq[hgrp][j].w;
-                                }
-                        }
-#pragma unroll
-                        for (int hgrp = 0; hgrp < 2; ++hgrp) {
-                            const int ug = uu + hgrp * PRODUCER_THREADS;
-                            const int trow = ug / (BN / 8), c8 = ug % (BN / 8);
-                            const long long grow = (long long)w.m0 + trow;
-                            const int colg = w.n0 + c8 * 8;
-                            if (grow < p.m && colg < n_out)
-                                store8(p.out + grow * p.ld_out + colg, v[hgrp], colg, n_out, vec_ok,
-                                       TRANS_W ? nullptr : p.bias);
-                        }
-                    }
-                    if (threadIdx.x == 0) p.ws_count[w.tile_id] = 0u;  // ready for the next launch
-                }
-            }
-            NF4_TRACE(5);
             // the staging areas live in weight slots: nobody may decode the next unit into them
             // before every warp has read its staging back
             named_bar_sync(1, PRODUCER_THREADS);
-            NF4_TRACE(6);
+            NF4_TRACE(4);
         }
     }
 
@@ -682,9 +678,70 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
     }
     tc_fence_before_sync();
     __syncthreads();
+    if (CG == 2) cluster_sync_all();  // the peer may still read this CTA's shared memory / barriers
     if (warp == MMA_WARP) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        if (CG == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else         tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// Adds the split-K planes in slice order, applies the bias and writes fp16: out[i][j] =
+// fp16(sum_z ws[z][i][j] + bias[j]). Eight columns per thread, all slices' loads in flight at once.
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ ws, long long m, long long n_out, long long ldp,
+                     int splits, const __half* __restrict__ bias, __half* __restrict__ out,
+                     long long ld_out, int vec_ok) {
+    const long long groups_per_row = (n_out + 7) / 8;
+    const long long total = m * groups_per_row;
+    const size_t plane = (size_t)m * (size_t)ldp;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / groups_per_row;
+        const long long col = (i % groups_per_row) * 8;
+        const float* src = ws + row * ldp + col;
+        float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (col + 8 <= n_out) {
+            for (int z0 = 0; z0 < splits; z0 += 4) {
+                float4 a[4], b[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (z0 + j < splits) {
+                        const float4* s4 = reinterpret_cast<const float4*>(src + (size_t)(z0 + j) * plane);
+                        a[j] = __ldcs(s4);
+                        b[j] = __ldcs(s4 + 1);
+                    } else {
+                        a[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                        b[j] = a[j];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    v[0] += a[j].x; v[1] += a[j].y; v[2] += a[j].z; v[3] += a[j].w;
+                    v[4] += b[j].x; v[5] += b[j].y; v[6] += b[j].z; v[7] += b[j].w;
+                }
+            }
+        } else {
+            for (int z = 0; z < splits; ++z)
+                for (int e = 0; e < 8; ++e)
+                    if (col + e < n_out) v[e] += src[(size_t)z * plane + e];
+        }
+        if (bias != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (col + e < n_out) v[e] += __half2float(bias[col + e]);
+        }
+        __half* dst = out + row * ld_out + col;
+        if (vec_ok && col + 8 <= n_out) {
+            uint4 o;
+            o.x = pack_half2(v[0], v[1]); o.y = pack_half2(v[2], v[3]);
+            o.z = pack_half2(v[4], v[5]); o.w = pack_half2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(dst) = o;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+                if (col + e < n_out) dst[e] = __float2half_rn(v[e]);
+        }
     }
 }
 
@@ -723,36 +780,6 @@ static bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* ba
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Tiling and split-K plan shared by the launcher and the workspace-size query.
-GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int sm_count) {
-    GemmPlan pl;
-    pl.nacc = m > 128 ? 2 : 1;
-    const long long n_out = trans_w ? k_w : n_w;
-    const long long kc = trans_w ? n_w : k_w;
-    pl.m_tiles = (int)((m + 128 * pl.nacc - 1) / (128 * pl.nacc));
-    pl.n_tiles = (int)((n_out + BN - 1) / BN);
-    const int nkb = (int)((kc + BK - 1) / BK);
-    const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
-    int splits = 1;
-    if (tiles * 2 <= sm_count && tiles <= (long long)(GEMM_COUNTER_BYTES / sizeof(unsigned)) &&
-        nkb >= 8) {
-        splits = (int)(sm_count / tiles);
-        const int max_by_depth = nkb / 4;  // keep at least 4 k-blocks per slice
-        if (splits > max_by_depth) splits = max_by_depth;
-        if (splits > 16) splits = 16;
-        if (splits < 1) splits = 1;
-    }
-    pl.kb_per_split = (nkb + splits - 1) / splits;
-    pl.splits = (nkb + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty slice
-    pl.partial_bytes = pl.splits > 1
-        ? (size_t)tiles * pl.splits * (size_t)(128 * pl.nacc * BN) * sizeof(float) : 0;
-    // A fixed-size counter area (splitting only happens with fewer tiles than SMs, so 1024
-    // counters always suffice): its extent never depends on the shape, so the bytes that must stay
-    // zero are the same for every call that shares a workspace.
-    pl.counter_bytes = pl.splits > 1 ? GEMM_COUNTER_BYTES : 0;
-    return pl;
-}
-
 static int debug_flags() {
     static int flags = -1;
     if (flags < 0) {
@@ -762,16 +789,47 @@ static int debug_flags() {
     return flags;
 }
 
-template <int NACC, bool TRANS_W, int STAGES>
+// Tiling and split-K plan shared by the launcher and the workspace-size query.
+GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int sm_count) {
+    GemmPlan pl;
+    if (m <= 128)      { pl.cg = 1; pl.nacc = 1; }
+    else if (m <= 256) { pl.cg = 2; pl.nacc = 1; }
+    else               { pl.cg = 2; pl.nacc = 2; }
+    if ((debug_flags() & 16) && m > 128) { pl.cg = 1; pl.nacc = 2; }  // tuning: single-CTA tiles
+    const int rows = 128 * pl.cg * pl.nacc;
+    const long long n_out = trans_w ? k_w : n_w;
+    const long long kc = trans_w ? n_w : k_w;
+    pl.m_tiles = (int)((m + rows - 1) / rows);
+    pl.n_tiles = (int)((n_out + BN - 1) / BN);
+    const int nkb = (int)((kc + BK - 1) / BK);
+    const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
+    const int slots = sm_count / pl.cg;  // units that run at the same time
+    int splits = 1;
+    if (tiles * 2 <= slots && nkb >= 8) {
+        splits = (int)(slots / tiles);
+        const int max_by_depth = nkb / 4;  // keep at least 4 k-blocks per slice
+        if (splits > max_by_depth) splits = max_by_depth;
+        if (splits > 16) splits = 16;
+        if (splits < 1) splits = 1;
+    }
+    pl.kb_per_split = (nkb + splits - 1) / splits;
+    pl.splits = (nkb + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty slice
+    pl.ldp = (n_out + 3) / 4 * 4;
+    pl.ws_bytes = pl.splits > 1 ? (size_t)pl.splits * (size_t)m * (size_t)pl.ldp * sizeof(float) : 0;
+    return pl;
+}
+
+template <int CG, int NACC, bool TRANS_W, int STAGES>
 static cudaError_t launch_cfg(const GemmArgs& a, const GemmPlan& pl, cudaStream_t stream,
                               const char** why) {
-    using L = SmemLayout<NACC, STAGES>;
-    auto kernel = nf4_gemm_kernel<NACC, TRANS_W, STAGES>;
+    using L = SmemLayout<CG, NACC, STAGES>;
+    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::DYNAMIC_BYTES);
     if (e != cudaSuccess) { *why = "cudaFuncSetAttribute(shared memory)"; return e; }
 
     const long long kc = TRANS_W ? a.n_w : a.k_w;
+    const long long n_out = TRANS_W ? a.k_w : a.n_w;
     CUtensorMap tm_act, tm_codes;
     if (!make_map_2d(&tm_act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.act, (uint64_t)kc, (uint64_t)a.m,
                      (uint64_t)a.ld_act * 2, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)) {
@@ -780,9 +838,10 @@ static cudaError_t launch_cfg(const GemmArgs& a, const GemmPlan& pl, cudaStream_
     }
     const bool ok = TRANS_W
         ? make_map_2d(&tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.codes, (uint64_t)a.k_w / 2,
-                      (uint64_t)a.n_w, (uint64_t)a.k_w / 2, BN / 2, BK, CU_TENSOR_MAP_SWIZZLE_128B)
+                      (uint64_t)a.n_w, (uint64_t)a.k_w / 2, L::NB / 2, BK,
+                      CG == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)
         : make_map_2d(&tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.codes, (uint64_t)a.k_w / 2,
-                      (uint64_t)a.n_w, (uint64_t)a.k_w / 2, BK / 2, BN, CU_TENSOR_MAP_SWIZZLE_NONE);
+                      (uint64_t)a.n_w, (uint64_t)a.k_w / 2, BK / 2, L::NB, CU_TENSOR_MAP_SWIZZLE_NONE);
     if (!ok) { *why = "cuTensorMapEncodeTiled(codes)"; return cudaErrorInvalidValue; }
 
     GemmParams p;
@@ -802,35 +861,79 @@ static cudaError_t launch_cfg(const GemmArgs& a, const GemmPlan& pl, cudaStream_
     p.n_tiles = pl.n_tiles;
     p.splits = pl.splits;
     p.kb_per_split = pl.kb_per_split;
-    p.ws_count = nullptr;
-    p.ws_partials = nullptr;
+    p.ldp = pl.ldp;
+    p.ws = nullptr;
     p.debug = debug_flags();
     if (p.splits > 1) {
-        if (a.workspace == nullptr || a.workspace_bytes < pl.counter_bytes + pl.partial_bytes) {
+        if (a.workspace == nullptr || a.workspace_bytes < pl.ws_bytes) {
             p.splits = 1;  // no scratch given: one unit per tile walks the whole K range
             p.kb_per_split = (int)((kc + BK - 1) / BK);
         } else {
-            p.ws_count = static_cast<unsigned int*>(a.workspace);
-            p.ws_partials = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + pl.counter_bytes);
+            p.ws = static_cast<float*>(a.workspace);
         }
     }
     const long long units = (long long)p.m_tiles * p.n_tiles * p.splits;
-    const unsigned grid = (unsigned)(units < a.sm_count ? units : a.sm_count);
-    kernel<<<grid, GEMM_THREADS, L::DYNAMIC_BYTES, stream>>>(tm_act, tm_codes, p);
-    e = cudaGetLastError();
-    if (e != cudaSuccess) *why = "kernel launch";
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = L::DYNAMIC_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CG;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = CG == 2 ? 1 : 0;
+
+    // Units that can be resident at once: one CTA per SM; pairs must sit in one GPC, so ask the
+    // runtime how many clusters fit (once per configuration and device count is stable).
+    int slots = a.sm_count / CG;
+    if (CG == 2) {
+        static int max_clusters = -1;
+        if (max_clusters < 0) {
+            cfg.gridDim = dim3((unsigned)(a.sm_count / 2) * 2, 1, 1);
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n > 0)
+                max_clusters = n;
+            else
+                max_clusters = a.sm_count / 2;
+        }
+        if (max_clusters < slots) slots = max_clusters;
+    }
+    const unsigned grid = (unsigned)(units < slots ? units : slots) * CG;
+    cfg.gridDim = dim3(grid, 1, 1);
+    e = cudaLaunchKernelEx(&cfg, kernel, tm_act, tm_codes, p);
+    if (e != cudaSuccess) { *why = "kernel launch"; return e; }
+
+    if (p.splits > 1) {
+        const long long total = a.m * ((n_out + 7) / 8);
+        long long blocks = (total + 255) / 256;
+        const long long cap = (long long)a.sm_count * 8;
+        if (blocks > cap) blocks = cap;
+        const int vec_ok = (a.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15) == 0);
+        splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+            p.ws, a.m, n_out, p.ldp, p.splits, TRANS_W ? nullptr : a.bias, a.out, a.ld_out, vec_ok);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) *why = "split-K reduce launch";
+    }
     return e;
 }
 
 cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why) {
     *why = "";
     const GemmPlan pl = plan_gemm(a.m, a.n_w, a.k_w, a.trans_w, a.sm_count);
-    if (pl.nacc == 2) {
-        return a.trans_w ? launch_cfg<2, true, 3>(a, pl, stream, why)
-                         : launch_cfg<2, false, 3>(a, pl, stream, why);
-    }
-    return a.trans_w ? launch_cfg<1, true, 4>(a, pl, stream, why)
-                     : launch_cfg<1, false, 4>(a, pl, stream, why);
+    if (pl.cg == 2 && pl.nacc == 2)
+        return a.trans_w ? launch_cfg<2, 2, true, 4>(a, pl, stream, why)
+                         : launch_cfg<2, 2, false, 4>(a, pl, stream, why);
+    if (pl.cg == 2)
+        return a.trans_w ? launch_cfg<2, 1, true, 6>(a, pl, stream, why)
+                         : launch_cfg<2, 1, false, 6>(a, pl, stream, why);
+    if (pl.nacc == 2)
+        return a.trans_w ? launch_cfg<1, 2, true, 3>(a, pl, stream, why)
+                         : launch_cfg<1, 2, false, 3>(a, pl, stream, why);
+    return a.trans_w ? launch_cfg<1, 1, true, 4>(a, pl, stream, why)
+                     : launch_cfg<1, 1, false, 4>(a, pl, stream, why);
 }
 
 }  // namespace nf4
@@ -841,6 +944,15 @@ extern "C" int nf4dbg_read_trace(unsigned long long* dst, int max_entries) {
     if (max_entries < n) return -1;
     if (cudaDeviceSynchronize() != cudaSuccess) return -2;
     if (cudaMemcpyFromSymbol(dst, nf4::g_trace, sizeof(unsigned long long) * n) != cudaSuccess)
+        return -3;
+    return n;
+}
+
+extern "C" int nf4dbg_read_trace2(unsigned long long* dst, int max_entries) {
+    const int n = 2 * nf4::TRACE2_EVENTS * nf4::TRACE2_ITERS;
+    if (max_entries < n) return -1;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+    if (cudaMemcpyFromSymbol(dst, nf4::g_trace2, sizeof(unsigned long long) * n) != cudaSuccess)
         return -3;
     return n;
 }

@@ -51,15 +51,15 @@ struct GemmArgs {
     size_t workspace_bytes;
 };
 
-constexpr size_t GEMM_COUNTER_BYTES = 4096;  // split-K arrival counters at the workspace head
-
 // Tiling and split-K plan of one GEMM call.
 struct GemmPlan {
+    int cg;            // CTAs cooperating on one tile (1, or 2 = CTA pair)
     int nacc;          // 128-row accumulators per CTA (1 or 2)
     int m_tiles, n_tiles;
-    int splits;        // CTAs sharing one tile along K
-    int kb_per_split;  // 64-deep k-blocks per CTA
-    size_t counter_bytes, partial_bytes;  // workspace layout: counters first, then partials
+    int splits;        // units sharing one tile along K
+    int kb_per_split;  // 64-deep k-blocks per unit
+    long long ldp;     // row pitch (floats) of a split-K partial plane
+    size_t ws_bytes;   // split-K scratch: splits planes of m x ldp floats (0 when not split)
 };
 GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int sm_count);
 

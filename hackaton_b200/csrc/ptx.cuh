@@ -186,18 +186,22 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t local_addr, uint32_t ra
     return a;
 }
 
-// Arrive (release at cluster scope) on a barrier given by its cluster-window address.
+// Arrive on a barrier given by its cluster-window address (it may live in the peer CTA). The
+// shared-memory writes it publishes are consumed by the tensor cores (async proxy) and were fenced
+// with fence.proxy.async beforehand; a cluster-scope release on every arrive costs about a
+// microsecond per pipeline stage on B200 and is not needed for that hand-over.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
-                 : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
-__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+// Non-blocking phase test, used to poll the barriers that the peer CTA signals (remote arrives,
+// multicast tcgen05.commit).
+__device__ __forceinline__ uint32_t mbar_test_wait_cluster(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(done)
@@ -206,14 +210,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t
     return done;
 }
 
-// Bounded wait that acquires at cluster scope (for barriers the peer CTA arrives on).
+// Bounded polling wait for a barrier signalled from the peer CTA.
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (mbar_test_wait_cluster(bar, parity)) return true;
     unsigned long long t0 = 0;
     uint32_t polls = 0;
-    while (!mbar_try_wait_cluster(bar, parity)) {
-        if ((++polls & 31u) == 0u) {
+    while (!mbar_test_wait_cluster(bar, parity)) {
+        if ((++polls & 1023u) == 0u) {
             if (*abort_flag) return false;
             unsigned long long now = globaltimer_ns();
             if (t0 == 0) {

@@ -119,19 +119,18 @@ def _stream_ptr(device):
 
 
 _ws_need = {}      # (device, n_rows, n_cols, m, backward) -> bytes of split-K scratch
-_ws_buffers = {}   # (device, stream) -> uint8 tensor; its counter prefix is zero between calls
+_ws_buffers = {}   # (device, stream) -> uint8 tensor
 
 
 def _workspace(device, n_rows, n_cols, m, backward):
     """Split-K scratch for one GEMM call on the current stream: (pointer, bytes) or (None, 0).
-    One buffer per (device, stream), grown on demand and zeroed when it is created: the kernels
-    leave its counters at zero, so it is never cleared again. Calls on the same stream run one
-    after the other and can share it; other streams get their own."""
+    One buffer per (device, stream), grown on demand; it needs no initialisation. Calls on the
+    same stream run one after the other and can share it; other streams get their own."""
     key = (device.index, n_rows, n_cols, m, backward)
     need = _ws_need.get(key)
     if need is None:
         with torch.cuda.device(device):
-            need = int(_lib.lib().nf4b200_workspace_bytes(n_rows, n_cols, m, int(backward), None))
+            need = int(_lib.lib().nf4b200_workspace_bytes(n_rows, n_cols, m, int(backward)))
         if need < 0:
             _lib.check(need)
         _ws_need[key] = need
@@ -140,7 +139,7 @@ def _workspace(device, n_rows, n_cols, m, backward):
     skey = (device.index, torch.cuda.current_stream(device).cuda_stream)
     buf = _ws_buffers.get(skey)
     if buf is None or buf.numel() < need:
-        buf = torch.zeros(max(need, 1 << 22), dtype=torch.uint8, device=device)
+        buf = torch.empty(max(need, 1 << 22), dtype=torch.uint8, device=device)
         _ws_buffers[skey] = buf
     return buf.data_ptr(), buf.numel()
 

@@ -104,15 +104,13 @@ int nf4b200_linear_bwd_dx(const nf4b200_weight* w, const void* dy, int64_t m, in
 /*
  * Bytes of split-K scratch that nf4b200_linear_fwd (backward == 0) or nf4b200_linear_bwd_dx
  * (backward == 1) can use for a weight [n_rows, n_cols] and m rows on the current device; 0 when
- * the shape has enough tiles to fill the GPU without splitting. The scratch starts with a
- * fixed-size area of 32-bit arrival counters (`*counter_bytes_out` bytes, the same for every
- * shape): those bytes must be zero before the first use; the kernels leave them zero, so one
- * buffer serves any number of calls, of any shapes, without clearing. Calls that may overlap on the GPU (different streams) need separate
- * buffers. The reference has no counterpart: it lets cuBLAS pick its own workspace
- * (solution/nf4.py:92,99).
+ * the shape has enough tiles to fill the GPU without splitting. The scratch holds fp32 partial
+ * sums between the GEMM kernel and the reduction kernel of one call; its contents need no
+ * initialisation and mean nothing afterwards, so one buffer serves any number of calls on one
+ * stream. Calls that may overlap on the GPU (different streams) need separate buffers. The
+ * reference has no counterpart: it lets cuBLAS pick its own workspace (solution/nf4.py:92,99).
  */
-int64_t nf4b200_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int backward,
-                                int64_t* counter_bytes_out);
+int64_t nf4b200_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int backward);
 
 /*
  * Rank-16 projection used by both passes of the LoRA update (peft's lora_A / lora_B linears;
