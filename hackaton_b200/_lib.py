@@ -16,10 +16,11 @@ LIB_PATH = Path(__file__).resolve().parent / "libnf4b200.so"
 EXPORTS = (
     "nf4b200_query", "nf4b200_last_error", "nf4b200_device_status", "nf4b200_dequant",
     "nf4b200_linear_fwd", "nf4b200_linear_bwd_dx", "nf4b200_lora_down", "nf4b200_lora_grad",
-    "nf4b200_workspace_bytes",
+    "nf4b200_workspace_bytes", "nf4b200_linear_fwd_static",
 )
 
 F16, BF16, F32 = 0, 1, 2
+STATIC_SCRATCH_BYTES = 32 << 20   # NF4B200_STATIC_SCRATCH_BYTES in include/nf4b200.h
 
 
 class Nf4Error(RuntimeError):
@@ -68,6 +69,9 @@ def lib() -> ctypes.CDLL:
                                              c_void_p, c_void_p, c_int64, c_void_p, c_size_t,
                                              c_void_p]
     handle.nf4b200_workspace_bytes.argtypes = [c_int64, c_int64, c_int64, c_int]
+    handle.nf4b200_linear_fwd_static.argtypes = [POINTER(Weight), c_void_p, c_int64, c_int64,
+                                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                                 c_void_p]
     handle.nf4b200_lora_down.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
                                          c_int64, c_float, c_void_p, c_void_p]
     handle.nf4b200_lora_grad.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p,

@@ -150,6 +150,14 @@ int set_workspace(nf4::GemmArgs& g, void* workspace, size_t bytes) {
 
 namespace nf4 {
 
+int set_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
 int* device_status_word() {
     DeviceInfo* d = nullptr;
     if (current_device(&d) != NF4B200_OK) return nullptr;

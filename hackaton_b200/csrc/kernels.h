@@ -86,6 +86,9 @@ struct LoraGradArgs {
 };
 cudaError_t launch_lora_grad(const LoraGradArgs& a, cudaStream_t stream);
 
+// Records a message for nf4b200_last_error() on this thread and returns `code`.
+int set_error(int code, const char* fmt, ...);
+
 // Device-side status word: 0, or a code written by a kernel whose bounded wait ran out.
 int* device_status_word();   // device address of the word for the current device
 cudaError_t read_and_clear_device_status(int* out);

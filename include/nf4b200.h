@@ -92,6 +92,22 @@ int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_
                        void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * The same forward as nf4b200_linear_fwd for callers that have no device memory to lend: hosts
+ * whose memory pool is fixed at start-up, plug-ins that must not allocate inside another
+ * component's stream-ordered region, processes at their memory limit. The split-K scratch is a
+ * fixed array of NF4B200_STATIC_SCRATCH_BYTES inside the library image (each GPU that loads the
+ * library holds it until the process exits); this entry point allocates nothing. Shapes that need
+ * more scratch than that are refused with NF4B200_EINVAL and a message naming both sizes.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call outside any stream capture. All calls on a device share the array: calls that
+ * can overlap on the GPU would race on it. It has no counterpart in the reference.
+ */
+#define NF4B200_STATIC_SCRATCH_BYTES (32u << 20)
+int nf4b200_linear_fwd_static(const nf4b200_weight* w, const void* x, int64_t m, int64_t ldx,
+                              const void* bias, const void* xa, const void* lora_b, void* y,
+                              int64_t ldy, void* stream);
+
+/*
  * Input gradient of the same linear, decode fused:
  *   dx[m, n_cols] = dy[m, n_rows] . W (+ u[m, rank] . lora_a[rank, n_cols])
  * Replaces NF4Linear.backward (solution/nf4.py:94-99): a second dequantize_nf4 + torch.matmul.
