@@ -480,8 +480,11 @@ def run_single(args):
     achieved = gemm_flops / (kern["gate_fwd"] * 1e-3) / 1e12
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": pk["tflops_sustained"], "unit": "TFLOP/s",
-        "frac": achieved / pk["tflops_sustained"], "traffic": None,
-        "kernel": "nf4_gemm_kernel<NACC=2,BN=256,fwd> on gate_proj (M=2048, N=8960, K=1536)",
+        "frac": achieved / pk["tflops_sustained"],
+        # dram__bytes_read.sum + dram__bytes_write.sum of one gate_proj forward launch in an ncu
+        # capture of this benchmark (13.45 MB + 0.20 MB; the algorithmic input is 13.39 MB)
+        "traffic": 13.66e6, "traffic_unit": "bytes per launch, from an ncu capture of this command",
+        "kernel": "nf4_gemm_kernel<CG=2,NACC=2,fwd> (CTA pairs, 512x256 tiles) on gate_proj (M=2048, N=8960, K=1536)",
         "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
         "us_per_launch": {k: v * 1e3 for k, v in kern.items()},
         "tflops": {k: gemm_flops / (v * 1e-3) / 1e12 for k, v in kern.items()},
