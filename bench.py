@@ -602,6 +602,27 @@ def run_multi(args):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     local_ms = float(t.item())
 
+    # end to end: every step's inputs come from pinned host memory, a scalar goes back
+    host = make_activations(shapes, m, device, pinned=True, world=world)
+    dev_in = {k: torch.empty_like(v, device=device) for k, v in host.items()}
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    metric_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def run_e2e(i):
+        for key, src in host.items():
+            dev_in[key].copy_(src, non_blocking=True)
+        outs = step_sharded(layers[i % n_rot], dev_in)
+        metric_host.copy_(outs[-1].float().mean(), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(2):
+        run_e2e(i)
+    e2e_steps = 3
+    _, _, e2e_wall = timed_steps(run_e2e, e2e_steps, barrier=dist.barrier)
+    t = torch.tensor([e2e_wall], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_wall = float(t.item())
+
     if rank == 0:
         value = flops * args.steps / (total_ms * 1e-3) / 1e12
         gathered = 2.0 * m * sum(n for n, _ in shapes.values())
@@ -622,7 +643,9 @@ def run_multi(args):
                          "traffic": None,
                          "kernel": "nf4_gemm_kernel, per GPU, local shards only (no collectives)"},
             "cpu_baseline": None,
-            "e2e": None,
+            "e2e": {"value": flops * e2e_steps / e2e_wall / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,
+                    "steps": e2e_steps, "ms_per_step": e2e_wall / e2e_steps * 1e3},
             "gpu_launches": 14 * args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

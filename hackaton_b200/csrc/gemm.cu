@@ -48,6 +48,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
@@ -172,18 +173,22 @@ __device__ __forceinline__ Unit make_unit(int u, const GemmParams& p, int rows_p
     return w;
 }
 
-template <int CG, int NACC, bool TRANS_W, int STAGES>
+template <int CG, int NACC, bool TRANS_W, int STAGES, int DW>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                 const __grid_constant__ CUtensorMap tm_codes, const GemmParams p) {
     using L = SmemLayout<CG, NACC, STAGES>;
     constexpr int NB = L::NB;
-    constexpr int WORDS = 4 / CG;  // 32-bit code words (8 weights each) per producer thread
-    static_assert(NB * BK / 8 == PRODUCER_THREADS * WORDS, "producer work split");
+    // DW of the 16 producer warps decode (all 16 drain the accumulators); each decoding thread
+    // expands WORDS 32-bit code words (8 weights each) per k-block
+    constexpr int DECODE_THREADS = DW * 32;
+    constexpr int WORDS = NB * BK / 8 / DECODE_THREADS;
+    static_assert(WORDS == 2 || WORDS == 4, "producer work split");
     constexpr uint32_t TMEM_COLS = NACC * BN;
     static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
     constexpr int ROWS_PER_TILE = 128 * CG * NACC;  // token rows of a unit (whole pair)
-    constexpr uint32_t ARRIVALS = CG * PRODUCER_WARPS;
+    constexpr uint32_t ARRIVALS = CG * PRODUCER_WARPS;  // "TMEM drained" arrivals (all warps)
+    constexpr uint32_t W_ARRIVALS = CG * DW;             // "weights ready" arrivals
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -214,7 +219,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full_tma(s), 1);
-            mbar_init(bar_full_w(s), ARRIVALS);
+            mbar_init(bar_full_w(s), W_ARRIVALS);
             mbar_init(bar_empty(s), 1);
         }
         mbar_init(bar_tmem_full, 1);
@@ -399,14 +404,16 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                 dst = (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
                 chunk0 = part * WORDS;
             } else {
-                row = ((pt >> 6) << 3) | (pt & 7);
-                const int e = (pt >> 3) & 7;
+                constexpr int PPR = (NB / 2) / (4 * WORDS);  // pieces per 64-row tile row
+                row = ((pt / (8 * PPR)) << 3) | (pt & 7);
+                const int e = (pt >> 3) % PPR;
                 klocal = e * 8 * WORDS;
+                const int byte = e * 4 * WORDS;              // offset of the piece inside its row
                 if (CG == 1)
-                    src_off = (uint32_t)row * 128u + (uint32_t)((e ^ (row & 7)) << 4);
+                    src_off = (uint32_t)row * 128u + (uint32_t)(((byte >> 4) ^ (row & 7)) << 4);
                 else
                     src_off = (uint32_t)row * 64u +
-                              (uint32_t)((((e >> 1) ^ ((row >> 1) & 3)) << 4) + (e & 1) * 8);
+                              (uint32_t)((((byte >> 4) ^ ((row >> 1) & 3)) << 4) + (byte & 15));
                 dst = (uint32_t)(klocal >> 6) * 8192u + (uint32_t)(row >> 3) * 1024u +
                       (uint32_t)(row & 7) * 128u;
                 chunk0 = (klocal & 63) >> 3;
@@ -468,9 +475,9 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                 }
                 blk += blk_step;
             };
-            if (!fail) fetch_scale(0);
+            if (!fail && warp < DW) fetch_scale(0);
 
-            for (int it = 0; it < w.n_iter && !fail; ++it, ++g) {
+            for (int it = 0; warp < DW && it < w.n_iter && !fail; ++it, ++g) {
                 const int s = (int)(g % STAGES);
                 const uint32_t ph = (g / STAGES) & 1u;
                 const uint32_t stage_off = (uint32_t)s * L::STAGE_BYTES;
@@ -506,7 +513,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                     const uint32_t wbase = abase + L::A_BYTES;
                     const uint4 zero = make_uint4(0, 0, 0, 0);
                     // this CTA's ext_a rows: two 16-byte halves per row
-                    for (int c = pt; c < 128 * NACC * 2; c += PRODUCER_THREADS) {
+                    for (int c = pt; c < 128 * NACC * 2; c += DECODE_THREADS) {
                         const int r_all = c >> 1, half = c & 1;
                         const int acc = r_all >> 7, r = r_all & 127;
                         const long long gm = (long long)w.m0 + acc * (128 * CG) + (int)rank * 128 + r;
@@ -517,7 +524,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                                    (r & 7) * 16, v);
                     }
                     if (!TRANS_W) {
-                        for (int c = pt; c < NB * 2; c += PRODUCER_THREADS) {
+                        for (int c = pt; c < NB * 2; c += DECODE_THREADS) {
                             const int r = c >> 1, half = c & 1;
                             const long long gn = (long long)nb0 + r;
                             uint4 v = zero;
@@ -527,7 +534,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                         }
                     } else {
                         // lora_a [16, K_w]: chunk (r, gq) = 8 consecutive k_w of rank row r
-                        for (int c = pt; c < 16 * (NB / 8); c += PRODUCER_THREADS) {
+                        for (int c = pt; c < 16 * (NB / 8); c += DECODE_THREADS) {
                             const int r = c / (NB / 8), gq = c % (NB / 8);
                             const long long kw = (long long)nb0 + gq * 8;
                             uint4 v = zero;
@@ -608,7 +615,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                             const uint4 v = lds128(staging + rr * 128 + ((rd_chunk ^ (rr & 7)) << 4));
                             const long long grow = grow0 + rr;
                             const int colg = w.n0 + ch0 * 32 + rd_chunk * 8;
-                            if (grow < p.m && colg < n_out) {
+                            if (grow < p.m && colg < n_out && !(p.debug & 64)) {
                                 __half* dst = p.out + grow * p.ld_out + colg;
                                 if (vec_ok && colg + 8 <= n_out) {
                                     *reinterpret_cast<uint4*>(dst) = v;
@@ -796,6 +803,14 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
     else if (m <= 256) { pl.cg = 2; pl.nacc = 1; }
     else               { pl.cg = 2; pl.nacc = 2; }
     if ((debug_flags() & 16) && m > 128) { pl.cg = 1; pl.nacc = 2; }  // tuning: single-CTA tiles
+    int force_splits = 0;
+    if (const char* e = std::getenv("NF4B200_PLAN")) {  // tuning: "nacc,splits" for pair tiles
+        int a = 0, b = 0;
+        if (std::sscanf(e, "%d,%d", &a, &b) == 2 && m > 128) {
+            if (a == 1 || a == 2) { pl.cg = 2; pl.nacc = a; }
+            force_splits = b;
+        }
+    }
     const int rows = 128 * pl.cg * pl.nacc;
     const long long n_out = trans_w ? k_w : n_w;
     const long long kc = trans_w ? n_w : k_w;
@@ -812,6 +827,7 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
         if (splits > 16) splits = 16;
         if (splits < 1) splits = 1;
     }
+    if (force_splits > 0) splits = force_splits < nkb ? force_splits : nkb;
     pl.kb_per_split = (nkb + splits - 1) / splits;
     pl.splits = (nkb + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty slice
     pl.ldp = (n_out + 3) / 4 * 4;
@@ -819,11 +835,11 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
     return pl;
 }
 
-template <int CG, int NACC, bool TRANS_W, int STAGES>
+template <int CG, int NACC, bool TRANS_W, int STAGES, int DW>
 static cudaError_t launch_cfg(const GemmArgs& a, const GemmPlan& pl, cudaStream_t stream,
                               const char** why) {
     using L = SmemLayout<CG, NACC, STAGES>;
-    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES>;
+    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::DYNAMIC_BYTES);
     if (e != cudaSuccess) { *why = "cudaFuncSetAttribute(shared memory)"; return e; }
@@ -923,17 +939,22 @@ static cudaError_t launch_cfg(const GemmArgs& a, const GemmPlan& pl, cudaStream_
 cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why) {
     *why = "";
     const GemmPlan pl = plan_gemm(a.m, a.n_w, a.k_w, a.trans_w, a.sm_count);
-    if (pl.cg == 2 && pl.nacc == 2)
-        return a.trans_w ? launch_cfg<2, 2, true, 4>(a, pl, stream, why)
-                         : launch_cfg<2, 2, false, 4>(a, pl, stream, why);
+    const bool dw8 = (debug_flags() & 32) != 0;  // tuning: 8 decoding warps with twice the work
+    if (pl.cg == 2 && pl.nacc == 2) {
+        if (dw8)
+            return a.trans_w ? launch_cfg<2, 2, true, 4, 8>(a, pl, stream, why)
+                             : launch_cfg<2, 2, false, 4, 8>(a, pl, stream, why);
+        return a.trans_w ? launch_cfg<2, 2, true, 4, 16>(a, pl, stream, why)
+                         : launch_cfg<2, 2, false, 4, 16>(a, pl, stream, why);
+    }
     if (pl.cg == 2)
-        return a.trans_w ? launch_cfg<2, 1, true, 6>(a, pl, stream, why)
-                         : launch_cfg<2, 1, false, 6>(a, pl, stream, why);
+        return a.trans_w ? launch_cfg<2, 1, true, 6, 16>(a, pl, stream, why)
+                         : launch_cfg<2, 1, false, 6, 16>(a, pl, stream, why);
     if (pl.nacc == 2)
-        return a.trans_w ? launch_cfg<1, 2, true, 3>(a, pl, stream, why)
-                         : launch_cfg<1, 2, false, 3>(a, pl, stream, why);
-    return a.trans_w ? launch_cfg<1, 1, true, 4>(a, pl, stream, why)
-                     : launch_cfg<1, 1, false, 4>(a, pl, stream, why);
+        return a.trans_w ? launch_cfg<1, 2, true, 3, 16>(a, pl, stream, why)
+                         : launch_cfg<1, 2, false, 3, 16>(a, pl, stream, why);
+    return a.trans_w ? launch_cfg<1, 1, true, 4, 16>(a, pl, stream, why)
+                     : launch_cfg<1, 1, false, 4, 16>(a, pl, stream, why);
 }
 
 }  // namespace nf4

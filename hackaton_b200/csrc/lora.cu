@@ -23,102 +23,75 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 }
 
 // ------------------------------------------------------------------------------------ lora_down
-// Block: 4 warps x 2 rows. Columns are walked in chunks of 512; P's chunk sits in shared memory
-// as fp32 [16][512]. Lane l owns columns l*8 + 256*t of the chunk.
+// A block of 4 warps owns LD_ROWS rows; each warp takes a quarter of the columns for all of them
+// (lane l owns 8 columns at a time), then the four partial results are added through shared
+// memory. P (at most a few hundred KB, shared by every block) is read straight from global memory
+// with 16-byte loads and lives in L1/L2.
 constexpr int LD_WARPS = 4;
-constexpr int LD_ROWS_PER_WARP = 2;
-constexpr int LD_ROWS = LD_WARPS * LD_ROWS_PER_WARP;
+constexpr int LD_ROWS_PER_WARP = 4;   // rows whose sums one warp carries (= rows per block)
+constexpr int LD_ROWS = LD_ROWS_PER_WARP;
 constexpr int LD_THREADS = LD_WARPS * 32;
-constexpr int LD_CHUNK = 512;
 
+template <bool RANK_MAJOR>  // P is row-major [16, C] (true) or row-major [C, 16] (false)
 __global__ void __launch_bounds__(LD_THREADS)
 lora_down_kernel(const __half* __restrict__ in, long long m, long long c, long long ld_in,
-                 const __half* __restrict__ p, long long p_stride_r, long long p_stride_c,
-                 float scaling, __half* __restrict__ out, int vec_ok, int p_vec) {
-    __shared__ __align__(16) float p_s[16][LD_CHUNK];
+                 const __half* __restrict__ p, float scaling, __half* __restrict__ out) {
+    __shared__ float part[LD_WARPS][LD_ROWS_PER_WARP][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long row0 = (long long)blockIdx.x * LD_ROWS + warp * LD_ROWS_PER_WARP;
+    const long long row0 = (long long)blockIdx.x * LD_ROWS;
     float acc[LD_ROWS_PER_WARP][16];
 #pragma unroll
     for (int r = 0; r < LD_ROWS_PER_WARP; ++r)
 #pragma unroll
         for (int j = 0; j < 16; ++j) acc[r][j] = 0.f;
 
-    for (long long c0 = 0; c0 < c; c0 += LD_CHUNK) {
-        __syncthreads();
-        // stage P[c0 .. c0+512) as fp32 [16][512] with 16-byte loads along the source's
-        // contiguous axis (element-wise when the layout or alignment does not allow them)
-        if (p_vec && p_stride_c == 1) {           // row-major [16, C]
-            for (int i = threadIdx.x; i < 16 * (LD_CHUNK / 8); i += LD_THREADS) {
-                const int j = i / (LD_CHUNK / 8), cc = (i % (LD_CHUNK / 8)) * 8;
-                const long long gc = c0 + cc;
-                float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                if (gc + 8 <= c) {
-                    unpack8(__ldg(reinterpret_cast<const uint4*>(p + j * p_stride_r + gc)), f);
-                } else {
-                    for (int e = 0; e < 8; ++e)
-                        if (gc + e < c) f[e] = __half2float(p[j * p_stride_r + gc + e]);
-                }
-                *reinterpret_cast<float4*>(&p_s[j][cc]) = make_float4(f[0], f[1], f[2], f[3]);
-                *reinterpret_cast<float4*>(&p_s[j][cc + 4]) = make_float4(f[4], f[5], f[6], f[7]);
-            }
-        } else if (p_vec && p_stride_r == 1 && p_stride_c == 16) {   // row-major [C, 16]
-            for (int i = threadIdx.x; i < LD_CHUNK * 2; i += LD_THREADS) {
-                const int cc = i >> 1, h = i & 1;
-                const long long gc = c0 + cc;
-                float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-                if (gc < c) unpack8(__ldg(reinterpret_cast<const uint4*>(p + gc * 16 + h * 8)), f);
+    // this warp's column range: a quarter of the columns, in multiples of 8 (c % 8 == 0 here)
+    const long long groups = c / 8;
+    const long long g_begin = groups * warp / LD_WARPS, g_end = groups * (warp + 1) / LD_WARPS;
+    for (long long gc = (g_begin + lane) * 8; gc < g_end * 8; gc += 256) {
+        float x[LD_ROWS_PER_WARP][8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) p_s[h * 8 + e][cc] = f[e];
-            }
-        } else {
-            for (int i = threadIdx.x; i < 16 * LD_CHUNK; i += LD_THREADS) {
-                int cc, j;
-                if (p_stride_c == 1) { j = i / LD_CHUNK; cc = i % LD_CHUNK; }
-                else                 { cc = i / 16;      j = i % 16; }
-                const long long gc = c0 + cc;
-                p_s[j][cc] = gc < c ? __half2float(p[gc * p_stride_c + j * p_stride_r]) : 0.f;
-            }
-        }
-        __syncthreads();
-#pragma unroll
-        for (int t = 0; t < LD_CHUNK / 256; ++t) {
-            const int cc = lane * 8 + 256 * t;
-            const long long gc = c0 + cc;
-            float x[LD_ROWS_PER_WARP][8];
-#pragma unroll
-            for (int r = 0; r < LD_ROWS_PER_WARP; ++r) {
-                const long long gr = row0 + r;
+        for (int r = 0; r < LD_ROWS_PER_WARP; ++r) {
+            const long long gr = row0 + r;
+            if (gr < m) {
+                unpack8(__ldg(reinterpret_cast<const uint4*>(in + gr * ld_in + gc)), x[r]);
+            } else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[r][e] = 0.f;
-                if (gr < m && gc < c) {
-                    const __half* src = in + gr * ld_in + gc;
-                    if (vec_ok && gc + 8 <= c) {
-                        unpack8(__ldg(reinterpret_cast<const uint4*>(src)), x[r]);
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e)
-                            if (gc + e < c) x[r][e] = __half2float(src[e]);
-                    }
-                }
             }
+        }
+        if (RANK_MAJOR) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                const float4 pa = *reinterpret_cast<const float4*>(&p_s[j][cc]);
-                const float4 pb = *reinterpret_cast<const float4*>(&p_s[j][cc + 4]);
+                float pv[8];
+                unpack8(__ldg(reinterpret_cast<const uint4*>(p + (long long)j * c + gc)), pv);
 #pragma unroll
                 for (int r = 0; r < LD_ROWS_PER_WARP; ++r) {
                     float a = acc[r][j];
-                    a = fmaf(x[r][0], pa.x, a); a = fmaf(x[r][1], pa.y, a);
-                    a = fmaf(x[r][2], pa.z, a); a = fmaf(x[r][3], pa.w, a);
-                    a = fmaf(x[r][4], pb.x, a); a = fmaf(x[r][5], pb.y, a);
-                    a = fmaf(x[r][6], pb.z, a); a = fmaf(x[r][7], pb.w, a);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) a = fmaf(x[r][e], pv[e], a);
                     acc[r][j] = a;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float pa[8], pb[8];
+                const uint4* src = reinterpret_cast<const uint4*>(p + (gc + e) * 16);
+                unpack8(__ldg(src), pa);
+                unpack8(__ldg(src + 1), pb);
+#pragma unroll
+                for (int r = 0; r < LD_ROWS_PER_WARP; ++r) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        acc[r][j] = fmaf(x[r][e], pa[j], acc[r][j]);
+                        acc[r][8 + j] = fmaf(x[r][e], pb[j], acc[r][8 + j]);
+                    }
                 }
             }
         }
     }
-    // butterfly over the 32 lanes, then lanes 0..7 write one half2 each per row
+    // butterfly over the 32 lanes, fold the four warps, lanes 0..7 of warp 0..3 write the rows
 #pragma unroll
     for (int r = 0; r < LD_ROWS_PER_WARP; ++r) {
 #pragma unroll
@@ -126,28 +99,55 @@ lora_down_kernel(const __half* __restrict__ in, long long m, long long c, long l
             float v = acc[r][j];
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            acc[r][j] = v * scaling;
+            if (lane == 0) part[warp][r][j] = v;
         }
+    }
+    __syncthreads();
+    if (threadIdx.x < LD_ROWS * 8) {
+        const int r = threadIdx.x >> 3, jp = (threadIdx.x & 7) * 2;
         const long long gr = row0 + r;
-        if (gr < m && lane < 8) {
+        if (gr < m) {
             float a = 0.f, b = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if (lane == j) { a = acc[r][2 * j]; b = acc[r][2 * j + 1]; }
-            *reinterpret_cast<__half2*>(out + gr * 16 + 2 * lane) = __floats2half2_rn(a, b);
+            for (int w = 0; w < LD_WARPS; ++w) { a += part[w][r][jp]; b += part[w][r][jp + 1]; }
+            *reinterpret_cast<__half2*>(out + gr * 16 + jp) = __floats2half2_rn(a * scaling, b * scaling);
         }
     }
 }
 
+// Layout-agnostic variant (any strides, any alignment): one thread per output element.
+__global__ void __launch_bounds__(256)
+lora_down_generic_kernel(const __half* __restrict__ in, long long m, long long c, long long ld_in,
+                         const __half* __restrict__ p, long long p_stride_r, long long p_stride_c,
+                         float scaling, __half* __restrict__ out) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= m * 16) return;
+    const long long row = i / 16;
+    const int j = (int)(i % 16);
+    float acc = 0.f;
+    for (long long cc = 0; cc < c; ++cc)
+        acc = fmaf(__half2float(in[row * ld_in + cc]), __half2float(p[cc * p_stride_c + j * p_stride_r]),
+                   acc);
+    out[row * 16 + j] = __float2half_rn(acc * scaling);
+}
+
 cudaError_t launch_lora_down(const LoraDownArgs& a, cudaStream_t stream) {
     if (a.m <= 0) return cudaSuccess;
+    const bool aligned = (a.ld_in % 8 == 0) && (a.c % 8 == 0) &&
+                         ((reinterpret_cast<uintptr_t>(a.in) & 15) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(a.p) & 15) == 0);
     const unsigned blocks = (unsigned)((a.m + LD_ROWS - 1) / LD_ROWS);
-    const int vec_ok = (a.ld_in % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.in) & 15) == 0);
-    const int p_vec = ((reinterpret_cast<uintptr_t>(a.p) & 15) == 0) &&
-                      (a.p_stride_c != 1 || a.p_stride_r % 8 == 0);
-    lora_down_kernel<<<blocks, LD_THREADS, 0, stream>>>(a.in, a.m, a.c, a.ld_in, a.p, a.p_stride_r,
-                                                        a.p_stride_c, a.scaling, a.out, vec_ok,
-                                                        p_vec);
+    if (aligned && a.p_stride_c == 1 && a.p_stride_r == a.c) {
+        lora_down_kernel<true><<<blocks, LD_THREADS, 0, stream>>>(a.in, a.m, a.c, a.ld_in, a.p,
+                                                                   a.scaling, a.out);
+    } else if (aligned && a.p_stride_r == 1 && a.p_stride_c == 16) {
+        lora_down_kernel<false><<<blocks, LD_THREADS, 0, stream>>>(a.in, a.m, a.c, a.ld_in, a.p,
+                                                                    a.scaling, a.out);
+    } else {
+        const long long total = a.m * 16;
+        lora_down_generic_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+            a.in, a.m, a.c, a.ld_in, a.p, a.p_stride_r, a.p_stride_c, a.scaling, a.out);
+    }
     return cudaGetLastError();
 }
 
