@@ -23,85 +23,73 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 }
 
 // ------------------------------------------------------------------------------------ lora_down
-// A block of 4 warps owns LD_ROWS rows; each warp takes a quarter of the columns for all of them
-// (lane l owns 8 columns at a time), then the four partial results are added through shared
-// memory. P (at most a few hundred KB, shared by every block) is read straight from global memory
-// with 16-byte loads and lives in L1/L2.
-constexpr int LD_WARPS = 4;
-constexpr int LD_ROWS_PER_WARP = 4;   // rows whose sums one warp carries (= rows per block)
-constexpr int LD_ROWS = LD_ROWS_PER_WARP;
+// Tensor-core version (mma.sync m16n8k16, fp16 in / fp32 accumulate: the op is bound by reading
+// `in` once, the legacy warp-level MMA is ample). A block owns 16 rows; its LD_WARPS warps split
+// the columns, each walking 32 columns per step:
+//   lane (g = lane/4, t = lane%4) loads 8 contiguous halves in[g][c0 + 8t ..] and in[g+8][...]
+//   (one 16-byte load each) and the matching 8 halves of P for outputs j = g and j = 8 + g.
+// The contraction index may be visited in any order as long as A and B agree, so halves 0..3 of
+// those 8 feed the first k16 step (a0a1 | a4a5) and halves 4..7 the second: no shuffles, no
+// shared-memory staging. The warps' 16x16 partial tiles are added through shared memory.
+constexpr int LD_WARPS = 8;
+constexpr int LD_ROWS = 16;
 constexpr int LD_THREADS = LD_WARPS * 32;
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
 template <bool RANK_MAJOR>  // P is row-major [16, C] (true) or row-major [C, 16] (false)
 __global__ void __launch_bounds__(LD_THREADS)
 lora_down_kernel(const __half* __restrict__ in, long long m, long long c, long long ld_in,
                  const __half* __restrict__ p, float scaling, __half* __restrict__ out) {
-    __shared__ float part[LD_WARPS][LD_ROWS_PER_WARP][16];
+    __shared__ float part[LD_WARPS][16][17];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
     const long long row0 = (long long)blockIdx.x * LD_ROWS;
-    float acc[LD_ROWS_PER_WARP][16];
-#pragma unroll
-    for (int r = 0; r < LD_ROWS_PER_WARP; ++r)
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc[r][j] = 0.f;
+    const long long r_lo = row0 + g, r_hi = row0 + g + 8;
+    float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};  // outputs j 0..7, 8..15
 
-    // this warp's column range: a quarter of the columns, in multiples of 8 (c % 8 == 0 here)
-    const long long groups = c / 8;
-    const long long g_begin = groups * warp / LD_WARPS, g_end = groups * (warp + 1) / LD_WARPS;
-    for (long long gc = (g_begin + lane) * 8; gc < g_end * 8; gc += 256) {
-        float x[LD_ROWS_PER_WARP][8];
-#pragma unroll
-        for (int r = 0; r < LD_ROWS_PER_WARP; ++r) {
-            const long long gr = row0 + r;
-            if (gr < m) {
-                unpack8(__ldg(reinterpret_cast<const uint4*>(in + gr * ld_in + gc)), x[r]);
+    const long long chunks = (c + 31) / 32;   // c % 8 == 0 on this path
+    const long long ch_begin = chunks * warp / LD_WARPS, ch_end = chunks * (warp + 1) / LD_WARPS;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (long long ch = ch_begin; ch < ch_end; ++ch) {
+        const long long col = ch * 32 + t * 8;
+        const bool col_ok = col < c;
+        uint4 a_lo = zero, a_hi = zero, b_lo = zero, b_hi = zero;
+        if (col_ok) {
+            if (r_lo < m) a_lo = __ldg(reinterpret_cast<const uint4*>(in + r_lo * ld_in + col));
+            if (r_hi < m) a_hi = __ldg(reinterpret_cast<const uint4*>(in + r_hi * ld_in + col));
+            if (RANK_MAJOR) {
+                b_lo = __ldg(reinterpret_cast<const uint4*>(p + (long long)g * c + col));
+                b_hi = __ldg(reinterpret_cast<const uint4*>(p + (long long)(g + 8) * c + col));
             } else {
+                __half lo[8], hi[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) x[r][e] = 0.f;
-            }
-        }
-        if (RANK_MAJOR) {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                float pv[8];
-                unpack8(__ldg(reinterpret_cast<const uint4*>(p + (long long)j * c + gc)), pv);
-#pragma unroll
-                for (int r = 0; r < LD_ROWS_PER_WARP; ++r) {
-                    float a = acc[r][j];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) a = fmaf(x[r][e], pv[e], a);
-                    acc[r][j] = a;
+                for (int e = 0; e < 8; ++e) {
+                    lo[e] = __ldg(p + (col + e) * 16 + g);
+                    hi[e] = __ldg(p + (col + e) * 16 + g + 8);
                 }
-            }
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                float pa[8], pb[8];
-                const uint4* src = reinterpret_cast<const uint4*>(p + (gc + e) * 16);
-                unpack8(__ldg(src), pa);
-                unpack8(__ldg(src + 1), pb);
-#pragma unroll
-                for (int r = 0; r < LD_ROWS_PER_WARP; ++r) {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        acc[r][j] = fmaf(x[r][e], pa[j], acc[r][j]);
-                        acc[r][8 + j] = fmaf(x[r][e], pb[j], acc[r][8 + j]);
-                    }
-                }
+                b_lo = *reinterpret_cast<const uint4*>(lo);
+                b_hi = *reinterpret_cast<const uint4*>(hi);
             }
         }
+        // k16 step 0: halves 0,1 | 2,3 ; step 1: halves 4,5 | 6,7
+        mma16816(d0, a_lo.x, a_hi.x, a_lo.y, a_hi.y, b_lo.x, b_lo.y);
+        mma16816(d1, a_lo.x, a_hi.x, a_lo.y, a_hi.y, b_hi.x, b_hi.y);
+        mma16816(d0, a_lo.z, a_hi.z, a_lo.w, a_hi.w, b_lo.z, b_lo.w);
+        mma16816(d1, a_lo.z, a_hi.z, a_lo.w, a_hi.w, b_hi.z, b_hi.w);
     }
-    // butterfly over the 32 lanes, fold the four warps, lanes 0..7 of warp 0..3 write the rows
-#pragma unroll
-    for (int r = 0; r < LD_ROWS_PER_WARP; ++r) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            float v = acc[r][j];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0) part[warp][r][j] = v;
-        }
-    }
+    // accumulator layout: d[0],d[1] -> (row g, cols 2t, 2t+1); d[2],d[3] -> (row g+8, same cols)
+    part[warp][g][2 * t] = d0[0];         part[warp][g][2 * t + 1] = d0[1];
+    part[warp][g + 8][2 * t] = d0[2];     part[warp][g + 8][2 * t + 1] = d0[3];
+    part[warp][g][8 + 2 * t] = d1[0];     part[warp][g][8 + 2 * t + 1] = d1[1];
+    part[warp][g + 8][8 + 2 * t] = d1[2]; part[warp][g + 8][8 + 2 * t + 1] = d1[3];
     __syncthreads();
     if (threadIdx.x < LD_ROWS * 8) {
         const int r = threadIdx.x >> 3, jp = (threadIdx.x & 7) * 2;
@@ -239,8 +227,109 @@ lora_grad_kernel(const __half* __restrict__ z, long long m, long long c, long lo
     }
 }
 
+// Tensor-core version of lora_grad: D[j][c] = sum_m s[m][j] * z[m][c] with mma.sync m16n8k16.
+// The contraction runs over the slow (row) index of both operands, so 32-token chunks of z
+// ([32 x 128]) and s ([32 x 16]) are staged in shared memory with 16-byte loads and read back
+// transposed with ldmatrix.trans. 8 warps, each owning 16 of the block's 128 columns; chunk i+1 is
+// fetched into registers while chunk i is multiplied.
+constexpr int LGM_COLS = 128, LGM_CHUNK = 32, LGM_ROWS = 256, LGM_THREADS = 256;
+constexpr int LGM_ZP = LGM_COLS + 8;   // padded row pitches (halves): conflict-free ldmatrix
+constexpr int LGM_SP = 16 + 8;
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                                  uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__global__ void __launch_bounds__(LGM_THREADS)
+lora_grad_mma_kernel(const __half* __restrict__ z, long long m, long long c, long long ld_z,
+                     const __half* __restrict__ s, float* __restrict__ out, long long o_stride_r,
+                     long long o_stride_c) {
+    __shared__ __align__(16) __half zt[2][LGM_CHUNK][LGM_ZP];
+    __shared__ __align__(16) __half st[2][LGM_CHUNK][LGM_SP];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const long long c0 = (long long)blockIdx.x * LGM_COLS;
+    const long long m0 = (long long)blockIdx.y * LGM_ROWS;
+    const long long m_end = (m0 + LGM_ROWS < m) ? m0 + LGM_ROWS : m;
+    const int n_chunks = (int)((m_end - m0 + LGM_CHUNK - 1) / LGM_CHUNK);
+
+    // staging assignment: z chunk = 32 rows x 16 uint4 -> 2 per thread; s chunk = 32 rows x 2 uint4
+    const int zr = threadIdx.x >> 4, zc = (threadIdx.x & 15) * 8;   // rows zr and zr + 16
+    const int sr = threadIdx.x >> 1, sc = (threadIdx.x & 1) * 8;    // threads 0..63
+    uint4 zreg[2], sreg;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    auto fetch = [&](int chunk) {
+        const long long r0 = m0 + (long long)chunk * LGM_CHUNK;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const long long r = r0 + zr + 16 * h;
+            zreg[h] = (r < m_end && c0 + zc < c)
+                ? __ldg(reinterpret_cast<const uint4*>(z + r * ld_z + c0 + zc)) : zero;
+        }
+        if (threadIdx.x < 64) {
+            const long long r = r0 + sr;
+            sreg = r < m_end ? __ldg(reinterpret_cast<const uint4*>(s + r * 16 + sc)) : zero;
+        }
+    };
+    auto stash = [&](int buf) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+            *reinterpret_cast<uint4*>(&zt[buf][zr + 16 * h][zc]) = zreg[h];
+        if (threadIdx.x < 64) *reinterpret_cast<uint4*>(&st[buf][sr][sc]) = sreg;
+    };
+
+    float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};  // columns 16w+0..7, +8..15
+    fetch(0);
+    stash(0);
+    __syncthreads();
+    for (int ch = 0; ch < n_chunks; ++ch) {
+        const int buf = ch & 1;
+        if (ch + 1 < n_chunks) fetch(ch + 1);
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+            // A (16 j x 16 k) from st[k][j]: matrices (j0-7,k0-7), (j8-15,k0-7), (j0-7,k8-15), (j8-15,k8-15)
+            const int q = lane >> 3, i = lane & 7;
+            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+            ldmatrix_x4_trans((uint32_t)__cvta_generic_to_shared(
+                                  &st[buf][ks * 16 + (q >> 1) * 8 + i][(q & 1) * 8]),
+                              a0, a1, a2, a3);
+            // B (16 k x 8 n) x 2 n-tiles from zt[k][n]: (k0-7,n0), (k8-15,n0), (k0-7,n0+8), (k8-15,n0+8)
+            ldmatrix_x4_trans((uint32_t)__cvta_generic_to_shared(
+                                  &zt[buf][ks * 16 + (q & 1) * 8 + i][warp * 16 + (q >> 1) * 8]),
+                              b0, b1, b2, b3);
+            mma16816(d0, a0, a1, a2, a3, b0, b1);
+            mma16816(d1, a0, a1, a2, a3, b2, b3);
+        }
+        if (ch + 1 < n_chunks) stash(buf ^ 1);
+        __syncthreads();
+    }
+    // d[0],d[1] -> (j = g, columns 2t, 2t+1 of the n-tile); d[2],d[3] -> (j = g + 8, same columns)
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+        const float* d = nt == 0 ? d0 : d1;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const long long col = c0 + warp * 16 + nt * 8 + 2 * t + (e & 1);
+            const int j = g + (e >> 1) * 8;
+            if (col < c) atomicAdd(out + col * o_stride_c + j * o_stride_r, d[e]);
+        }
+    }
+}
+
 cudaError_t launch_lora_grad(const LoraGradArgs& a, cudaStream_t stream) {
     if (a.m <= 0 || a.c <= 0) return cudaSuccess;
+    const bool aligned = (a.ld_z % 8 == 0) && (a.c % 8 == 0) &&
+                         ((reinterpret_cast<uintptr_t>(a.z) & 15) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(a.s) & 15) == 0);
+    if (aligned) {
+        dim3 grid_mma((unsigned)((a.c + LGM_COLS - 1) / LGM_COLS),
+                      (unsigned)((a.m + LGM_ROWS - 1) / LGM_ROWS));
+        lora_grad_mma_kernel<<<grid_mma, LGM_THREADS, 0, stream>>>(a.z, a.m, a.c, a.ld_z, a.s, a.out,
+                                                                   a.o_stride_r, a.o_stride_c);
+        return cudaGetLastError();
+    }
     dim3 grid((unsigned)((a.c + LG_COLS - 1) / LG_COLS), (unsigned)((a.m + LG_ROWS - 1) / LG_ROWS));
     const int vec_ok = (a.ld_z % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.z) & 7) == 0);
     lora_grad_kernel<<<grid, LG_THREADS, 0, stream>>>(a.z, a.m, a.c, a.ld_z, a.s, a.out,
