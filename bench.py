@@ -186,54 +186,76 @@ def make_activations(shapes, m, device, pinned=False, world=1):
 SCALING = LORA_ALPHA / RANK_LORA
 
 
+GROUPS = (("q", "k", "v"), ("o",), ("gate", "up"), ("down",))   # projections that share an input
+
+
 def step_functional(layer, acts):
     """Forward then backward over the seven projections through the functional kernel wrappers
-    (no autograd graph, no host copies): the device-resident timing path. Returns the outputs."""
+    (no autograd graph, no host copies): the device-resident timing path. q/k/v and gate/up share
+    their input, so each group is one launch forward and one launch (summed dX) backward, as the
+    model's own data flow has it. Returns the outputs."""
+    from hackaton_b200.group import linear_backward_dx_group, linear_forward_group
     from hackaton_b200.lora import lora_down, lora_grad
-    from hackaton_b200.nf4 import linear_backward_dx, linear_forward
 
     outs, saved = [], {}
-    for name in ORDER:
-        e, x = layer[name], acts[INPUT_OF[name]]
-        if "A" in e:
-            xa = lora_down(x, e["A"], True, SCALING)
-            saved[name] = xa
-            outs.append(linear_forward(x, e["packed"], None, e["state"], xa=xa, lora_b=e["B"]))
-        else:
-            outs.append(linear_forward(x, e["packed"], None, e["state"]))
-    for name in reversed(ORDER):
-        e, dy, x = layer[name], acts["dy_" + name], acts[INPUT_OF[name]]
-        if "A" in e:
-            u = lora_down(dy, e["B"], False, SCALING)
-            outs.append(linear_backward_dx(dy, e["packed"], e["state"], u=u, lora_a=e["A"]))
-            outs.append(lora_grad(x, u, True))
-            outs.append(lora_grad(dy, saved[name], False))
-        else:
-            outs.append(linear_backward_dx(dy, e["packed"], e["state"]))
+    for group in GROUPS:
+        x = acts[INPUT_OF[group[0]]]
+        weights = [(layer[n]["packed"], layer[n]["state"]) for n in group]
+        xas, lbs = [], []
+        for n in group:
+            e = layer[n]
+            if "A" in e:
+                saved[n] = lora_down(x, e["A"], True, SCALING)
+                xas.append(saved[n])
+                lbs.append(e["B"])
+            else:
+                xas.append(None)
+                lbs.append(None)
+        outs += linear_forward_group(x, weights, None, xas, lbs)
+    for group in reversed(GROUPS):
+        x = acts[INPUT_OF[group[0]]]
+        weights = [(layer[n]["packed"], layer[n]["state"]) for n in group]
+        dys = [acts["dy_" + n] for n in group]
+        us, las = [], []
+        for n, dy in zip(group, dys):
+            e = layer[n]
+            if "A" in e:
+                us.append(lora_down(dy, e["B"], False, SCALING))
+                las.append(e["A"])
+            else:
+                us.append(None)
+                las.append(None)
+        outs.append(linear_backward_dx_group(dys, weights, us, las))
+        for n, dy, u in zip(group, dys, us):
+            if u is not None:
+                outs.append(lora_grad(x, u, True))
+                outs.append(lora_grad(dy, saved[n], False))
     return outs
 
 
-KERNELS_PER_STEP = 7 + 2 + 7 + 2 + 4  # GEMMs fwd, lora_down fwd, GEMMs bwd, lora_down bwd, lora_grad
+# kernels of this library per step: 4 GEMM launches + 3 split-K reductions (q/k/v outputs) + 1 (o)
+# + 1 (down) forward; 4 GEMM launches + 3 reductions backward; 4 lora_down; 4 lora_grad
+KERNELS_PER_STEP = 4 + 5 + 4 + 3 + 4 + 4
 
 
 def step_autograd(layer, acts_dev):
     """The same step through the public autograd API (what a user of the package calls)."""
-    from hackaton_b200 import nf4_linear, nf4_lora_linear
+    from hackaton_b200 import Projection, nf4_linear_group
 
     metric = None
     leaves = {}
     for key in ("x_attn", "x_o", "x_mlp", "x_down"):
         leaves[key] = acts_dev[key].detach().requires_grad_()
-    params = []
-    for name in ORDER:
-        e, x = layer[name], leaves[INPUT_OF[name]]
-        if "A" in e:
-            a, b = e["A"].detach().requires_grad_(), e["B"].detach().requires_grad_()
-            params += [a, b]
-            y = nf4_lora_linear(x, e["packed"], None, e["state"], a, b, SCALING)
-        else:
-            y = nf4_linear(x, e["packed"], None, e["state"])
-        y.backward(acts_dev["dy_" + name])
+    for group in GROUPS:
+        x = leaves[INPUT_OF[group[0]]]
+        projs = []
+        for n in group:
+            e = layer[n]
+            a = e["A"].detach().requires_grad_() if "A" in e else None
+            b = e["B"].detach().requires_grad_() if "B" in e else None
+            projs.append(Projection(e["packed"], e["state"], None, a, b, SCALING))
+        ys = nf4_linear_group(x, projs)
+        torch.autograd.backward(list(ys), [acts_dev["dy_" + n] for n in group])
     for leaf in leaves.values():
         s = leaf.grad.float().mean()
         metric = s if metric is None else metric + s

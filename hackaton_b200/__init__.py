@@ -4,12 +4,14 @@ mergentlegen/hackaton as hand-written sm_100a CUDA kernels behind the reference'
     from hackaton_b200 import dequantize_nf4, nf4_linear, nf4_lora_linear, apply
 """
 
+from .group import Projection, nf4_linear_group
 from .lora import NF4LoRALinear, nf4_lora_linear
 from .nf4 import NF4Linear, can_dequantize, dequantize_nf4, nf4_linear
 from .patches import apply, patch_nf4_matmul, patch_peft_lora
 from .quantize import QuantState, quantize_nf4
 
 __all__ = [
-    "NF4Linear", "NF4LoRALinear", "QuantState", "apply", "can_dequantize", "dequantize_nf4",
-    "nf4_linear", "nf4_lora_linear", "patch_nf4_matmul", "patch_peft_lora", "quantize_nf4",
+    "NF4Linear", "NF4LoRALinear", "Projection", "QuantState", "apply", "can_dequantize",
+    "dequantize_nf4", "nf4_linear", "nf4_linear_group", "nf4_lora_linear", "patch_nf4_matmul",
+    "patch_peft_lora", "quantize_nf4",
 ]

@@ -16,7 +16,8 @@ LIB_PATH = Path(__file__).resolve().parent / "libnf4b200.so"
 EXPORTS = (
     "nf4b200_query", "nf4b200_last_error", "nf4b200_device_status", "nf4b200_dequant",
     "nf4b200_linear_fwd", "nf4b200_linear_bwd_dx", "nf4b200_lora_down", "nf4b200_lora_grad",
-    "nf4b200_workspace_bytes", "nf4b200_linear_fwd_static",
+    "nf4b200_workspace_bytes", "nf4b200_linear_fwd_static", "nf4b200_linear_fwd_group",
+    "nf4b200_linear_bwd_dx_group", "nf4b200_workspace_bytes_group",
 )
 
 F16, BF16, F32 = 0, 1, 2
@@ -76,8 +77,16 @@ def lib() -> ctypes.CDLL:
                                          c_int64, c_float, c_void_p, c_void_p]
     handle.nf4b200_lora_grad.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                          c_int64, c_int64, c_void_p]
+    pw, pv, pi64 = POINTER(POINTER(Weight)), POINTER(c_void_p), POINTER(c_int64)
+    handle.nf4b200_linear_fwd_group.argtypes = [c_int, pw, c_void_p, c_int64, c_int64, pv, pv, pv,
+                                                pv, pi64, c_void_p, c_size_t, c_void_p]
+    handle.nf4b200_linear_bwd_dx_group.argtypes = [c_int, pw, pv, c_int64, pi64, pv, pv, c_void_p,
+                                                   c_int64, c_void_p, c_size_t, c_void_p]
+    handle.nf4b200_workspace_bytes_group.argtypes = [c_int, pi64, c_int64, c_int64, c_int]
+    handle.nf4b200_workspace_bytes_group.restype = c_int64
     for name in EXPORTS:
-        if name not in ("nf4b200_last_error", "nf4b200_workspace_bytes"):
+        if name not in ("nf4b200_last_error", "nf4b200_workspace_bytes",
+                        "nf4b200_workspace_bytes_group"):
             getattr(handle, name).restype = c_int
     handle.nf4b200_workspace_bytes.restype = c_int64
     _lib = handle

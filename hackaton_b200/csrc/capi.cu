@@ -292,6 +292,109 @@ int nf4b200_linear_bwd_dx(const nf4b200_weight* w, const void* dy, int64_t m, in
     return NF4B200_OK;
 }
 
+int nf4b200_linear_fwd_group(int count, const nf4b200_weight* const* w, const void* x, int64_t m,
+                             int64_t ldx, const void* const* bias, const void* const* xa,
+                             const void* const* lora_b, void* const* y, const int64_t* ldy,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (count < 1 || count > nf4::GEMM_MAX_GROUP)
+        return fail(NF4B200_EINVAL, "group of %d weights (1..%d allowed)", count, nf4::GEMM_MAX_GROUP);
+    if (!w || !y || !ldy) return fail(NF4B200_EINVAL, "fwd_group: NULL array");
+    nf4::GemmGroupArgs ga;
+    ga.count = count;
+    for (int i = 0; i < count; ++i) {
+        if ((rc = check_weight(w[i], true)) != NF4B200_OK) return rc;
+        if (w[i]->n_cols != w[0]->n_cols)
+            return fail(NF4B200_EINVAL, "fwd_group: weights must have the same number of columns");
+        if (!y[i]) return fail(NF4B200_EINVAL, "fwd_group: y[%d] is NULL", i);
+        if (ldy[i] < w[i]->n_rows)
+            return fail(NF4B200_EINVAL, "fwd_group: y[%d] row stride %lld < %lld columns", i,
+                        (long long)ldy[i], (long long)w[i]->n_rows);
+        const void* xa_i = xa ? xa[i] : nullptr;
+        const void* lb_i = lora_b ? lora_b[i] : nullptr;
+        if ((xa_i == nullptr) != (lb_i == nullptr))
+            return fail(NF4B200_EINVAL, "fwd_group: xa[%d] and lora_b[%d] must both be given or NULL", i, i);
+        if (xa_i && (!aligned16(xa_i) || !aligned16(lb_i)))
+            return fail(NF4B200_EINVAL, "fwd_group: xa / lora_b are not 16-byte aligned");
+        nf4::GemmArgs& g = ga.item[i];
+        fill_gemm(g, w[i], d->sms);
+        g.act = static_cast<const __half*>(x); g.m = m; g.ld_act = ldx;
+        g.out = static_cast<__half*>(y[i]); g.ld_out = ldy[i];
+        g.bias = static_cast<const __half*>(bias ? bias[i] : nullptr);
+        g.ext_a = static_cast<const __half*>(xa_i);
+        g.ext_b = static_cast<const __half*>(lb_i);
+        g.trans_w = false;
+        if ((rc = set_workspace(g, workspace, workspace_bytes)) != NF4B200_OK) return rc;
+    }
+    if ((rc = check_act("x", x, m, ldx, w[0]->n_cols)) != NF4B200_OK) return rc;
+    const char* why = "";
+    cudaError_t e = nf4::launch_gemm_group(ga, static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess)
+        return fail(NF4B200_ECUDA, "linear_fwd_group: %s: %s", why, cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_linear_bwd_dx_group(int count, const nf4b200_weight* const* w, const void* const* dy,
+                                int64_t m, const int64_t* lddy, const void* const* u,
+                                const void* const* lora_a, void* dx, int64_t lddx, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (count < 1 || count > nf4::GEMM_MAX_GROUP)
+        return fail(NF4B200_EINVAL, "group of %d weights (1..%d allowed)", count, nf4::GEMM_MAX_GROUP);
+    if (!w || !dy || !lddy || !dx) return fail(NF4B200_EINVAL, "bwd_group: NULL argument");
+    nf4::GemmGroupArgs ga;
+    ga.count = count;
+    for (int i = 0; i < count; ++i) {
+        if ((rc = check_weight(w[i], true)) != NF4B200_OK) return rc;
+        if (w[i]->n_cols != w[0]->n_cols)
+            return fail(NF4B200_EINVAL, "bwd_group: weights must have the same number of columns");
+        if ((rc = check_act("dy", dy[i], m, lddy[i], w[i]->n_rows)) != NF4B200_OK) return rc;
+        const void* u_i = u ? u[i] : nullptr;
+        const void* la_i = lora_a ? lora_a[i] : nullptr;
+        if ((u_i == nullptr) != (la_i == nullptr))
+            return fail(NF4B200_EINVAL, "bwd_group: u[%d] and lora_a[%d] must both be given or NULL", i, i);
+        if (u_i && (!aligned16(u_i) || !aligned16(la_i)))
+            return fail(NF4B200_EINVAL, "bwd_group: u / lora_a are not 16-byte aligned");
+        nf4::GemmArgs& g = ga.item[i];
+        fill_gemm(g, w[i], d->sms);
+        g.act = static_cast<const __half*>(dy[i]); g.m = m; g.ld_act = lddy[i];
+        g.out = static_cast<__half*>(dx); g.ld_out = lddx;
+        g.bias = nullptr;
+        g.ext_a = static_cast<const __half*>(u_i);
+        g.ext_b = static_cast<const __half*>(la_i);
+        g.trans_w = true;
+        if ((rc = set_workspace(g, workspace, workspace_bytes)) != NF4B200_OK) return rc;
+    }
+    if (lddx < w[0]->n_cols)
+        return fail(NF4B200_EINVAL, "bwd_group: dx row stride %lld < %lld columns", (long long)lddx,
+                    (long long)w[0]->n_cols);
+    const char* why = "";
+    cudaError_t e = nf4::launch_gemm_group(ga, static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess)
+        return fail(NF4B200_ECUDA, "linear_bwd_dx_group: %s: %s", why, cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int64_t nf4b200_workspace_bytes_group(int count, const int64_t* n_rows, int64_t n_cols, int64_t m,
+                                      int backward) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (count < 1 || count > nf4::GEMM_MAX_GROUP || !n_rows || n_cols <= 0 || m <= 0)
+        return fail(NF4B200_EINVAL, "workspace_bytes_group: bad arguments");
+    long long rows[nf4::GEMM_MAX_GROUP];
+    for (int i = 0; i < count; ++i) {
+        if (n_rows[i] <= 0) return fail(NF4B200_EINVAL, "workspace_bytes_group: bad shape");
+        rows[i] = n_rows[i];
+    }
+    const nf4::GemmPlan pl = nf4::plan_gemm_group(m, rows, count, n_cols, backward != 0, d->sms);
+    return (int64_t)pl.ws_bytes;
+}
+
 int64_t nf4b200_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int backward) {
     DeviceInfo* d = nullptr;
     int rc = require_sm100(&d);

@@ -66,34 +66,56 @@ constexpr int MMA_WARP = PRODUCER_WARPS + 1;
 constexpr int BK = 64;   // k-block depth = one quantisation block
 constexpr int BN = 256;  // output-tile width
 
-struct GemmParams {
+// One weight of a group. Forward groups share the activations and stack their outputs along N
+// (one output buffer each); backward groups share the output and stack along the contraction
+// (one dY each). `first` is the group-wide index of the problem's first n-tile (forward) or
+// first k-block (backward).
+struct GemmProblem {
     const void* absmax;
     const float* code2;
     const float* absmax2;
     const float* offset;
     const float* code16;
-    const __half* bias;
-    const __half* ext_a;
-    const __half* ext_b;
-    __half* out;
-    int* status;
-    float* ws;               // split-K: fp32 planes [slice][m][ldp]
+    const __half* bias;   // forward only
+    const __half* ext_a;  // rank-16 left factor [M, 16] (xa / u) or null
+    const __half* ext_b;  // forward: lora_b [n_w, 16]; backward: lora_a [16, k_w]
+    __half* out;          // forward: this problem's output; backward: only problem 0's is used
+    float* ws;            // split-K planes [slice][m][ldp] (same remark)
     long long ld_out, ldp;
-    int m, n_w, k_w;
+    int n_w;              // rows of this weight
+    int first;
     int nested, nested_shift, nested_blocksize;
+    int pad;
+};
+
+constexpr int MAXP = GEMM_MAX_GROUP;
+
+struct GemmParams {
+    GemmProblem prob[MAXP];
+    int* status;
+    int n_prob;
+    int n_ext;               // backward: problems that carry a rank-16 extension
+    int m, k_w;              // token rows; columns of every weight of the group
+    int nkb_total;           // k-blocks of the whole contraction
     int m_tiles, n_tiles, splits, kb_per_split;
     int debug;               // bit 0: producers skip the decode, bit 1: phase trace (tuning only)
 };
 
-template <int CG, int NACC, int STAGES>
+struct GemmMaps {
+    CUtensorMap act[MAXP];    // forward: only [0]; backward: one dY per problem
+    CUtensorMap codes[MAXP];
+};
+
+template <int CG, int NACC, int STAGES, int TABLES_>
 struct SmemLayout {
     static constexpr int NB = BN / CG;                 // weight-tile columns decoded by one CTA
     static constexpr int A_BYTES = NACC * 128 * BK * 2;
     static constexpr int W_BYTES = NB * BK * 2;
     static constexpr int C_BYTES = NB * BK / 2;
     static constexpr int STAGE_BYTES = A_BYTES + W_BYTES + C_BYTES;
+    static constexpr int TABLES = TABLES_;  // second-level tables kept in shared memory
     static constexpr int TABLE2_OFF = STAGES * STAGE_BYTES;
-    static constexpr int BAR_OFF = TABLE2_OFF + 1024;
+    static constexpr int BAR_OFF = TABLE2_OFF + 1024 * TABLES;
     static constexpr int TOTAL = BAR_OFF + 256;
     static constexpr int DYNAMIC_BYTES = TOTAL + 1024;  // slack for 1024-byte alignment
     static constexpr int WARPS_PER_W_SLOT = W_BYTES / 4096;  // 4 KB epilogue staging per warp
@@ -152,32 +174,57 @@ __device__ unsigned long long g_trace2[2 * TRACE2_EVENTS * TRACE2_ITERS];
 
 // One work unit of the persistent loop.
 struct Unit {
-    int m0, n0;         // tile origin (token row, output column)
-    int kb_begin, nkb;  // slice of k-blocks
-    int n_iter;         // nkb (+1 when this unit also runs the K extension)
+    int m0, n0;         // tile origin (token row, output column inside the problem's output)
+    int kb_begin, nkb;  // slice of (group-wide) k-blocks
+    int n_iter;         // nkb + the K-extension steps this unit also runs
     int slice;
+    int prob;           // forward: the problem this tile belongs to; backward: 0
 };
 
-__device__ __forceinline__ Unit make_unit(int u, const GemmParams& p, int rows_per_tile,
-                                          int nkb_total) {
+// Problem that owns group-wide index idx (n-tile for forward, k-block for backward).
+__device__ __forceinline__ int find_problem(const GemmParams& p, int idx) {
+    if (p.n_prob == 1) return 0;
+    int r = 0;
+#pragma unroll
+    for (int i = 1; i < MAXP; ++i)
+        if (i < p.n_prob && idx >= p.prob[i].first) r = i;
+    return r;
+}
+
+template <bool TRANS_W>
+__device__ __forceinline__ Unit make_unit(int u, const GemmParams& p, int rows_per_tile) {
     Unit w;
     const int tile = u / p.splits;
     w.slice = u % p.splits;
     const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
     w.m0 = mt * rows_per_tile;
-    w.n0 = nt * BN;
+    w.prob = TRANS_W ? 0 : find_problem(p, nt);
+    w.n0 = (nt - (TRANS_W ? 0 : p.prob[w.prob].first)) * BN;
     w.kb_begin = w.slice * p.kb_per_split;
-    const int kb_end = min(w.kb_begin + p.kb_per_split, nkb_total);
+    const int kb_end = min(w.kb_begin + p.kb_per_split, p.nkb_total);
     w.nkb = kb_end - w.kb_begin;
-    w.n_iter = w.nkb + ((p.ext_a != nullptr && w.slice == 0) ? 1 : 0);
+    int ext = 0;
+    if (w.slice == 0) ext = TRANS_W ? p.n_ext : (p.prob[w.prob].ext_a != nullptr ? 1 : 0);
+    w.n_iter = w.nkb + ext;
     return w;
 }
 
-template <int CG, int NACC, bool TRANS_W, int STAGES, int DW>
+// Backward: the e-th problem (in group order) that carries an extension.
+__device__ __forceinline__ int ext_problem(const GemmParams& p, int e) {
+    int seen = 0, r = 0;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i)
+        if (i < p.n_prob && p.prob[i].ext_a != nullptr) {
+            if (seen == e) r = i;
+            ++seen;
+        }
+    return r;
+}
+
+template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
-                const __grid_constant__ CUtensorMap tm_codes, const GemmParams p) {
-    using L = SmemLayout<CG, NACC, STAGES>;
+nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmParams p) {
+    using L = SmemLayout<CG, NACC, STAGES, TABLES>;
     constexpr int NB = L::NB;
     // DW of the 16 producer warps decode (all 16 drain the accumulators); each decoding thread
     // expands WORDS 32-bit code words (8 weights each) per k-block
@@ -211,8 +258,6 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
     const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;  // 0 = leader of the pair
     const int pair = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int n_pairs = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
-    const int kc = TRANS_W ? p.n_w : p.k_w;  // contraction length
-    const int nkb_total = (kc + BK - 1) / BK;
     const int total_units = p.m_tiles * p.n_tiles * p.splits;
     const int blocks_per_row = p.k_w >> 6;
 
@@ -228,8 +273,8 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
         fence_barrier_init();
     }
     if (warp == TMA_WARP && lane == 0) {
-        tma_prefetch_desc(&tm_act);
-        tma_prefetch_desc(&tm_codes);
+        tma_prefetch_desc(&maps.act[0]);
+        tma_prefetch_desc(&maps.codes[0]);
     }
     if (warp == MMA_WARP) {
         if (CG == 2) {
@@ -240,7 +285,10 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
             tmem_relinquish();
         }
     }
-    if (p.nested && threadIdx.x < 256) table2[threadIdx.x] = p.code2[threadIdx.x];
+    if (threadIdx.x < 256) {
+        for (int i = 0; i < L::TABLES && i < p.n_prob; ++i)
+            if (p.prob[i].nested) table2[i * 256 + threadIdx.x] = p.prob[i].code2[threadIdx.x];
+    }
     tc_fence_before_sync();
     __syncthreads();
     if (CG == 2) cluster_sync_all();  // the peer's barriers and TMEM exist before anyone uses them
@@ -260,7 +308,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
             uint32_t g = 0;  // ring position, running across units
             uint32_t unit_iter2 = 0;
             for (int u = pair; u < total_units && !fail; u += n_pairs, ++unit_iter2) {
-                const Unit w = make_unit(u, p, ROWS_PER_TILE, nkb_total);
+                const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
                 for (int it = 0; it < w.n_iter; ++it, ++g) {
                     const int s = (int)(g % STAGES);
                     const uint32_t ph = (g / STAGES) & 1u;
@@ -270,18 +318,20 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                     if (!free_slot) { fail = 1; break; }
                     NF4_TRACE2(0, it);
                     if (it < w.nkb) {
-                        const int kb = w.kb_begin + it;
+                        const int kbg = w.kb_begin + it;                 // group-wide k-block
+                        const int pi = TRANS_W ? find_problem(p, kbg) : w.prob;
+                        const int kb = TRANS_W ? kbg - p.prob[pi].first : kbg;
                         mbar_arrive_expect_tx(bar_full_tma(s), L::A_BYTES + L::C_BYTES);
 #pragma unroll
                         for (int a = 0; a < NACC; ++a)
-                            tma_load_2d(sa + a * (128 * BK * 2), &tm_act, kb * BK,
+                            tma_load_2d(sa + a * (128 * BK * 2), &maps.act[TRANS_W ? pi : 0], kb * BK,
                                         w.m0 + a * (128 * CG) + (int)rank * 128, bar_full_tma(s));
                         const uint32_t sc = sa + L::A_BYTES + L::W_BYTES;
                         const int nb0 = w.n0 + (int)rank * NB;
                         if (TRANS_W)
-                            tma_load_2d(sc, &tm_codes, nb0 / 2, kb * BK, bar_full_tma(s));
+                            tma_load_2d(sc, &maps.codes[pi], nb0 / 2, kb * BK, bar_full_tma(s));
                         else
-                            tma_load_2d(sc, &tm_codes, kb * (BK / 2), nb0, bar_full_tma(s));
+                            tma_load_2d(sc, &maps.codes[pi], kb * (BK / 2), nb0, bar_full_tma(s));
                     } else {
                         mbar_arrive(bar_full_tma(s));  // extension step: producers bring operands
                     }
@@ -296,7 +346,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
             uint32_t unit_iter = 0;
             long long wait_tma = 0, wait_w = 0;  // tuning: cycles the issuer spent on each barrier
             for (int u = pair; u < total_units && !fail; u += n_pairs, ++unit_iter) {
-                const Unit w = make_unit(u, p, ROWS_PER_TILE, nkb_total);
+                const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
                 // the accumulators of the previous unit must have been drained (in both CTAs)
                 if (!mbar_wait_cluster(bar_tmem_empty, (unit_iter & 1u) ^ 1u, abort_flag)) {
                     fail = 6;
@@ -375,15 +425,16 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
         // ------------------------------------------------------------------ decode producers
         const int pt = threadIdx.x;  // 0..511: WORDS code words (8 weights each) per k-block
         RegLut lut;
-        {
+        int lut_prob = -1;  // problem whose 16-entry table is currently held in registers
+        auto load_lut = [&](int pi) {
             uint16_t bits[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) bits[i] = __half_as_ushort(__float2half_rn(p.code16[i]));
+            for (int i = 0; i < 16; ++i)
+                bits[i] = __half_as_ushort(__float2half_rn(__ldg(p.prob[pi].code16 + i)));
             lut = make_reg_lut(bits);
-        }
-        const float offset = p.nested ? *p.offset : 0.f;
-        const uint8_t* absmax_u8 = static_cast<const uint8_t*>(p.absmax);
-        const float* absmax_f32 = static_cast<const float*>(p.absmax);
+            lut_prob = pi;
+        };
+        load_lut(0);
 
         // Piece geometry (a piece = the 4*WORDS code bytes of one thread).
         // Forward: the code tile is [NB rows][32 B], pieces in memory order.
@@ -430,50 +481,56 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
         constexpr int CHUNKS_PER_GRP = NACC * (BN / 32) / 4;
         const uint32_t staging = smem_base + (uint32_t)(warp / L::WARPS_PER_W_SLOT) * L::STAGE_BYTES +
                                  L::A_BYTES + (uint32_t)(warp % L::WARPS_PER_W_SLOT) * 4096u;
-        const int n_out = TRANS_W ? p.k_w : p.n_w;
         const bool split = p.splits > 1;
-        const bool vec_ok = (p.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 15) == 0);
 
         uint32_t g = 0;
         uint32_t unit_iter = 0;
         for (int u = pair; u < total_units; u += n_pairs, ++unit_iter) {
-            const Unit w = make_unit(u, p, ROWS_PER_TILE, nkb_total);
+            const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
             NF4_TRACE(0);
             const int nb0 = w.n0 + (int)rank * NB;  // first weight-tile column of this CTA
 
-            // First-level scale index of this thread's piece (32-bit: n_blocks < 2^31).
-            //   forward : block (nb0 + row) * bpr + kb          valid while nb0 + row < N_w
-            //   backward: block (kb*64 + row) * bpr + kw / 64   valid while kb*64 + row < N_w, kw < K_w
-            uint32_t blk, blk_step;
-            bool col_ok;
-            if (!TRANS_W) {
-                blk = (uint32_t)(nb0 + row) * (uint32_t)blocks_per_row + (uint32_t)w.kb_begin;
-                blk_step = 1u;
-                col_ok = nb0 + row < p.n_w;
-            } else {
-                const int kw = nb0 + klocal;
-                blk = (uint32_t)(w.kb_begin * BK + row) * (uint32_t)blocks_per_row + (uint32_t)(kw >> 6);
-                blk_step = (uint32_t)BK * (uint32_t)blocks_per_row;
-                col_ok = kw < p.k_w;
-            }
-            uint32_t raw_q = 0;   // u8 code (nested) or fp32 bits (flat) of the coming k-block
-            float raw_a2 = 0.f;   // its second-level scale
+            // First-level scale of this thread's piece in step `it` (32-bit indices: n_blocks < 2^31).
+            //   forward : block (nb0 + row) * bpr + kb           valid while nb0 + row < N_w
+            //   backward: block (kb*64 + row) * bpr + kw / 64    valid while kb*64 + row < N_w, kw < K_w
+            // with kb counted inside the problem that owns the step. The raw first-level entry (u8
+            // code or fp32 bits), the second-level scale and the offset are fetched one step ahead.
+            const int kw = nb0 + klocal;  // backward: first k_w column of this thread's piece
+            const uint32_t blk_base = TRANS_W
+                ? (uint32_t)row * (uint32_t)blocks_per_row + (uint32_t)(kw >> 6)
+                : (uint32_t)(nb0 + row) * (uint32_t)blocks_per_row;
+            const uint32_t blk_per_kb = (uint32_t)BK * (uint32_t)blocks_per_row;
+            uint32_t raw_q = 0;
+            float raw_a2 = 0.f, raw_off = 0.f;
+            int raw_prob = 0;
             bool raw_ok = false;
             auto fetch_scale = [&](int it) {
-                bool ok = col_ok;
-                if (TRANS_W) ok = ok && ((w.kb_begin + it) * BK + row < p.n_w);
+                const int kbg = w.kb_begin + it;
+                const int pi = TRANS_W ? find_problem(p, kbg) : w.prob;
+                const GemmProblem& pr = p.prob[pi];
+                const int kb = TRANS_W ? kbg - pr.first : kbg;
+                uint32_t blk;
+                bool ok;
+                if (!TRANS_W) {
+                    blk = blk_base + (uint32_t)kb;
+                    ok = nb0 + row < pr.n_w;
+                } else {
+                    blk = blk_base + (uint32_t)kb * blk_per_kb;
+                    ok = kw < p.k_w && kb * BK + row < pr.n_w;
+                }
                 raw_ok = ok;
+                raw_prob = pi;
                 if (ok) {
-                    if (p.nested) {
-                        raw_q = __ldg(absmax_u8 + blk);
-                        const uint32_t b2 = p.nested_shift >= 0
-                            ? (blk >> p.nested_shift) : (blk / (uint32_t)p.nested_blocksize);
-                        raw_a2 = __ldg(p.absmax2 + b2);
+                    if (pr.nested) {
+                        raw_q = __ldg(static_cast<const uint8_t*>(pr.absmax) + blk);
+                        const uint32_t b2 = pr.nested_shift >= 0
+                            ? (blk >> pr.nested_shift) : (blk / (uint32_t)pr.nested_blocksize);
+                        raw_a2 = __ldg(pr.absmax2 + b2);
+                        raw_off = __ldg(pr.offset);
                     } else {
-                        raw_q = __float_as_uint(__ldg(absmax_f32 + blk));
+                        raw_q = __float_as_uint(__ldg(static_cast<const float*>(pr.absmax) + blk));
                     }
                 }
-                blk += blk_step;
             };
             if (!fail && warp < DW) fetch_scale(0);
 
@@ -485,11 +542,13 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                     float sc;
                     if (!raw_ok)
                         sc = 0.f;  // rows / columns outside the weight contribute zeros
-                    else if (p.nested)
-                        sc = nested_scale(table2[raw_q], raw_a2, offset);
+                    else if (p.prob[raw_prob].nested)
+                        sc = nested_scale(table2[(L::TABLES > 1 ? raw_prob * 256 : 0) + raw_q], raw_a2,
+                                          raw_off);
                     else
                         sc = __uint_as_float(raw_q);
                     const __half2 scale2 = __float2half2_rn(sc);
+                    if (raw_prob != lut_prob) load_lut(raw_prob);
                     if (it + 1 < w.nkb) fetch_scale(it + 1);
                     if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 4; break; }
                     if (threadIdx.x == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(1, it); }
@@ -509,6 +568,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                 } else {
                     // K extension operands, unswizzled core-matrix layout (see the MMA branch).
                     if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 4; break; }
+                    const GemmProblem& pe = p.prob[TRANS_W ? ext_problem(p, it - w.nkb) : w.prob];
                     const uint32_t abase = smem_base + stage_off;
                     const uint32_t wbase = abase + L::A_BYTES;
                     const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -519,7 +579,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                         const long long gm = (long long)w.m0 + acc * (128 * CG) + (int)rank * 128 + r;
                         uint4 v = zero;
                         if (gm < p.m)
-                            v = __ldg(reinterpret_cast<const uint4*>(p.ext_a + gm * 16) + half);
+                            v = __ldg(reinterpret_cast<const uint4*>(pe.ext_a + gm * 16) + half);
                         sts128(abase + acc * (128 * BK * 2) + (r >> 3) * 256 + half * 128 +
                                    (r & 7) * 16, v);
                     }
@@ -528,19 +588,19 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                             const int r = c >> 1, half = c & 1;
                             const long long gn = (long long)nb0 + r;
                             uint4 v = zero;
-                            if (gn < p.n_w)
-                                v = __ldg(reinterpret_cast<const uint4*>(p.ext_b + gn * 16) + half);
+                            if (gn < pe.n_w)
+                                v = __ldg(reinterpret_cast<const uint4*>(pe.ext_b + gn * 16) + half);
                             sts128(wbase + (r >> 3) * 256 + half * 128 + (r & 7) * 16, v);
                         }
                     } else {
                         // lora_a [16, K_w]: chunk (r, gq) = 8 consecutive k_w of rank row r
                         for (int c = pt; c < 16 * (NB / 8); c += DECODE_THREADS) {
                             const int r = c / (NB / 8), gq = c % (NB / 8);
-                            const long long kw = (long long)nb0 + gq * 8;
+                            const long long kwc = (long long)nb0 + gq * 8;
                             uint4 v = zero;
-                            if (kw < p.k_w)
+                            if (kwc < p.k_w)
                                 v = __ldg(reinterpret_cast<const uint4*>(
-                                    p.ext_b + (long long)r * p.k_w + kw));
+                                    pe.ext_b + (long long)r * p.k_w + kwc));
                             sts128(wbase + (r >> 3) * (NB * 16) + gq * 128 + (r & 7) * 16, v);
                         }
                     }
@@ -561,6 +621,9 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                 if (!mbar_wait(bar_tmem_full, unit_iter & 1u, abort_flag)) fail = 5;
             }
             NF4_TRACE(2);
+            const GemmProblem& po = p.prob[w.prob];  // backward: problem 0 carries the output
+            const int n_out = TRANS_W ? p.k_w : po.n_w;
+            const bool vec_ok = (po.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(po.out) & 15) == 0);
             if (!fail) {
                 tc_fence_after_sync();
                 const int lrow = lane;  // row of this lane inside its quadrant
@@ -587,13 +650,13 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                             tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN +
                                               (ch0 + h) * 32, r);
                             tmem_ld_wait();
-                            if (!TRANS_W && p.bias != nullptr) {
+                            if (!TRANS_W && po.bias != nullptr) {
                                 const int cb = w.n0 + (ch0 + h) * 32;
 #pragma unroll
                                 for (int e = 0; e < 32; ++e)
                                     if (cb + e < n_out)
                                         r[e] = __float_as_uint(__uint_as_float(r[e]) +
-                                                               __half2float(p.bias[cb + e]));
+                                                               __half2float(po.bias[cb + e]));
                             }
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
@@ -616,7 +679,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                             const long long grow = grow0 + rr;
                             const int colg = w.n0 + ch0 * 32 + rd_chunk * 8;
                             if (grow < p.m && colg < n_out && !(p.debug & 64)) {
-                                __half* dst = p.out + grow * p.ld_out + colg;
+                                __half* dst = po.out + grow * po.ld_out + colg;
                                 if (vec_ok && colg + 8 <= n_out) {
                                     *reinterpret_cast<uint4*>(dst) = v;
                                 } else {
@@ -632,7 +695,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                 } else {
                     // fp32 partial sums of this slice: one [32 rows x 32 cols] box per chunk into
                     // the slice's row-major plane
-                    float* plane = p.ws + (size_t)w.slice * ((size_t)p.m * (size_t)p.ldp);
+                    float* plane = po.ws + (size_t)w.slice * ((size_t)p.m * (size_t)po.ldp);
 #pragma unroll 1
                     for (int t = grp * CHUNKS_PER_GRP; t < (grp + 1) * CHUNKS_PER_GRP; ++t) {
                         const int acc = t / (BN / 32), ch = t % (BN / 32);
@@ -654,7 +717,7 @@ nf4_gemm_kernel(const __grid_constant__ CUtensorMap tm_act,
                             const long long grow = grow0 + rr;
                             const int colg = w.n0 + ch * 32 + rd_chunk * 4;
                             if (grow < p.m && colg < n_out) {
-                                float* dst = plane + grow * p.ldp + colg;  // ldp % 4 == 0
+                                float* dst = plane + grow * po.ldp + colg;  // ldp % 4 == 0
                                 if (colg + 4 <= n_out) {
                                     __stcg(reinterpret_cast<uint4*>(dst), v);
                                 } else {
@@ -797,12 +860,13 @@ static int debug_flags() {
 }
 
 // Tiling and split-K plan shared by the launcher and the workspace-size query.
-GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int sm_count) {
+GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long k_w, bool trans_w,
+                         int sm_count) {
     GemmPlan pl;
     if (m <= 128)      { pl.cg = 1; pl.nacc = 1; }
     else if (m <= 256) { pl.cg = 2; pl.nacc = 1; }
     else               { pl.cg = 2; pl.nacc = 2; }
-    if ((debug_flags() & 16) && m > 128) { pl.cg = 1; pl.nacc = 2; }  // tuning: single-CTA tiles
+    if ((debug_flags() & 16) && m > 128 && count == 1) { pl.cg = 1; pl.nacc = 2; }  // tuning
     int force_splits = 0;
     if (const char* e = std::getenv("NF4B200_PLAN")) {  // tuning: "nacc,splits" for pair tiles
         int a = 0, b = 0;
@@ -812,11 +876,27 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
         }
     }
     const int rows = 128 * pl.cg * pl.nacc;
-    const long long n_out = trans_w ? k_w : n_w;
-    const long long kc = trans_w ? n_w : k_w;
     pl.m_tiles = (int)((m + rows - 1) / rows);
-    pl.n_tiles = (int)((n_out + BN - 1) / BN);
-    const int nkb = (int)((kc + BK - 1) / BK);
+    int n_tiles = 0, nkb = 0;
+    size_t ws_floats = 0;
+    for (int i = 0; i < count; ++i) {
+        if (trans_w) {
+            pl.first[i] = nkb;                          // first k-block of problem i
+            nkb += (int)((n_w[i] + BK - 1) / BK);
+        } else {
+            pl.first[i] = n_tiles;                      // first n-tile of problem i
+            n_tiles += (int)((n_w[i] + BN - 1) / BN);
+            pl.ldp[i] = (n_w[i] + 3) / 4 * 4;
+        }
+    }
+    if (trans_w) {
+        n_tiles = (int)((k_w + BN - 1) / BN);
+        pl.ldp[0] = (k_w + 3) / 4 * 4;
+    } else {
+        nkb = (int)((k_w + BK - 1) / BK);
+    }
+    pl.n_tiles = n_tiles;
+    pl.nkb = nkb;
     const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
     const int slots = sm_count / pl.cg;  // units that run at the same time
     int splits = 1;
@@ -830,62 +910,91 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
     if (force_splits > 0) splits = force_splits < nkb ? force_splits : nkb;
     pl.kb_per_split = (nkb + splits - 1) / splits;
     pl.splits = (nkb + pl.kb_per_split - 1) / pl.kb_per_split;  // no empty slice
-    pl.ldp = (n_out + 3) / 4 * 4;
-    pl.ws_bytes = pl.splits > 1 ? (size_t)pl.splits * (size_t)m * (size_t)pl.ldp * sizeof(float) : 0;
+    for (int i = 0; i < (trans_w ? 1 : count); ++i) {
+        pl.ws_off[i] = ws_floats;
+        if (pl.splits > 1) ws_floats += (size_t)pl.splits * (size_t)m * (size_t)pl.ldp[i];
+    }
+    pl.ws_bytes = ws_floats * sizeof(float);
     return pl;
 }
 
-template <int CG, int NACC, bool TRANS_W, int STAGES, int DW>
-static cudaError_t launch_cfg(const GemmArgs& a, const GemmPlan& pl, cudaStream_t stream,
+GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int sm_count) {
+    return plan_gemm_group(m, &n_w, 1, k_w, trans_w, sm_count);
+}
+
+template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES>
+static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaStream_t stream,
                               const char** why) {
-    using L = SmemLayout<CG, NACC, STAGES>;
-    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW>;
+    using L = SmemLayout<CG, NACC, STAGES, TABLES>;
+    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW, TABLES>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::DYNAMIC_BYTES);
     if (e != cudaSuccess) { *why = "cudaFuncSetAttribute(shared memory)"; return e; }
 
-    const long long kc = TRANS_W ? a.n_w : a.k_w;
-    const long long n_out = TRANS_W ? a.k_w : a.n_w;
-    CUtensorMap tm_act, tm_codes;
-    if (!make_map_2d(&tm_act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.act, (uint64_t)kc, (uint64_t)a.m,
-                     (uint64_t)a.ld_act * 2, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B)) {
-        *why = "cuTensorMapEncodeTiled(activations)";
-        return cudaErrorInvalidValue;
-    }
-    const bool ok = TRANS_W
-        ? make_map_2d(&tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.codes, (uint64_t)a.k_w / 2,
-                      (uint64_t)a.n_w, (uint64_t)a.k_w / 2, L::NB / 2, BK,
-                      CG == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)
-        : make_map_2d(&tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.codes, (uint64_t)a.k_w / 2,
-                      (uint64_t)a.n_w, (uint64_t)a.k_w / 2, BK / 2, L::NB, CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (!ok) { *why = "cuTensorMapEncodeTiled(codes)"; return cudaErrorInvalidValue; }
-
+    const GemmArgs& a0 = ga.item[0];
+    const long long m = a0.m, k_w = a0.k_w;
+    GemmMaps maps;
     GemmParams p;
-    p.absmax = a.absmax; p.code2 = a.code2; p.absmax2 = a.absmax2; p.offset = a.offset;
-    p.code16 = a.code16; p.bias = a.bias; p.ext_a = a.ext_a; p.ext_b = a.ext_b; p.out = a.out;
-    p.status = device_status_word();
-    p.ld_out = a.ld_out; p.m = (int)a.m; p.n_w = (int)a.n_w; p.k_w = (int)a.k_w;
-    p.nested = a.nested; p.nested_blocksize = a.nested_blocksize;
-    p.nested_shift = -1;
-    if (a.nested_blocksize > 0 && (a.nested_blocksize & (a.nested_blocksize - 1)) == 0) {
-        int s = 0;
-        while ((1 << s) < a.nested_blocksize) ++s;
-        p.nested_shift = s;
+    p.n_prob = ga.count;
+    p.n_ext = 0;
+    for (int i = 0; i < ga.count; ++i) {
+        const GemmArgs& a = ga.item[i];
+        if (TRANS_W || i == 0) {
+            const long long kc = TRANS_W ? a.n_w : k_w;
+            if (!make_map_2d(&maps.act[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.act, (uint64_t)kc,
+                             (uint64_t)m, (uint64_t)a.ld_act * 2, BK, 128,
+                             CU_TENSOR_MAP_SWIZZLE_128B)) {
+                *why = "cuTensorMapEncodeTiled(activations)";
+                return cudaErrorInvalidValue;
+            }
+        }
+        const bool ok = TRANS_W
+            ? make_map_2d(&maps.codes[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, a.codes, (uint64_t)k_w / 2,
+                          (uint64_t)a.n_w, (uint64_t)k_w / 2, L::NB / 2, BK,
+                          CG == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)
+            : make_map_2d(&maps.codes[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, a.codes, (uint64_t)k_w / 2,
+                          (uint64_t)a.n_w, (uint64_t)k_w / 2, BK / 2, L::NB,
+                          CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (!ok) { *why = "cuTensorMapEncodeTiled(codes)"; return cudaErrorInvalidValue; }
+        GemmProblem& q = p.prob[i];
+        q.absmax = a.absmax; q.code2 = a.code2; q.absmax2 = a.absmax2; q.offset = a.offset;
+        q.code16 = a.code16; q.bias = a.bias; q.ext_a = a.ext_a; q.ext_b = a.ext_b;
+        q.out = a.out; q.ld_out = a.ld_out; q.ws = nullptr; q.ldp = pl.ldp[TRANS_W ? 0 : i];
+        q.n_w = (int)a.n_w; q.first = pl.first[i];
+        q.nested = a.nested; q.nested_blocksize = a.nested_blocksize;
+        q.nested_shift = -1;
+        if (a.nested_blocksize > 0 && (a.nested_blocksize & (a.nested_blocksize - 1)) == 0) {
+            int sft = 0;
+            while ((1 << sft) < a.nested_blocksize) ++sft;
+            q.nested_shift = sft;
+        }
+        q.pad = 0;
+        if (a.ext_a != nullptr) ++p.n_ext;
     }
+    for (int i = ga.count; i < MAXP; ++i) {
+        p.prob[i] = p.prob[0];
+        maps.codes[i] = maps.codes[0];
+    }
+    if (!TRANS_W)
+        for (int i = 1; i < MAXP; ++i) maps.act[i] = maps.act[0];
+    else
+        for (int i = ga.count; i < MAXP; ++i) maps.act[i] = maps.act[0];
+    p.status = device_status_word();
     if (p.status == nullptr) { *why = "device status word"; return cudaErrorInvalidValue; }
+    p.m = (int)m; p.k_w = (int)k_w;
+    p.nkb_total = pl.nkb;
     p.m_tiles = pl.m_tiles;
     p.n_tiles = pl.n_tiles;
     p.splits = pl.splits;
     p.kb_per_split = pl.kb_per_split;
-    p.ldp = pl.ldp;
-    p.ws = nullptr;
     p.debug = debug_flags();
     if (p.splits > 1) {
-        if (a.workspace == nullptr || a.workspace_bytes < pl.ws_bytes) {
+        if (a0.workspace == nullptr || a0.workspace_bytes < pl.ws_bytes) {
             p.splits = 1;  // no scratch given: one unit per tile walks the whole K range
-            p.kb_per_split = (int)((kc + BK - 1) / BK);
+            p.kb_per_split = pl.nkb;
         } else {
-            p.ws = static_cast<float*>(a.workspace);
+            for (int i = 0; i < (TRANS_W ? 1 : ga.count); ++i)
+                p.prob[i].ws = static_cast<float*>(a0.workspace) + pl.ws_off[i];
         }
     }
     const long long units = (long long)p.m_tiles * p.n_tiles * p.splits;
@@ -903,58 +1012,77 @@ static cudaError_t launch_cfg(const GemmArgs& a, const GemmPlan& pl, cudaStream_
     cfg.numAttrs = CG == 2 ? 1 : 0;
 
     // Units that can be resident at once: one CTA per SM; pairs must sit in one GPC, so ask the
-    // runtime how many clusters fit (once per configuration and device count is stable).
-    int slots = a.sm_count / CG;
+    // runtime how many clusters fit (once per configuration).
+    int slots = a0.sm_count / CG;
     if (CG == 2) {
         static int max_clusters = -1;
         if (max_clusters < 0) {
-            cfg.gridDim = dim3((unsigned)(a.sm_count / 2) * 2, 1, 1);
+            cfg.gridDim = dim3((unsigned)(a0.sm_count / 2) * 2, 1, 1);
             int n = 0;
             if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n > 0)
                 max_clusters = n;
             else
-                max_clusters = a.sm_count / 2;
+                max_clusters = a0.sm_count / 2;
         }
         if (max_clusters < slots) slots = max_clusters;
     }
     const unsigned grid = (unsigned)(units < slots ? units : slots) * CG;
     cfg.gridDim = dim3(grid, 1, 1);
-    e = cudaLaunchKernelEx(&cfg, kernel, tm_act, tm_codes, p);
+    e = cudaLaunchKernelEx(&cfg, kernel, maps, p);
     if (e != cudaSuccess) { *why = "kernel launch"; return e; }
 
     if (p.splits > 1) {
-        const long long total = a.m * ((n_out + 7) / 8);
-        long long blocks = (total + 255) / 256;
-        const long long cap = (long long)a.sm_count * 8;
-        if (blocks > cap) blocks = cap;
-        const int vec_ok = (a.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15) == 0);
-        splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
-            p.ws, a.m, n_out, p.ldp, p.splits, TRANS_W ? nullptr : a.bias, a.out, a.ld_out, vec_ok);
-        e = cudaGetLastError();
-        if (e != cudaSuccess) *why = "split-K reduce launch";
+        for (int i = 0; i < (TRANS_W ? 1 : ga.count); ++i) {
+            const GemmArgs& a = ga.item[i];
+            const long long n_out = TRANS_W ? k_w : a.n_w;
+            const long long total = m * ((n_out + 7) / 8);
+            long long blocks = (total + 255) / 256;
+            const long long cap = (long long)a0.sm_count * 8;
+            if (blocks > cap) blocks = cap;
+            const int vec_ok = (a.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15) == 0);
+            splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+                p.prob[i].ws, m, n_out, p.prob[i].ldp, p.splits, TRANS_W ? nullptr : a.bias, a.out,
+                a.ld_out, vec_ok);
+            e = cudaGetLastError();
+            if (e != cudaSuccess) { *why = "split-K reduce launch"; return e; }
+        }
     }
     return e;
 }
 
-cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why) {
+cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, const char** why) {
     *why = "";
-    const GemmPlan pl = plan_gemm(a.m, a.n_w, a.k_w, a.trans_w, a.sm_count);
+    if (ga.count < 1 || ga.count > GEMM_MAX_GROUP) { *why = "group size"; return cudaErrorInvalidValue; }
+    long long n_w[GEMM_MAX_GROUP];
+    for (int i = 0; i < ga.count; ++i) n_w[i] = ga.item[i].n_w;
+    const GemmArgs& a = ga.item[0];
+    const GemmPlan pl = plan_gemm_group(a.m, n_w, ga.count, a.k_w, a.trans_w, a.sm_count);
     const bool dw8 = (debug_flags() & 32) != 0;  // tuning: 8 decoding warps with twice the work
     if (pl.cg == 2 && pl.nacc == 2) {
         if (dw8)
-            return a.trans_w ? launch_cfg<2, 2, true, 4, 8>(a, pl, stream, why)
-                             : launch_cfg<2, 2, false, 4, 8>(a, pl, stream, why);
-        return a.trans_w ? launch_cfg<2, 2, true, 4, 16>(a, pl, stream, why)
-                         : launch_cfg<2, 2, false, 4, 16>(a, pl, stream, why);
+            return a.trans_w ? launch_cfg<2, 2, true, 4, 8, MAXP>(ga, pl, stream, why)
+                             : launch_cfg<2, 2, false, 4, 8, MAXP>(ga, pl, stream, why);
+        return a.trans_w ? launch_cfg<2, 2, true, 4, 16, MAXP>(ga, pl, stream, why)
+                         : launch_cfg<2, 2, false, 4, 16, MAXP>(ga, pl, stream, why);
     }
     if (pl.cg == 2)
-        return a.trans_w ? launch_cfg<2, 1, true, 6, 16>(a, pl, stream, why)
-                         : launch_cfg<2, 1, false, 6, 16>(a, pl, stream, why);
+        return a.trans_w ? launch_cfg<2, 1, true, 6, 16, MAXP>(ga, pl, stream, why)
+                         : launch_cfg<2, 1, false, 6, 16, MAXP>(ga, pl, stream, why);
     if (pl.nacc == 2)
-        return a.trans_w ? launch_cfg<1, 2, true, 3, 16>(a, pl, stream, why)
-                         : launch_cfg<1, 2, false, 3, 16>(a, pl, stream, why);
-    return a.trans_w ? launch_cfg<1, 1, true, 4, 16>(a, pl, stream, why)
-                     : launch_cfg<1, 1, false, 4, 16>(a, pl, stream, why);
+        return a.trans_w ? launch_cfg<1, 2, true, 3, 16, 1>(ga, pl, stream, why)
+                         : launch_cfg<1, 2, false, 3, 16, 1>(ga, pl, stream, why);
+    if (ga.count > 1)  // small-M groups: one stage less makes room for every problem's table
+        return a.trans_w ? launch_cfg<1, 1, true, 3, 16, MAXP>(ga, pl, stream, why)
+                         : launch_cfg<1, 1, false, 3, 16, MAXP>(ga, pl, stream, why);
+    return a.trans_w ? launch_cfg<1, 1, true, 4, 16, 1>(ga, pl, stream, why)
+                     : launch_cfg<1, 1, false, 4, 16, 1>(ga, pl, stream, why);
+}
+
+cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why) {
+    GemmGroupArgs ga;
+    ga.count = 1;
+    ga.item[0] = a;
+    return launch_gemm_group(ga, stream, why);
 }
 
 }  // namespace nf4

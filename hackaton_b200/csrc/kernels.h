@@ -51,6 +51,8 @@ struct GemmArgs {
     size_t workspace_bytes;
 };
 
+constexpr int GEMM_MAX_GROUP = 4;  // weights that one grouped launch can take
+
 // Tiling and split-K plan of one GEMM call.
 struct GemmPlan {
     int cg;            // CTAs cooperating on one tile (1, or 2 = CTA pair)
@@ -58,13 +60,29 @@ struct GemmPlan {
     int m_tiles, n_tiles;
     int splits;        // units sharing one tile along K
     int kb_per_split;  // 64-deep k-blocks per unit
-    long long ldp;     // row pitch (floats) of a split-K partial plane
-    size_t ws_bytes;   // split-K scratch: splits planes of m x ldp floats (0 when not split)
+    int nkb;           // k-blocks of the whole contraction
+    int first[GEMM_MAX_GROUP];        // first n-tile (forward) / k-block (backward) per problem
+    long long ldp[GEMM_MAX_GROUP];    // row pitch (floats) of each output's split-K planes
+    size_t ws_off[GEMM_MAX_GROUP];    // offset (floats) of each output's planes in the scratch
+    size_t ws_bytes;   // split-K scratch: per output, splits planes of m x ldp floats (0: no split)
 };
+
+struct GemmArgs;
+// A group of up to GEMM_MAX_GROUP weights with the same number of columns. Forward: shared
+// activations (item[0].act), one output per item. Backward: one dY per item (item[i].act), the
+// products are summed into item[0].out. m, trans_w, sm_count and the workspace come from item[0].
+GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long k_w, bool trans_w,
+                         int sm_count);
 GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int sm_count);
+
+struct GemmGroupArgs {
+    int count;
+    GemmArgs item[GEMM_MAX_GROUP];
+};
 
 // Returns cudaSuccess or the failing CUDA error; `why` receives a short reason on failure.
 cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why);
+cudaError_t launch_gemm_group(const GemmGroupArgs& a, cudaStream_t stream, const char** why);
 
 struct LoraDownArgs {
     const __half* in;

@@ -129,6 +129,28 @@ int nf4b200_linear_bwd_dx(const nf4b200_weight* w, const void* dy, int64_t m, in
 int64_t nf4b200_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int backward);
 
 /*
+ * Grouped launches for projections that sit side by side in the model (the call sites of
+ * solution/patches.py:32-41 and :98-99: q/k/v share the post-norm hidden state, gate/up share the
+ * MLP input). `count` weights (1..4) with the same n_cols go through one kernel launch:
+ *   forward : y[i][m, n_rows_i] = x . W_i^T (+ bias[i]) (+ xa[i] . lora_b[i]^T)   one x, one y each
+ *   backward: dx[m, n_cols] = sum_i dy[i][m, n_rows_i] . W_i (+ u[i] . lora_a[i])  one dx for all
+ * which is what autograd needs, since the inputs' gradients of such projections are summed anyway.
+ * The arrays bias / xa / lora_b / u / lora_a may be NULL or hold NULL entries. The scratch rules
+ * are those of nf4b200_workspace_bytes. The reference launches one decode + one cuBLAS call per
+ * projection (solution/nf4.py:87-99) and has no grouped counterpart.
+ */
+int nf4b200_linear_fwd_group(int count, const nf4b200_weight* const* w, const void* x, int64_t m,
+                             int64_t ldx, const void* const* bias, const void* const* xa,
+                             const void* const* lora_b, void* const* y, const int64_t* ldy,
+                             void* workspace, size_t workspace_bytes, void* stream);
+int nf4b200_linear_bwd_dx_group(int count, const nf4b200_weight* const* w, const void* const* dy,
+                                int64_t m, const int64_t* lddy, const void* const* u,
+                                const void* const* lora_a, void* dx, int64_t lddx, void* workspace,
+                                size_t workspace_bytes, void* stream);
+int64_t nf4b200_workspace_bytes_group(int count, const int64_t* n_rows, int64_t n_cols, int64_t m,
+                                      int backward);
+
+/*
  * Rank-16 projection used by both passes of the LoRA update (peft's lora_A / lora_B linears;
  * third-party in the reference, configured at README.md:91 and task/task.yaml:18-21):
  *   out[m, 16] = scaling * in[m, c] . P        (fp16 in, fp32 accumulate, fp16 out)

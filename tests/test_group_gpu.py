@@ -1,0 +1,85 @@
+"""GPU: grouped launches (q/k/v sharing one input, their input gradients summed) through the C
+ABI against the oracle and against the one-projection-at-a-time path."""
+
+import pytest
+import torch
+
+from oracle import nf4_oracle
+from tests.util import oracle_weight, synthetic_weight
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def build(m, k, ns, lora_on, seed):
+    from hackaton_b200 import Projection
+
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(m, k, generator=g).half()
+    projs, cpu = [], []
+    for i, n in enumerate(ns):
+        packed, state = synthetic_weight(n, k, True, seed=seed + i, device="cuda")
+        w = oracle_weight(packed, state)
+        dy = torch.randn(m, n, generator=g).half()
+        bias = (torch.randn(n, generator=g) * 0.1).half() if i == 1 else None
+        a = b = None
+        if i in lora_on:
+            a = ((torch.rand(16, k, generator=g) * 2 - 1) / k ** 0.5).half()
+            b = (torch.randn(n, 16, generator=g) * 0.2).half()
+        cpu.append((w, dy, bias, a, b))
+        projs.append(Projection(packed, state,
+                                None if bias is None else bias.cuda().requires_grad_(),
+                                None if a is None else a.cuda().requires_grad_(),
+                                None if b is None else b.cuda().requires_grad_(), 2.0))
+    return x, projs, cpu
+
+
+@pytest.mark.parametrize("m,k,ns,lora_on", [
+    (2048, 1536, (1536, 256, 256), (0, 2)),   # q, k, v of Qwen2.5-1.5B with LoRA on q and v
+    (300, 192, (264, 64, 8), (1,)),           # ragged sizes
+    (2048, 1536, (512, 512), ()),             # no LoRA
+    (64, 128, (256, 256, 128, 64), (3,)),     # single-CTA tiles, four members
+])
+def test_group_forward_backward_vs_oracle(cuda_lib, m, k, ns, lora_on):
+    from hackaton_b200 import nf4_linear_group
+
+    x, projs, cpu = build(m, k, ns, lora_on, seed=m + k)
+    xg = x.cuda().requires_grad_()
+    ys = nf4_linear_group(xg, projs)
+    torch.autograd.backward(list(ys), [c[1].cuda() for c in cpu])
+    torch.cuda.synchronize()
+    dx_ref = torch.zeros(m, k)
+    for y, pr, (w, dy, bias, a, b) in zip(ys, projs, cpu):
+        if a is None:
+            y_ref = nf4_oracle.linear_fwd(x, w, bias)
+            dx_ref += dy.float() @ w.float()
+        else:
+            y_ref, _ = nf4_oracle.lora_fwd(x, w, a, b, 2.0, bias)
+            dxi, da, db = nf4_oracle.lora_bwd(dy, x, w, a, b, 2.0)
+            dx_ref += dy.float() @ w.float() + 2.0 * (dy.float() @ b.float()) @ a.float()
+            assert nf4_oracle.max_rel_err(pr.lora_a.grad.cpu(), da) <= TOL
+            assert nf4_oracle.max_rel_err(pr.lora_b.grad.cpu(), db) <= TOL
+        assert nf4_oracle.max_rel_err(y.detach().cpu(), y_ref) <= TOL
+        if bias is not None:
+            torch.testing.assert_close(pr.bias.grad.float().cpu(), dy.float().sum(0), rtol=2e-2, atol=2e-1)
+    assert nf4_oracle.max_rel_err(xg.grad.cpu(), dx_ref) <= TOL
+    cuda_lib.device_status()
+
+
+def test_group_equals_one_at_a_time(cuda_lib):
+    from hackaton_b200 import nf4_linear
+    from hackaton_b200.group import linear_backward_dx_group, linear_forward_group
+    from hackaton_b200.nf4 import linear_backward_dx
+
+    m, k, ns = 2048, 1536, (1536, 256, 256)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(m, k, generator=g, device="cuda").half()
+    ws = [synthetic_weight(n, k, True, seed=40 + i, device="cuda") for i, n in enumerate(ns)]
+    ys = linear_forward_group(x, ws)
+    for y, (packed, state) in zip(ys, ws):
+        one = nf4_linear(x, packed, None, state)
+        assert float((y.float() - one.float()).abs().max() / one.float().abs().max()) < 2e-3
+    dys = [torch.randn(m, n, generator=g, device="cuda").half() for n in ns]
+    dx = linear_backward_dx_group(dys, ws)
+    ref = sum(linear_backward_dx(dy, p, s).float() for dy, (p, s) in zip(dys, ws))
+    assert float((dx.float() - ref).abs().max() / ref.abs().max()) < 5e-3
