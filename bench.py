@@ -483,8 +483,28 @@ def run_single(args):
     reps = 2 * N_LAYERS
 
     def time_kernel(fn):
+        """Average device time (ms) of one launch: `reps` launches over the rotating layers, as one
+        CUDA graph between two events (eager launches of a ~55 us kernel are bound by the host's
+        launch rate, not by the kernel), median of five replays."""
         for i in range(8):
             fn(i)
+        torch.cuda.synchronize()
+        if use_graphs:
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(side):
+                    with torch.cuda.graph(g, stream=side):
+                        outs = [fn(i) for i in range(reps)]
+                torch.cuda.current_stream().wait_stream(side)
+                g.replay()
+                _, per, _ = timed_steps(lambda i: g.replay(), 5)
+                del outs
+                return sorted(per)[2] / reps
+            except Exception as exc:
+                print(f"[bench] kernel graph capture failed ({exc!r}); timing eager launches",
+                      file=sys.stderr)
         total, _, _ = timed_steps(fn, reps)
         return total / reps
 
@@ -508,6 +528,8 @@ def run_single(args):
         "traffic": 13.66e6, "traffic_unit": "bytes per launch, from an ncu capture of this command",
         "kernel": "nf4_gemm_kernel<CG=2,NACC=2,fwd> (CTA pairs, 512x256 tiles) on gate_proj (M=2048, N=8960, K=1536)",
         "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
+        "timing": f"CUDA events around a graph of {reps} launches over the rotating layers"
+                  if use_graphs else "CUDA events around eager launches",
         "us_per_launch": {k: v * 1e3 for k, v in kern.items()},
         "tflops": {k: gemm_flops / (v * 1e-3) / 1e12 for k, v in kern.items()},
     }

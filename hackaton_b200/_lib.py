@@ -17,7 +17,8 @@ EXPORTS = (
     "nf4b200_query", "nf4b200_last_error", "nf4b200_device_status", "nf4b200_dequant",
     "nf4b200_linear_fwd", "nf4b200_linear_bwd_dx", "nf4b200_lora_down", "nf4b200_lora_grad",
     "nf4b200_workspace_bytes", "nf4b200_linear_fwd_static", "nf4b200_linear_fwd_group",
-    "nf4b200_linear_bwd_dx_group", "nf4b200_workspace_bytes_group",
+    "nf4b200_linear_bwd_dx_group", "nf4b200_workspace_bytes_group", "nf4b200_scales16_bytes",
+    "nf4b200_prepare_scales",
 )
 
 F16, BF16, F32 = 0, 1, 2
@@ -37,7 +38,7 @@ class Weight(Structure):
         ("codes", c_void_p), ("absmax", c_void_p), ("code2", c_void_p), ("absmax2", c_void_p),
         ("offset", c_void_p), ("code16", c_void_p), ("n_rows", c_int64), ("n_cols", c_int64),
         ("blocksize", c_int32), ("nested_blocksize", c_int32), ("nested", c_int32),
-        ("reserved", c_int32),
+        ("reserved", c_int32), ("scales16", c_void_p),
     ]
 
 
@@ -84,9 +85,12 @@ def lib() -> ctypes.CDLL:
                                                    c_int64, c_void_p, c_size_t, c_void_p]
     handle.nf4b200_workspace_bytes_group.argtypes = [c_int, pi64, c_int64, c_int64, c_int]
     handle.nf4b200_workspace_bytes_group.restype = c_int64
+    handle.nf4b200_scales16_bytes.argtypes = [c_int64, c_int64]
+    handle.nf4b200_scales16_bytes.restype = c_int64
+    handle.nf4b200_prepare_scales.argtypes = [POINTER(Weight), c_void_p, c_void_p]
     for name in EXPORTS:
         if name not in ("nf4b200_last_error", "nf4b200_workspace_bytes",
-                        "nf4b200_workspace_bytes_group"):
+                        "nf4b200_workspace_bytes_group", "nf4b200_scales16_bytes"):
             getattr(handle, name).restype = c_int
     handle.nf4b200_workspace_bytes.restype = c_int64
     _lib = handle

@@ -109,6 +109,13 @@ int check_weight(const nf4b200_weight* w, bool for_gemm) {
         if (!aligned16(w->codes)) return fail(NF4B200_EINVAL, "codes pointer is not 16-byte aligned");
         if (w->n_rows > 0x7FFFFFFF || w->n_cols > 0x7FFFFFFF)
             return fail(NF4B200_EINVAL, "weight dimension exceeds 2^31");
+        if (w->scales16 != nullptr) {
+            if (!aligned16(w->scales16))
+                return fail(NF4B200_EINVAL, "scales16 is not 16-byte aligned");
+            if (w->n_rows % 8 != 0)
+                return fail(NF4B200_EINVAL, "scales16 needs n_rows %% 8 == 0, got %lld",
+                            (long long)w->n_rows);
+        }
     }
     return NF4B200_OK;
 }
@@ -131,6 +138,7 @@ void fill_gemm(nf4::GemmArgs& g, const nf4b200_weight* w, int sms) {
     g.absmax2 = w->absmax2;
     g.offset = w->offset;
     g.code16 = w->code16;
+    g.scales16 = static_cast<const __half*>(w->scales16);
     g.n_w = w->n_rows;
     g.k_w = w->n_cols;
     g.nested = w->nested ? 1 : 0;
@@ -227,6 +235,31 @@ int nf4b200_dequant(const nf4b200_weight* w, void* out, int out_dtype, void* str
     a.sm_count = d->sms;
     cudaError_t e = nf4::launch_dequant(a, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(NF4B200_ECUDA, "dequant launch: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int64_t nf4b200_scales16_bytes(int64_t n_rows, int64_t n_cols) {
+    if (n_rows <= 0 || n_cols <= 0 || n_cols % 64 != 0 || n_rows % 8 != 0) return 0;
+    return n_rows * (n_cols / 64) * 2;
+}
+
+int nf4b200_prepare_scales(const nf4b200_weight* w, void* scales16, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    nf4b200_weight tmp;
+    if (w) { tmp = *w; tmp.scales16 = nullptr; }
+    if ((rc = check_weight(w ? &tmp : nullptr, true)) != NF4B200_OK) return rc;
+    if (w->n_rows % 8 != 0)
+        return fail(NF4B200_EINVAL, "prepare_scales needs n_rows %% 8 == 0, got %lld",
+                    (long long)w->n_rows);
+    if (!scales16 || !aligned16(scales16))
+        return fail(NF4B200_EINVAL, "scales16 must be a 16-byte aligned device pointer");
+    cudaError_t e = nf4::launch_prepare_scales(
+        w->absmax, w->code2, w->absmax2, w->offset, w->n_rows, w->n_cols / 64, w->nested ? 1 : 0,
+        w->nested ? w->nested_blocksize : 1, static_cast<__half*>(scales16), d->sms,
+        static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "prepare_scales launch: %s", cudaGetErrorString(e));
     return NF4B200_OK;
 }
 

@@ -136,4 +136,42 @@ cudaError_t launch_dequant(const DequantArgs& a, cudaStream_t stream) {
     }
 }
 
+// Block-scale table for the fused GEMM: out[kb][row] = fp16(scale of block row * bpr + kb), i.e. the
+// (double-)dequantised absmax rounded to fp16 exactly as the GEMM's decode step rounds it, stored
+// k-block-major so that the scales a tile needs are contiguous in both directions.
+__global__ void __launch_bounds__(256)
+prepare_scales_kernel(const void* __restrict__ absmax, const float* __restrict__ code2,
+                      const float* __restrict__ absmax2, const float* __restrict__ offset,
+                      long long n_rows, long long bpr, int nested, int nested_blocksize,
+                      __half* __restrict__ out) {
+    const long long total = n_rows * bpr;
+    const float off = nested ? __ldg(offset) : 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long kb = i / n_rows, row = i % n_rows;  // consecutive threads: consecutive rows
+        const long long blk = row * bpr + kb;
+        float sc;
+        if (nested)
+            sc = nested_scale(__ldg(code2 + __ldg(static_cast<const uint8_t*>(absmax) + blk)),
+                              __ldg(absmax2 + blk / nested_blocksize), off);
+        else
+            sc = __ldg(static_cast<const float*>(absmax) + blk);
+        out[i] = __float2half_rn(sc);
+    }
+}
+
+cudaError_t launch_prepare_scales(const void* absmax, const float* code2, const float* absmax2,
+                                  const float* offset, long long n_rows, long long bpr, int nested,
+                                  int nested_blocksize, __half* out, int sm_count,
+                                  cudaStream_t stream) {
+    const long long total = n_rows * bpr;
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    prepare_scales_kernel<<<(unsigned)blocks, 256, 0, stream>>>(absmax, code2, absmax2, offset, n_rows,
+                                                               bpr, nested, nested_blocksize, out);
+    return cudaGetLastError();
+}
+
 }  // namespace nf4

@@ -10,28 +10,35 @@
 // the 64-deep k-blocks; each CTA holds 128*NACC of its rows (activations in shared memory,
 // accumulators in its own TMEM) and decodes only half of the weight tile, which the tensor cores
 // of both SMs then read. With CG = 1 (token counts up to 128) a single CTA owns a 128 x 256 tile.
-// Roles inside a CTA (18 warps):
-//   warps 0..15  producers: read packed codes from shared memory, fetch the block scales (u8
-//                absmax -> second-level table -> * absmax2 + offset, prefetched one k-block
-//                ahead), expand codes through a register-resident fp16 table (byte permutes, no
-//                shared-memory lookups) and write the fp16 weight tile in the 128-byte-swizzled
-//                layout the MMA descriptor expects. At the end of a unit the same warps drain the
-//                accumulators (tcgen05.ld), transpose them through shared memory and store whole
-//                128-byte lines.
-//   warp 16      TMA: this CTA's activation tiles (128-byte swizzle) and code tile of each
-//                k-block into a STAGES-deep ring; it runs ahead into the next unit while the
-//                producers are still in the epilogue of the current one.
+// Roles inside a CTA (19 warps):
+//   warps 0..15  producers: read the packed codes and the block scale of their piece from the code
+//                ring, expand the codes through a register-resident fp16 table (byte permutes, no
+//                shared-memory lookups), wait for the operand slot to be free and write the fp16
+//                weight tile in the 128-byte-swizzled layout the MMA descriptor expects. They work
+//                as one group of 16 warps or as two groups of 8 that take the k-blocks in turn. At
+//                the end of a unit all 16 drain the accumulators (tcgen05.ld), transpose them
+//                through shared memory and store whole 128-byte lines.
+//   warp 16      TMA: this CTA's activation tiles (128-byte swizzle) of each k-block into the
+//                STAGES-deep operand ring; it runs ahead into the next unit while the producers
+//                are still in the epilogue of the current one.
 //   warp 17      allocates TMEM; in the leader CTA one lane issues the MMAs (N = 256, K = 16) and
 //                commits each k-block to the ring's "empty" barriers and each unit to
-//                "accumulators full" (multicast to both CTAs of a pair).
+//                "accumulators full" (multicast to both CTAs of a pair). In the peer CTA one lane
+//                forwards "activation tile landed" to the leader.
+//   warp 18      feeds the code ring (NC slots, deeper than the operand ring, so that HBM latency
+//                stays out of the operand ring's cycle): per k-block one TMA for this CTA's code
+//                tile and the tile's block scales. With a ready-made scale table (see
+//                launch_prepare_scales) that is one more small TMA; without, two asynchronous
+//                4-byte copies per scale (the word holding the u8 absmax entry and the fp32
+//                second-level scale), which the producers turn into
+//                code2[u8] * absmax2 + offset themselves.
 // The weight tile is always stored as rows of n_w holding 64 consecutive k_w (128 bytes, chunk
 // index XOR row%8). Forward reads it as a K-major B operand; backward as an MN-major one.
 // With NACC = 2 two accumulators (two token sub-tiles) reuse each decoded weight tile.
 //
-// Synchronisation across a pair: the producers of both CTAs arrive (one lane per warp, release at
-// cluster scope) on the leader's "weights ready" barrier; the peer's producers only get there
-// after their own TMA barrier fired, so that one barrier also vouches for the peer's activation
-// tile. Accumulator hand-back ("TMEM drained") works the same way.
+// Synchronisation across a pair: the producers of both CTAs and the peer's forwarding lane arrive
+// (plain arrives through the cluster window) on the leader's "operands ready" barrier of the
+// stage. Accumulator hand-back ("TMEM drained") works the same way.
 //
 // Split-K: when a problem has fewer tiles than the GPU has CTA slots, several units share a tile,
 // each over a slice of the k-blocks, and write fp32 partial sums as plain row-major planes
@@ -60,9 +67,10 @@ namespace nf4 {
 
 constexpr int PRODUCER_WARPS = 16;
 constexpr int PRODUCER_THREADS = PRODUCER_WARPS * 32;
-constexpr int GEMM_THREADS = PRODUCER_THREADS + 64;
+constexpr int GEMM_THREADS = PRODUCER_THREADS + 96;
 constexpr int TMA_WARP = PRODUCER_WARPS;
 constexpr int MMA_WARP = PRODUCER_WARPS + 1;
+constexpr int AUX_WARP = PRODUCER_WARPS + 2;
 constexpr int BK = 64;   // k-block depth = one quantisation block
 constexpr int BN = 256;  // output-tile width
 
@@ -98,12 +106,14 @@ struct GemmParams {
     int m, k_w;              // token rows; columns of every weight of the group
     int nkb_total;           // k-blocks of the whole contraction
     int m_tiles, n_tiles, splits, kb_per_split;
+    int prepared;            // every problem comes with a ready-made fp16 block-scale table
     int debug;               // bit 0: producers skip the decode, bit 1: phase trace (tuning only)
 };
 
 struct GemmMaps {
     CUtensorMap act[MAXP];    // forward: only [0]; backward: one dY per problem
     CUtensorMap codes[MAXP];
+    CUtensorMap scales[MAXP]; // fp16 block scales [K_w / 64][N_w] (only when `prepared`)
 };
 
 template <int CG, int NACC, int STAGES, int TABLES_>
@@ -112,12 +122,22 @@ struct SmemLayout {
     static constexpr int A_BYTES = NACC * 128 * BK * 2;
     static constexpr int W_BYTES = NB * BK * 2;
     static constexpr int C_BYTES = NB * BK / 2;
-    static constexpr int STAGE_BYTES = A_BYTES + W_BYTES + C_BYTES;
+    static constexpr int S_BYTES = NB * 8;             // raw block scale of each tile row: 2 words
+    static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;   // ring of MMA operands
     static constexpr int TABLES = TABLES_;  // second-level tables kept in shared memory
-    static constexpr int TABLE2_OFF = STAGES * STAGE_BYTES;
+    // Whatever the operand ring leaves free holds a second, deeper ring of packed codes and
+    // ready-made block scales, so that their HBM latency stays out of the operand ring's cycle.
+    static constexpr int FIXED_BYTES = STAGES * STAGE_BYTES + 64 + 1024 * TABLES + 512 + 1024;
+    static constexpr int NC_FIT = (232448 - FIXED_BYTES) / (C_BYTES + S_BYTES);
+    static constexpr int NC = NC_FIT > 8 ? 8 : NC_FIT;
+    static constexpr int CODES_OFF = STAGES * STAGE_BYTES;
+    static constexpr int SCALE_OFF = CODES_OFF + NC * C_BYTES;
+    static constexpr int META_OFF = SCALE_OFF + NC * S_BYTES;
+    static constexpr int TABLE2_OFF = META_OFF + 64;
     static constexpr int BAR_OFF = TABLE2_OFF + 1024 * TABLES;
-    static constexpr int TOTAL = BAR_OFF + 256;
+    static constexpr int TOTAL = BAR_OFF + 512;
     static constexpr int DYNAMIC_BYTES = TOTAL + 1024;  // slack for 1024-byte alignment
+    static_assert(NC >= 2, "no room for the code ring");
     static constexpr int WARPS_PER_W_SLOT = W_BYTES / 4096;  // 4 KB epilogue staging per warp
     static_assert(STAGES * WARPS_PER_W_SLOT >= PRODUCER_WARPS, "staging needs more weight slots");
     static_assert(DYNAMIC_BYTES <= 232448, "exceeds the 227 KB of shared memory per CTA");
@@ -134,6 +154,39 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
     uint2 v;
     asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
     return v;
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// Asynchronous 4-byte copy global -> shared (no register, no scoreboard), and the arrive that
+// fires on `bar` once all earlier copies of this thread have landed (the barrier's expected
+// count must already include it).
+__device__ __forceinline__ void cp_async_4(uint32_t smem_dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_dst), "l"(src) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ uint2 lds64u(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
@@ -158,13 +211,17 @@ __device__ unsigned long long g_trace[TRACE_CTAS * TRACE_UNITS * TRACE_STAMPS];
 #define NF4_TRACE(slot)                                                                       \
     do {                                                                                      \
         if ((p.debug & 2) && threadIdx.x == 0 && blockIdx.x < TRACE_CTAS &&                   \
-            unit_iter < TRACE_UNITS)                                                          \
+            unit_iter < TRACE_UNITS) {                                                        \
             g_trace[(blockIdx.x * TRACE_UNITS + unit_iter) * TRACE_STAMPS + (slot)] =         \
                 globaltimer_ns();                                                             \
+            if ((slot) == 0 || (slot) == 4)                                                   \
+                g_trace[(blockIdx.x * TRACE_UNITS + unit_iter) * TRACE_STAMPS + 5 +           \
+                        ((slot) >> 2)] = (unsigned long long)clock64();                       \
+        }                                                                                     \
     } while (0)
 
 // Second tuning aid: per-k-block event times of the first pair's first unit.
-constexpr int TRACE2_EVENTS = 6, TRACE2_ITERS = 64;
+constexpr int TRACE2_EVENTS = 8, TRACE2_ITERS = 64;
 __device__ unsigned long long g_trace2[2 * TRACE2_EVENTS * TRACE2_ITERS];
 #define NF4_TRACE2(ev, it_)                                                                    \
     do {                                                                                       \
@@ -226,16 +283,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmParams p) {
     using L = SmemLayout<CG, NACC, STAGES, TABLES>;
     constexpr int NB = L::NB;
-    // DW of the 16 producer warps decode (all 16 drain the accumulators); each decoding thread
+    // The 16 producer warps form 16 / DW groups of DW warps that take the k-blocks in turn (all 16
+    // drain the accumulators): while one group publishes its tile (fence, barriers), the other is
+    // in the integer pipe. Each decoding thread
     // expands WORDS 32-bit code words (8 weights each) per k-block
     constexpr int DECODE_THREADS = DW * 32;
+    constexpr int GROUPS = PRODUCER_WARPS / DW;
     constexpr int WORDS = NB * BK / 8 / DECODE_THREADS;
     static_assert(WORDS == 2 || WORDS == 4, "producer work split");
     constexpr uint32_t TMEM_COLS = NACC * BN;
     static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
     constexpr int ROWS_PER_TILE = 128 * CG * NACC;  // token rows of a unit (whole pair)
     constexpr uint32_t ARRIVALS = CG * PRODUCER_WARPS;  // "TMEM drained" arrivals (all warps)
-    constexpr uint32_t W_ARRIVALS = CG * DW;             // "weights ready" arrivals
+    // "operands ready" arrivals: the decoding warps of both CTAs, plus one from the peer CTA that
+    // vouches for its activation tile
+    constexpr uint32_t W_ARRIVALS = CG * DW + (CG == 2 ? 1 : 0);
+    constexpr int NC = L::NC;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -248,10 +311,14 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
     auto bar_empty = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
     const uint32_t bar_tmem_full = bar_base + 8u * (3 * STAGES);
     const uint32_t bar_tmem_empty = bar_base + 8u * (3 * STAGES + 1);
+    auto bar_full_c = [&](int c) { return bar_base + 8u * (3 * STAGES + 2 + c); };
+    auto bar_empty_c = [&](int c) { return bar_base + 8u * (3 * STAGES + 2 + NC + c); };
+    constexpr int BAR_COUNT = 3 * STAGES + 2 + 2 * NC;
+    static_assert(8 * BAR_COUNT + 8 <= 512, "barrier area");
     volatile uint32_t* tmem_slot =
-        reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 2));
+        reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFF + 8 * BAR_COUNT);
     volatile int* abort_flag =
-        reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFF + 8 * (3 * STAGES + 2) + 4);
+        reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFF + 8 * BAR_COUNT + 4);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -267,15 +334,17 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
             mbar_init(bar_full_w(s), W_ARRIVALS);
             mbar_init(bar_empty(s), 1);
         }
+        for (int c = 0; c < NC; ++c) {
+            mbar_init(bar_full_c(c), 33);   // the TMA's expect_tx arrive + 32 lanes' scale copies
+            mbar_init(bar_empty_c(c), DW);  // every decoding warp has read its share
+        }
         mbar_init(bar_tmem_full, 1);
         mbar_init(bar_tmem_empty, ARRIVALS);
         *abort_flag = 0;
         fence_barrier_init();
     }
-    if (warp == TMA_WARP && lane == 0) {
-        tma_prefetch_desc(&maps.act[0]);
-        tma_prefetch_desc(&maps.codes[0]);
-    }
+    if (warp == TMA_WARP && lane == 0) tma_prefetch_desc(&maps.act[0]);
+    if (warp == AUX_WARP && lane == 0) tma_prefetch_desc(&maps.codes[0]);
     if (warp == MMA_WARP) {
         if (CG == 2) {
             tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -302,6 +371,35 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
 
     int fail = 0;
 
+    // Warp-wide waits: one lane polls the barrier, the others sleep at the warp vote. Keeps the
+    // shared-memory pipe free of 31 redundant polls per warp.
+    auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool {
+        if (mbar_try_wait(bar, parity)) return true;
+        const unsigned long long t0 = globaltimer_ns();
+        uint32_t polls = 0;
+        while (!mbar_try_wait(bar, parity)) {
+            __nanosleep(64);
+            if ((++polls & 63u) == 0u) {
+                if (*abort_flag) return false;
+                if (globaltimer_ns() - t0 > WAIT_TIMEOUT_NS) { *abort_flag = 1; return false; }
+            }
+        }
+        return true;
+    };
+    auto warp_wait_commit = [&](uint32_t bar, uint32_t parity) -> bool {
+        if (mbar_test_wait_cluster(bar, parity)) return true;
+        const unsigned long long t0 = globaltimer_ns();
+        uint32_t polls = 0;
+        while (!mbar_test_wait_cluster(bar, parity)) {
+            __nanosleep(64);
+            if ((++polls & 63u) == 0u) {
+                if (*abort_flag) return false;
+                if (globaltimer_ns() - t0 > WAIT_TIMEOUT_NS) { *abort_flag = 1; return false; }
+            }
+        }
+        return true;
+    };
+
     if (warp == TMA_WARP) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -321,17 +419,11 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                         const int kbg = w.kb_begin + it;                 // group-wide k-block
                         const int pi = TRANS_W ? find_problem(p, kbg) : w.prob;
                         const int kb = TRANS_W ? kbg - p.prob[pi].first : kbg;
-                        mbar_arrive_expect_tx(bar_full_tma(s), L::A_BYTES + L::C_BYTES);
+                        mbar_arrive_expect_tx(bar_full_tma(s), L::A_BYTES);
 #pragma unroll
                         for (int a = 0; a < NACC; ++a)
                             tma_load_2d(sa + a * (128 * BK * 2), &maps.act[TRANS_W ? pi : 0], kb * BK,
                                         w.m0 + a * (128 * CG) + (int)rank * 128, bar_full_tma(s));
-                        const uint32_t sc = sa + L::A_BYTES + L::W_BYTES;
-                        const int nb0 = w.n0 + (int)rank * NB;
-                        if (TRANS_W)
-                            tma_load_2d(sc, &maps.codes[pi], nb0 / 2, kb * BK, bar_full_tma(s));
-                        else
-                            tma_load_2d(sc, &maps.codes[pi], kb * (BK / 2), nb0, bar_full_tma(s));
                     } else {
                         mbar_arrive(bar_full_tma(s));  // extension step: producers bring operands
                     }
@@ -341,98 +433,226 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------ MMA issuer (leader)
         if (lane == 0 && rank == 0) {
+            // This single thread feeds the tensor cores of the whole pair, next to four busy decoding
+            // warps on its scheduler: the loop is written for a minimal instruction count. The ring
+            // loop is unrolled over the stages, so every descriptor is "constant + one add".
             constexpr uint32_t idesc = make_idesc_f16(BN, 0u, TRANS_W ? 1u : 0u, 128u * CG);
-            uint32_t g = 0;
+            // descriptor words of the swizzled main-loop operands (address field left at 0) ...
+            constexpr uint64_t A_MAIN = make_smem_desc(0, 16, 1024, LAYOUT_SW128);
+            constexpr uint64_t B_MAIN = TRANS_W ? make_smem_desc(0, 64 * 128, 1024, LAYOUT_SW128)
+                                                : make_smem_desc(0, 16, 1024, LAYOUT_SW128);
+            // ... and of the K extension's unswizzled core-matrix operands:
+            // A: [row/8][k-half][row%8][16 B]  -> LBO 128, SBO 256 (K-major).
+            // B forward:  same form over this CTA's NB n_w rows (K-major).
+            // B backward: [r/8][k_w/8][r%8][16 B] -> LBO NB*16, SBO 128 (MN-major).
+            constexpr uint64_t A_EXT = make_smem_desc(0, 128, 256, LAYOUT_NONE);
+            constexpr uint64_t B_EXT = TRANS_W ? make_smem_desc(0, NB * 16, 128, LAYOUT_NONE)
+                                               : make_smem_desc(0, 128, 256, LAYOUT_NONE);
+            constexpr uint32_t B_KSTEP = TRANS_W ? (16 * 128) >> 4 : 32 >> 4;  // 16 k further on
+            const uint32_t base4 = (smem_base & 0x3FFFFu) >> 4;
+
+            int u = pair;
             uint32_t unit_iter = 0;
-            long long wait_tma = 0, wait_w = 0;  // tuning: cycles the issuer spent on each barrier
-            for (int u = pair; u < total_units && !fail; u += n_pairs, ++unit_iter) {
-                const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
-                // the accumulators of the previous unit must have been drained (in both CTAs)
-                if (!mbar_wait_cluster(bar_tmem_empty, (unit_iter & 1u) ^ 1u, abort_flag)) {
-                    fail = 6;
-                    break;
-                }
+            bool have = u < total_units;
+            Unit w;
+            w.nkb = w.n_iter = 0;
+            int it = 0;
+            if (have) {
+                w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
                 tc_fence_after_sync();
-                for (int it = 0; it < w.n_iter; ++it, ++g) {
-                    const int s = (int)(g % STAGES);
-                    const uint32_t ph = (g / STAGES) & 1u;
-                    const uint32_t sa = smem_base + (uint32_t)s * L::STAGE_BYTES;
-                    const uint32_t sw = sa + L::A_BYTES;
+            }
+            uint32_t ph = 0;
+            while (have) {
+#pragma unroll
+                for (int s = 0; s < STAGES; ++s) {
+                    if (!have) continue;
                     const uint32_t unit_iter2 = unit_iter;
-                    const long long c0 = (p.debug & 2) ? clock64() : 0;
-                    if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 2; break; }
+                    if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 2; have = false; continue; }
                     NF4_TRACE2(3, it);
-                    const long long c1 = (p.debug & 2) ? clock64() : 0;
-                    if (!mbar_wait_cluster(bar_full_w(s), ph, abort_flag)) { fail = 3; break; }
+                    if (!mbar_wait_cluster(bar_full_w(s), ph, abort_flag)) { fail = 3; have = false; continue; }
                     NF4_TRACE2(4, it);
-                    if (p.debug & 2) {
-                        const long long c2 = clock64();
-                        wait_tma += c1 - c0;
-                        wait_w += c2 - c1;
-                    }
                     tc_fence_after_sync();
-                    if (it < w.nkb) {
-                        const uint64_t bdesc0 = TRANS_W
-                            ? make_smem_desc(sw, 64 * 128, 1024, LAYOUT_SW128)
-                            : make_smem_desc(sw, 16, 1024, LAYOUT_SW128);
+                    const uint32_t a4 = base4 + (uint32_t)s * (L::STAGE_BYTES >> 4);
+                    const uint32_t w4 = a4 + (L::A_BYTES >> 4);
+                    if (p.debug & 4) {
+                        // tuning aid: no MMAs, the commits below fire at once
+                    } else if (it < w.nkb) {
+                        const uint32_t first = it > 0 ? 1u : 0u;
 #pragma unroll
                         for (int k = 0; k < BK / 16; ++k) {
-                            const uint64_t bdesc =
-                                bdesc0 + (uint64_t)(TRANS_W ? (16 * 128) >> 4 : 32 >> 4) * k;
 #pragma unroll
-                            for (int a = 0; a < NACC; ++a) {
-                                const uint64_t adesc =
-                                    make_smem_desc(sa + a * (128 * BK * 2), 16, 1024, LAYOUT_SW128) +
-                                    (uint64_t)(32 >> 4) * k;
-                                const uint32_t accum = (it > 0 || k > 0) ? 1u : 0u;
-                                if (CG == 2) umma_f16_pair(tmem_base + a * BN, adesc, bdesc, idesc, accum);
-                                else         umma_f16(tmem_base + a * BN, adesc, bdesc, idesc, accum);
-                            }
+                            for (int a = 0; a < NACC; ++a)
+                                umma_f16_words<CG>(
+                                    tmem_base + a * BN,
+                                    a4 + (uint32_t)(A_MAIN & 0xFFFFFFFFu) + a * ((128 * BK * 2) >> 4) + 2 * k,
+                                    (uint32_t)(A_MAIN >> 32),
+                                    w4 + (uint32_t)(B_MAIN & 0xFFFFFFFFu) + B_KSTEP * k,
+                                    (uint32_t)(B_MAIN >> 32), idesc, k > 0 ? 1u : first);
                         }
                     } else {
-                        // K extension: unswizzled core-matrix operands (layout type 0).
-                        // A: [row/8][k-half][row%8][16 B]  -> LBO 128, SBO 256 (K-major).
-                        // B forward:  same form over this CTA's NB n_w rows (K-major).
-                        // B backward: [r/8][k_w/8][r%8][16 B] -> LBO NB*16, SBO 128 (MN-major).
-                        const uint64_t bdesc = TRANS_W
-                            ? make_smem_desc(sw, NB * 16, 128, LAYOUT_NONE)
-                            : make_smem_desc(sw, 128, 256, LAYOUT_NONE);
 #pragma unroll
-                        for (int a = 0; a < NACC; ++a) {
-                            const uint64_t adesc =
-                                make_smem_desc(sa + a * (128 * BK * 2), 128, 256, LAYOUT_NONE);
-                            const uint32_t accum = it > 0 ? 1u : 0u;
-                            if (CG == 2) umma_f16_pair(tmem_base + a * BN, adesc, bdesc, idesc, accum);
-                            else         umma_f16(tmem_base + a * BN, adesc, bdesc, idesc, accum);
-                        }
+                        for (int a = 0; a < NACC; ++a)
+                            umma_f16_words<CG>(tmem_base + a * BN,
+                                               a4 + (uint32_t)(A_EXT & 0xFFFFFFFFu) + a * ((128 * BK * 2) >> 4),
+                                               (uint32_t)(A_EXT >> 32), w4 + (uint32_t)(B_EXT & 0xFFFFFFFFu),
+                                               (uint32_t)(B_EXT >> 32), idesc, it > 0 ? 1u : 0u);
                     }
                     if (CG == 2) umma_commit_pair(bar_empty(s), (uint16_t)3);
                     else         umma_commit(bar_empty(s));
                     NF4_TRACE2(5, it);
+                    if (++it == w.n_iter) {
+                        // unit done: hand the accumulators to the epilogue, move on
+                        if (CG == 2) umma_commit_pair(bar_tmem_full, (uint16_t)3);
+                        else         umma_commit(bar_tmem_full);
+                        u += n_pairs;
+                        have = u < total_units;
+                        if (have) {
+                            w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
+                            it = 0;
+                            // the accumulators must have been drained (in both CTAs)
+                            if (!mbar_wait_cluster(bar_tmem_empty, unit_iter & 1u, abort_flag)) {
+                                fail = 6;
+                                have = false;
+                            }
+                            tc_fence_after_sync();
+                        }
+                        ++unit_iter;
+                    }
+                    if (s == STAGES - 1) ph ^= 1u;
                 }
-                if (!fail) {
-                    if (CG == 2) umma_commit_pair(bar_tmem_full, (uint16_t)3);
-                    else         umma_commit(bar_tmem_full);
-                }
-                if ((p.debug & 2) && blockIdx.x < TRACE_CTAS && unit_iter == 0) {
-                    g_trace[(blockIdx.x * TRACE_UNITS) * TRACE_STAMPS + 5] = (unsigned long long)wait_tma;
-                    g_trace[(blockIdx.x * TRACE_UNITS) * TRACE_STAMPS + 6] = (unsigned long long)wait_w;
-                    g_trace[(blockIdx.x * TRACE_UNITS) * TRACE_STAMPS + 7] = (unsigned long long)clock64();
+            }
+        } else if (CG == 2 && lane == 0) {
+            // Peer CTA: tell the leader when this CTA's activation tile of a step has landed.
+            uint32_t g = 0;
+            for (int u = pair; u < total_units && !fail; u += n_pairs) {
+                const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
+                for (int it = 0; it < w.n_iter; ++it, ++g) {
+                    const int s = (int)(g % STAGES);
+                    if (!mbar_wait(bar_full_tma(s), (g / STAGES) & 1u, abort_flag)) { fail = 8; break; }
+                    mbar_arrive_cluster(lead_full_w0 + 8u * s);
                 }
             }
         }
+    } else if (warp == AUX_WARP) {
+        // ------------------------------------------------------------------ codes + block scales
+        // Walks the weight k-blocks of this CTA's units in execution order, up to NC k-blocks
+        // ahead of the decoding warps. Per k-block: one TMA for the packed codes, and for each of
+        // the NB block scales of the tile two asynchronous 4-byte copies into the slot's scale
+        // array: the aligned word that holds the u8 first-level entry (or the fp32 absmax) and
+        // the fp32 second-level scale. Nothing is waited for here, so the HBM latency of a
+        // k-block overlaps with the NC - 1 k-blocks before it.
+        // Entry e = i*32 + lane. Forward: weight row nb0 + e, block (nb0+e)*bpr + kb. Backward:
+        // k row e / CB of the k-block and column block e % CB: block (kb*64 + krow)*bpr + nb0/64 + c.
+        // Entries outside the weight read block 0: their products meet zero-filled activations or
+        // land in columns that are never stored, they only have to be finite.
+        constexpr int EPL = NB / 32;  // scale entries per lane and k-block
+        constexpr int CB = NB / 64;   // backward: 64-wide k_w blocks across this CTA's tile
+        int c = 0;          // slot of the code ring
+        uint32_t cph = 0;   // its phase
+        for (int u = pair; u < total_units && !fail; u += n_pairs) {
+            const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
+            const int nb0 = w.n0 + (int)rank * NB;
+            int cur_prob = -1, n_w_cur = 0, first_cur = 0, sh = 0;
+            bool nested_cur = false;
+            const uint8_t* ab = nullptr;
+            const float* a2p = nullptr;
+            uint32_t blk0[EPL];
+            uint32_t unit_ok = 0;  // forward: rows inside the weight; backward: columns inside it
+            for (int it = 0; it < w.nkb; ++it) {
+                const int kbg = w.kb_begin + it;
+                const int pi = TRANS_W ? find_problem(p, kbg) : w.prob;
+                if (pi != cur_prob) {
+                    const GemmProblem& pr = p.prob[pi];
+                    cur_prob = pi;
+                    ab = static_cast<const uint8_t*>(pr.absmax);
+                    a2p = pr.absmax2;
+                    sh = pr.nested_shift;
+                    nested_cur = pr.nested != 0;
+                    n_w_cur = pr.n_w;
+                    first_cur = pr.first;
+                    unit_ok = 0;
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) {
+                        const int e = i * 32 + lane;
+                        if (!TRANS_W) {
+                            blk0[i] = (uint32_t)(nb0 + e) * (uint32_t)blocks_per_row;
+                            if (nb0 + e < n_w_cur) unit_ok |= 1u << i;
+                        } else {
+                            blk0[i] = (uint32_t)(e / CB) * (uint32_t)blocks_per_row +
+                                      (uint32_t)((nb0 >> 6) + e % CB);
+                            if (nb0 + (e % CB) * 64 < p.k_w) unit_ok |= 1u << i;
+                        }
+                    }
+                }
+                const int kb = TRANS_W ? kbg - first_cur : kbg;
+                if (!mbar_wait(bar_empty_c(c), cph ^ 1u, abort_flag)) { fail = 7; break; }
+                if (lane == 0) { const uint32_t unit_iter2 = (u == pair) ? 0u : 1u; NF4_TRACE2(6, it); }
+                if (lane == 0) {
+                    const uint32_t dst = smem_base + L::CODES_OFF + (uint32_t)c * L::C_BYTES;
+                    if (L::TABLES > 1) sts32(smem_base + L::META_OFF + 4u * c, (uint32_t)pi);
+                    mbar_arrive_expect_tx(bar_full_c(c), L::C_BYTES + (p.prepared ? NB * 2 : 0));
+                    if (TRANS_W) tma_load_2d(dst, &maps.codes[pi], nb0 / 2, kb * BK, bar_full_c(c));
+                    else         tma_load_2d(dst, &maps.codes[pi], kb * (BK / 2), nb0, bar_full_c(c));
+                    if (p.prepared) {
+                        // ready-made fp16 scales of the tile: forward NB rows of column kb,
+                        // backward 64 rows x CB column blocks
+                        const uint32_t sd = smem_base + L::SCALE_OFF + (uint32_t)c * L::S_BYTES;
+                        if (TRANS_W) tma_load_2d(sd, &maps.scales[pi], kb * BK, nb0 >> 6, bar_full_c(c));
+                        else         tma_load_2d(sd, &maps.scales[pi], nb0, kb, bar_full_c(c));
+                    }
+                }
+                if (p.prepared) {
+                    mbar_arrive(bar_full_c(c));  // (the barrier counts one arrival per lane)
+                    if (++c == NC) { c = 0; cph ^= 1u; }
+                    continue;
+                }
+                const uint32_t step =
+                    TRANS_W ? (uint32_t)kb * (uint32_t)(BK * blocks_per_row) : (uint32_t)kb;
+                const uint32_t sdst = smem_base + L::SCALE_OFF + (uint32_t)c * L::S_BYTES + 8u * lane;
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    bool ok = (unit_ok >> i) & 1u;
+                    if (TRANS_W && kb * BK + (i * 32 + lane) / CB >= n_w_cur) ok = false;
+                    const uint32_t blk = ok ? blk0[i] + step : 0u;
+                    if (nested_cur) {
+                        const uintptr_t a = reinterpret_cast<uintptr_t>(ab + blk) & ~(uintptr_t)3;
+                        cp_async_4(sdst + 256u * i, reinterpret_cast<const void*>(a));
+                        const uint32_t b2 = sh >= 0 ? (blk >> sh)
+                                                    : (blk / (uint32_t)p.prob[pi].nested_blocksize);
+                        cp_async_4(sdst + 256u * i + 4u, a2p + b2);
+                    } else {
+                        cp_async_4(sdst + 256u * i, reinterpret_cast<const float*>(ab) + blk);
+                    }
+                }
+                cp_async_arrive_noinc(bar_full_c(c));
+                if (lane == 0) { const uint32_t unit_iter2 = (u == pair) ? 0u : 1u; NF4_TRACE2(2, it); }
+                if (++c == NC) { c = 0; cph ^= 1u; }
+            }
+        }
+        // (every copy issued here is consumed by the decoding warps before the CTA ends)
     } else {
         // ------------------------------------------------------------------ decode producers
-        const int pt = threadIdx.x;  // 0..511: WORDS code words (8 weights each) per k-block
+        const int pt = threadIdx.x % DECODE_THREADS;  // WORDS code words (8 weights each) per k-block
+        const int group = warp / DW;                  // takes the ring positions g % GROUPS == group
         RegLut lut;
         int lut_prob = -1;  // problem whose 16-entry table is currently held in registers
+        // with it: whether its absmax is double-quantised, the offset, where its second-level
+        // table sits in shared memory, and the low address bits of its u8 absmax array
+        bool nested_p = false;
+        float off_val = 0.f;
+        uint32_t tab_off = 0, ab_low = 0;
         auto load_lut = [&](int pi) {
+            const GemmProblem& pr = p.prob[pi];
             uint16_t bits[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-                bits[i] = __half_as_ushort(__float2half_rn(__ldg(p.prob[pi].code16 + i)));
+                bits[i] = __half_as_ushort(__float2half_rn(__ldg(pr.code16 + i)));
             lut = make_reg_lut(bits);
             lut_prob = pi;
+            nested_p = pr.nested != 0;
+            off_val = nested_p ? __ldg(pr.offset) : 0.f;
+            tab_off = L::TABLES > 1 ? (uint32_t)pi * 256u : 0u;
+            ab_low = (uint32_t)(reinterpret_cast<uintptr_t>(pr.absmax) & 3u);
         };
         load_lut(0);
 
@@ -472,8 +692,14 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
 #pragma unroll
             for (int i = 0; i < WORDS; ++i)
                 dst_off[i] = smem_base + L::A_BYTES + dst + (uint32_t)(((chunk0 + i) ^ (row & 7)) << 4);
-            src_off += smem_base + L::A_BYTES + L::W_BYTES;
+            src_off += smem_base + L::CODES_OFF;
         }
+        // this thread's block scale inside a k-block's scale array (see the AUX warp)
+        const uint32_t scale_off = smem_base + L::SCALE_OFF +
+            8u * (uint32_t)(TRANS_W ? row * (NB / 64) + (klocal >> 6) : row);
+        // ... and in the ready-made form: forward [NB] halves, backward [NB / 64][64] halves
+        const uint32_t prep_off = smem_base + L::SCALE_OFF +
+            2u * (uint32_t)(TRANS_W ? (klocal >> 6) * 64 + row : row);
         // epilogue geometry: TMEM lane quadrant, column share, private 4 KB staging area inside
         // the weight slots of the ring (free while the accumulators are drained)
         const int q = warp & 3;
@@ -483,91 +709,80 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                                  L::A_BYTES + (uint32_t)(warp % L::WARPS_PER_W_SLOT) * 4096u;
         const bool split = p.splits > 1;
 
-        uint32_t g = 0;
+        uint32_t g = 0;   // position in the operand ring
+        uint32_t cslot = 0, cphase = 0;  // position in the code ring
         uint32_t unit_iter = 0;
         for (int u = pair; u < total_units; u += n_pairs, ++unit_iter) {
             const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
             NF4_TRACE(0);
             const int nb0 = w.n0 + (int)rank * NB;  // first weight-tile column of this CTA
+            // Byte of the copied absmax word that holds this thread's first-level entry: block
+            // index mod 4 (plus the array's own misalignment). Forward: block (nb0+row)*bpr + kb;
+            // backward: (kb*64+row)*bpr + (nb0 + klocal)/64, where the kb term is a multiple of 4.
+            const uint32_t sel_geo = TRANS_W
+                ? (uint32_t)row * (uint32_t)blocks_per_row + (uint32_t)((nb0 + klocal) >> 6)
+                : (uint32_t)(nb0 + row) * (uint32_t)blocks_per_row + (uint32_t)w.kb_begin;
 
-            // First-level scale of this thread's piece in step `it` (32-bit indices: n_blocks < 2^31).
-            //   forward : block (nb0 + row) * bpr + kb           valid while nb0 + row < N_w
-            //   backward: block (kb*64 + row) * bpr + kw / 64    valid while kb*64 + row < N_w, kw < K_w
-            // with kb counted inside the problem that owns the step. The raw first-level entry (u8
-            // code or fp32 bits), the second-level scale and the offset are fetched one step ahead.
-            const int kw = nb0 + klocal;  // backward: first k_w column of this thread's piece
-            const uint32_t blk_base = TRANS_W
-                ? (uint32_t)row * (uint32_t)blocks_per_row + (uint32_t)(kw >> 6)
-                : (uint32_t)(nb0 + row) * (uint32_t)blocks_per_row;
-            const uint32_t blk_per_kb = (uint32_t)BK * (uint32_t)blocks_per_row;
-            uint32_t raw_q = 0;
-            float raw_a2 = 0.f, raw_off = 0.f;
-            int raw_prob = 0;
-            bool raw_ok = false;
-            auto fetch_scale = [&](int it) {
-                const int kbg = w.kb_begin + it;
-                const int pi = TRANS_W ? find_problem(p, kbg) : w.prob;
-                const GemmProblem& pr = p.prob[pi];
-                const int kb = TRANS_W ? kbg - pr.first : kbg;
-                uint32_t blk;
-                bool ok;
-                if (!TRANS_W) {
-                    blk = blk_base + (uint32_t)kb;
-                    ok = nb0 + row < pr.n_w;
-                } else {
-                    blk = blk_base + (uint32_t)kb * blk_per_kb;
-                    ok = kw < p.k_w && kb * BK + row < pr.n_w;
-                }
-                raw_ok = ok;
-                raw_prob = pi;
-                if (ok) {
-                    if (pr.nested) {
-                        raw_q = __ldg(static_cast<const uint8_t*>(pr.absmax) + blk);
-                        const uint32_t b2 = pr.nested_shift >= 0
-                            ? (blk >> pr.nested_shift) : (blk / (uint32_t)pr.nested_blocksize);
-                        raw_a2 = __ldg(pr.absmax2 + b2);
-                        raw_off = __ldg(pr.offset);
-                    } else {
-                        raw_q = __float_as_uint(__ldg(static_cast<const float*>(pr.absmax) + blk));
-                    }
-                }
-            };
-            if (!fail && warp < DW) fetch_scale(0);
-
-            for (int it = 0; warp < DW && it < w.n_iter && !fail; ++it, ++g) {
+            for (int it = 0; it < w.n_iter && !fail; ++it, ++g) {
+                const uint32_t c = cslot;  // code-ring slot and phase of this step (weight steps)
+                const uint32_t cph = cphase;
+                if (it < w.nkb && ++cslot == NC) { cslot = 0; cphase ^= 1u; }
+                if (GROUPS > 1 && (int)(g % GROUPS) != group) continue;
                 const int s = (int)(g % STAGES);
                 const uint32_t ph = (g / STAGES) & 1u;
                 const uint32_t stage_off = (uint32_t)s * L::STAGE_BYTES;
                 if (it < w.nkb) {
-                    float sc;
-                    if (!raw_ok)
-                        sc = 0.f;  // rows / columns outside the weight contribute zeros
-                    else if (p.prob[raw_prob].nested)
-                        sc = nested_scale(table2[(L::TABLES > 1 ? raw_prob * 256 : 0) + raw_q], raw_a2,
-                                          raw_off);
-                    else
-                        sc = __uint_as_float(raw_q);
-                    const __half2 scale2 = __float2half2_rn(sc);
-                    if (raw_prob != lut_prob) load_lut(raw_prob);
-                    if (it + 1 < w.nkb) fetch_scale(it + 1);
-                    if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 4; break; }
-                    if (threadIdx.x == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(1, it); }
+                    // codes and scale of this k-block from the code ring; expand into registers,
+                    // hand the ring slot back, then wait for the operand slot to be free
+                    if (!warp_wait(bar_full_c(c), cph)) { fail = 4; break; }
+                    if (pt == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(1, it); }
+                    uint4 v[WORDS];
                     if (!(p.debug & 1)) {
-                        if (WORDS == 4) {
-                            const uint4 cw = lds128(src_off + stage_off);
-                            sts128(dst_off[0] + stage_off, decode_word_reg(cw.x, lut, scale2));
-                            sts128(dst_off[1] + stage_off, decode_word_reg(cw.y, lut, scale2));
-                            sts128(dst_off[WORDS - 2] + stage_off, decode_word_reg(cw.z, lut, scale2));
-                            sts128(dst_off[WORDS - 1] + stage_off, decode_word_reg(cw.w, lut, scale2));
-                        } else {
-                            const uint2 cw = lds64(src_off + stage_off);
-                            sts128(dst_off[0] + stage_off, decode_word_reg(cw.x, lut, scale2));
-                            sts128(dst_off[1] + stage_off, decode_word_reg(cw.y, lut, scale2));
+                        if (L::TABLES > 1 && p.n_prob > 1) {
+                            const int pi = (int)lds32(smem_base + L::META_OFF + 4u * c);
+                            if (pi != lut_prob) load_lut(pi);
                         }
+                        __half2 scale2;
+                        if (p.prepared) {
+                            const uint32_t h = lds16(prep_off + c * L::S_BYTES);
+                            const uint32_t hh = __byte_perm(h, 0u, 0x1010u);
+                            scale2 = *reinterpret_cast<const __half2*>(&hh);
+                        } else {
+                            const uint2 raw = lds64u(scale_off + c * L::S_BYTES);
+                            float sc;
+                            if (nested_p) {
+                                const uint32_t sel =
+                                    (sel_geo + ab_low + (TRANS_W ? 0u : (uint32_t)it)) & 3u;
+                                const uint32_t q8 = __byte_perm(raw.x, 0u, 0x4440u + sel);
+                                sc = nested_scale(table2[tab_off + q8], __uint_as_float(raw.y), off_val);
+                            } else {
+                                sc = __uint_as_float(raw.x);
+                            }
+                            scale2 = __float2half2_rn(sc);
+                        }
+                        if (WORDS == 4) {
+                            const uint4 cw = lds128(src_off + c * L::C_BYTES);
+                            v[0] = decode_word_reg(cw.x, lut, scale2);
+                            v[1] = decode_word_reg(cw.y, lut, scale2);
+                            v[WORDS - 2] = decode_word_reg(cw.z, lut, scale2);
+                            v[WORDS - 1] = decode_word_reg(cw.w, lut, scale2);
+                        } else {
+                            const uint2 cw = lds64(src_off + c * L::C_BYTES);
+                            v[0] = decode_word_reg(cw.x, lut, scale2);
+                            v[1] = decode_word_reg(cw.y, lut, scale2);
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_empty_c(c));
+                    if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
+                    if (pt == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(7, it); }
+                    if (!(p.debug & 1)) {
+#pragma unroll
+                        for (int i = 0; i < WORDS; ++i) sts128(dst_off[i] + stage_off, v[i]);
                     }
                 } else {
                     // K extension operands, unswizzled core-matrix layout (see the MMA branch).
-                    if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 4; break; }
+                    if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
                     const GemmProblem& pe = p.prob[TRANS_W ? ext_problem(p, it - w.nkb) : w.prob];
                     const uint32_t abase = smem_base + stage_off;
                     const uint32_t wbase = abase + L::A_BYTES;
@@ -612,13 +827,12 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                     if (CG == 2) mbar_arrive_cluster(lead_full_w0 + 8u * s);
                     else         mbar_arrive(bar_full_w(s));
                 }
-                if (threadIdx.x == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(2, it); }
             }
 
             // -------------------------------------------------------------- epilogue of the unit
             NF4_TRACE(1);
             if (!fail) {
-                if (!mbar_wait(bar_tmem_full, unit_iter & 1u, abort_flag)) fail = 5;
+                if (!warp_wait_commit(bar_tmem_full, unit_iter & 1u)) fail = 5;
             }
             NF4_TRACE(2);
             const GemmProblem& po = p.prob[w.prob];  // backward: problem 0 carries the output
@@ -678,7 +892,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                             const uint4 v = lds128(staging + rr * 128 + ((rd_chunk ^ (rr & 7)) << 4));
                             const long long grow = grow0 + rr;
                             const int colg = w.n0 + ch0 * 32 + rd_chunk * 8;
-                            if (grow < p.m && colg < n_out && !(p.debug & 64)) {
+                            if (grow < p.m && colg < n_out) {
                                 __half* dst = po.out + grow * po.ld_out + colg;
                                 if (vec_ok && colg + 8 <= n_out) {
                                     *reinterpret_cast<uint4*>(dst) = v;
@@ -937,6 +1151,7 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
     GemmParams p;
     p.n_prob = ga.count;
     p.n_ext = 0;
+    bool prepared = true;  // only if every weight of the group brings its scale table
     for (int i = 0; i < ga.count; ++i) {
         const GemmArgs& a = ga.item[i];
         if (TRANS_W || i == 0) {
@@ -956,6 +1171,19 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
                           (uint64_t)a.n_w, (uint64_t)k_w / 2, BK / 2, L::NB,
                           CU_TENSOR_MAP_SWIZZLE_NONE);
         if (!ok) { *why = "cuTensorMapEncodeTiled(codes)"; return cudaErrorInvalidValue; }
+        if (a.scales16 == nullptr) prepared = false;
+        if (a.scales16 != nullptr) {
+            // table [K_w / 64][N_w] fp16: forward box = NB rows of one column block, backward box =
+            // 64 rows x the CTA's column blocks
+            const bool oks = TRANS_W
+                ? make_map_2d(&maps.scales[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.scales16,
+                              (uint64_t)a.n_w, (uint64_t)k_w / 64, (uint64_t)a.n_w * 2, 64, L::NB / 64,
+                              CU_TENSOR_MAP_SWIZZLE_NONE)
+                : make_map_2d(&maps.scales[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.scales16,
+                              (uint64_t)a.n_w, (uint64_t)k_w / 64, (uint64_t)a.n_w * 2, L::NB, 1,
+                              CU_TENSOR_MAP_SWIZZLE_NONE);
+            if (!oks) { *why = "cuTensorMapEncodeTiled(scales)"; return cudaErrorInvalidValue; }
+        }
         GemmProblem& q = p.prob[i];
         q.absmax = a.absmax; q.code2 = a.code2; q.absmax2 = a.absmax2; q.offset = a.offset;
         q.code16 = a.code16; q.bias = a.bias; q.ext_a = a.ext_a; q.ext_b = a.ext_b;
@@ -971,10 +1199,13 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
         q.pad = 0;
         if (a.ext_a != nullptr) ++p.n_ext;
     }
+    for (int i = 0; i < MAXP; ++i)
+        if (!prepared || i >= ga.count) maps.scales[i] = maps.codes[0];  // never dereferenced
     for (int i = ga.count; i < MAXP; ++i) {
         p.prob[i] = p.prob[0];
         maps.codes[i] = maps.codes[0];
     }
+    p.prepared = prepared ? 1 : 0;
     if (!TRANS_W)
         for (int i = 1; i < MAXP; ++i) maps.act[i] = maps.act[0];
     else
@@ -1057,7 +1288,9 @@ cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, cons
     for (int i = 0; i < ga.count; ++i) n_w[i] = ga.item[i].n_w;
     const GemmArgs& a = ga.item[0];
     const GemmPlan pl = plan_gemm_group(a.m, n_w, ga.count, a.k_w, a.trans_w, a.sm_count);
-    const bool dw8 = (debug_flags() & 32) != 0;  // tuning: 8 decoding warps with twice the work
+    // Two alternating groups of 8 decoding warps measured faster for the forward form, one group
+    // of 16 for the backward form (NF4B200_DEBUG bit 5 swaps the choice, for tuning).
+    const bool dw8 = ((debug_flags() & 32) != 0) != !a.trans_w;
     if (pl.cg == 2 && pl.nacc == 2) {
         if (dw8)
             return a.trans_w ? launch_cfg<2, 2, true, 4, 8, MAXP>(ga, pl, stream, why)

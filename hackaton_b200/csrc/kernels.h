@@ -26,6 +26,12 @@ struct DequantArgs {
 
 cudaError_t launch_dequant(const DequantArgs& a, cudaStream_t stream);
 
+// fp16 block-scale table [n_cols / 64][n_rows] of a blocksize-64 weight (see dequant.cu).
+cudaError_t launch_prepare_scales(const void* absmax, const float* code2, const float* absmax2,
+                                  const float* offset, long long n_rows, long long bpr, int nested,
+                                  int nested_blocksize, __half* out, int sm_count,
+                                  cudaStream_t stream);
+
 // Fused dequant-GEMM. trans_w == false: out[M, N_w] = act[M, K_w] . W^T (forward).
 // trans_w == true: out[M, K_w] = act[M, N_w] . W (input gradient).
 struct GemmArgs {
@@ -35,6 +41,7 @@ struct GemmArgs {
     const float* absmax2;
     const float* offset;
     const float* code16;
+    const __half* scales16;  // optional ready-made block scales [k_w / 64][n_w] (fp16), or null
     long long n_w, k_w;
     int nested;
     int nested_blocksize;

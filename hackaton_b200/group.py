@@ -65,7 +65,7 @@ def _refs(items):
     for packed, state in items:
         packed = packed.reshape(-1)
         _require(packed, state)
-        refs.append(weight_ref(packed, state))
+        refs.append(weight_ref(packed, state).prepare())
     cols = refs[0].cols
     if any(r.cols != cols for r in refs):
         raise ValueError("grouped projections must have the same number of input features")

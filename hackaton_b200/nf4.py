@@ -15,6 +15,7 @@ Same names, arguments and meaning as the reference's solution/nf4.py:
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -55,6 +56,11 @@ def can_dequantize(packed, state):
                 and isinstance(getattr(state2, "code", None), torch.Tensor)
                 and state2.code.numel() == 256 and getattr(state2, "blocksize", 0) > 0)
     return absmax.dtype == torch.float32
+
+
+# Fused GEMM calls fetch ready-made fp16 block scales (built once per weight) instead of gathering
+# absmax / absmax2 on every call. Same results bit for bit; NF4B200_NO_PREPARED=1 turns it off.
+PREPARED_SCALES = os.environ.get("NF4B200_NO_PREPARED", "0") != "1"
 
 
 class WeightRef:
@@ -98,6 +104,27 @@ class WeightRef:
         self.keep = keep
         self.key = (packed.data_ptr(), state.absmax.data_ptr(), nested, rows, cols)
         self.rows, self.cols = rows, cols
+        self.scales16 = None
+
+    def prepare(self):
+        """Builds, once, the fp16 block-scale table the fused GEMM can fetch by TMA (see
+        nf4b200_prepare_scales in include/nf4b200.h) and hooks it into the descriptor. Weights
+        are frozen in QLoRA, so the table stays valid for the life of the quantisation state."""
+        if self.scales16 is not None or not PREPARED_SCALES:
+            return self
+        need = int(_lib.lib().nf4b200_scales16_bytes(self.rows, self.cols))
+        if need == 0 or self.struct.blocksize != 64:
+            return self
+        device = self.keep[0].device
+        table = torch.empty(need // 2, dtype=torch.float16, device=device)
+        with torch.cuda.device(device):
+            _lib.check(_lib.lib().nf4b200_prepare_scales(ctypes.byref(self.struct), table.data_ptr(),
+                                                         _stream_ptr(device)))
+            if not torch.cuda.is_current_stream_capturing():
+                torch.cuda.current_stream(device).synchronize()  # later calls may use other streams
+        self.scales16 = table
+        self.struct.scales16 = table.data_ptr()
+        return self
 
 
 def weight_ref(packed, state) -> WeightRef:
@@ -177,7 +204,7 @@ def linear_forward(x, packed, bias, state, xa=None, lora_b=None):
     """y = x . Wᵀ (+ bias) (+ xa . lora_bᵀ) through the fused kernel. x: fp16 [..., K]."""
     packed = packed.reshape(-1)
     _require(packed, state)
-    ref = weight_ref(packed, state)
+    ref = weight_ref(packed, state).prepare()
     if x.dtype != torch.float16:
         raise TypeError(f"hackaton_b200: the fused NF4 linear computes in fp16, got {x.dtype}")
     if x.shape[-1] != ref.cols:
@@ -203,7 +230,7 @@ def linear_backward_dx(grad_output, packed, state, u=None, lora_a=None):
     """dx = dy . W (+ u . lora_a) through the fused kernel. dy: fp16 [..., N]."""
     packed = packed.reshape(-1)
     _require(packed, state)
-    ref = weight_ref(packed, state)
+    ref = weight_ref(packed, state).prepare()
     if grad_output.dtype != torch.float16:
         raise TypeError(f"hackaton_b200: the fused NF4 linear computes in fp16, got {grad_output.dtype}")
     g2 = _rows_view(grad_output, ref.rows)

@@ -47,6 +47,7 @@ typedef struct nf4b200_weight {
     int32_t nested_blocksize; /* scales per second-level scale (256) */
     int32_t nested;         /* 1: double-quantised scales, 0: flat fp32 scales */
     int32_t reserved;
+    const void* scales16;   /* optional: table made by nf4b200_prepare_scales, else NULL */
 } nf4b200_weight;
 
 /* Device / build facts. */
@@ -59,6 +60,20 @@ int nf4b200_query(int device, nf4b200_props* out);
 
 /* Message for the last non-zero status returned on this thread ("" if none). */
 const char* nf4b200_last_error(void);
+
+/*
+ * Optional set-up step for the fused GEMM entry points. Writes the block scales of `w` (the
+ * (double-)dequantised absmax, rounded to fp16 exactly as the GEMM's decode rounds them) as an
+ * fp16 table [n_cols / 64][n_rows] into `scales16` (nf4b200_scales16_bytes(...) bytes, 16-byte
+ * aligned, n_rows % 8 == 0). A weight descriptor whose `scales16` field points at that table makes
+ * nf4b200_linear_fwd / _bwd_dx (and the group forms) fetch ready-made scales with one small TMA
+ * copy per 64-deep step instead of gathering absmax / absmax2 themselves; results are bit-identical
+ * either way. The table must be rebuilt if absmax / absmax2 / offset change. The reference has no
+ * counterpart: its kernel re-derives the scales on every call (solution/nf4.py:40-52).
+ * `w->scales16` is ignored by this call and by nf4b200_dequant.
+ */
+int64_t nf4b200_scales16_bytes(int64_t n_rows, int64_t n_cols); /* 0 if the shape is not eligible */
+int nf4b200_prepare_scales(const nf4b200_weight* w, void* scales16, void* stream);
 
 /*
  * Reads and clears the device-side status word of the current device (synchronises the device).

@@ -42,7 +42,8 @@ def test_binding_covers_the_header():
 def test_struct_layout_matches_header():
     from hackaton_b200 import _lib
 
-    assert ctypes.sizeof(_lib.Weight) == 6 * 8 + 2 * 8 + 4 * 4
+    assert ctypes.sizeof(_lib.Weight) == 6 * 8 + 2 * 8 + 4 * 4 + 8
+    assert _lib.Weight.scales16.offset == 80
     assert ctypes.sizeof(_lib.Props) == 4 * 4 + 8
 
 

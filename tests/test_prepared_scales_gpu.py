@@ -1,0 +1,120 @@
+"""The fused GEMM has two ways to get its block scales: a table built once per weight
+(nf4b200_prepare_scales, the default of the Python surface) and a per-call gather of absmax /
+absmax2. Both must give the same bits, and the table itself must equal the oracle's scales."""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from tests.util import oracle_weight, synthetic_weight
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture
+def gather_only(monkeypatch):
+    from hackaton_b200 import nf4
+    monkeypatch.setattr(nf4, "PREPARED_SCALES", False)
+
+
+def _oracle_scales(state, rows, cols):
+    """fp16 block scales [K/64][N] from the oracle's flattened absmax."""
+    from oracle import nf4_oracle
+    if getattr(state, "nested", False):
+        flat = nf4_oracle.flatten_absmax(
+            state.absmax.cpu().numpy(), state.state2.code.cpu().numpy(),
+            state.state2.absmax.cpu().numpy(), float(state.offset.cpu()), state.state2.blocksize)
+    else:
+        flat = state.absmax.cpu().numpy()
+    flat = np.asarray(flat, dtype=np.float32)
+    return np.ascontiguousarray(flat.reshape(rows, cols // 64).T).astype(np.float16)
+
+
+@pytest.mark.parametrize("nested", [True, False])
+@pytest.mark.parametrize("rows,cols", [(256, 1536), (1536, 8960), (8, 64)])
+def test_table_matches_oracle(rows, cols, nested):
+    from hackaton_b200 import _lib
+    from hackaton_b200.nf4 import weight_ref
+
+    packed, state = synthetic_weight(rows, cols, nested, seed=3, device="cuda")
+    ref = weight_ref(packed.reshape(-1), state)
+    need = _lib.lib().nf4b200_scales16_bytes(rows, cols)
+    assert need == rows * (cols // 64) * 2
+    table = torch.zeros(need // 2, dtype=torch.float16, device="cuda")
+    w = _lib.Weight.from_buffer_copy(ref.struct)
+    w.scales16 = None
+    _lib.check(_lib.lib().nf4b200_prepare_scales(ctypes.byref(w), table.data_ptr(), None))
+    torch.cuda.synchronize()
+    want = _oracle_scales(state, rows, cols)
+    got = table.cpu().numpy().reshape(cols // 64, rows)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def test_ineligible_shapes():
+    from hackaton_b200 import _lib
+    assert _lib.lib().nf4b200_scales16_bytes(12, 64) == 0     # rows not a multiple of 8
+    assert _lib.lib().nf4b200_scales16_bytes(16, 96) == 0     # columns not a multiple of 64
+
+
+@pytest.mark.parametrize("m,rows,cols", [(2048, 1536, 1536), (300, 264, 512), (64, 8960, 1536),
+                                         (2048, 1536, 8960)])
+@pytest.mark.parametrize("nested", [True, False])
+def test_both_paths_same_bits(m, rows, cols, nested):
+    from hackaton_b200 import nf4
+
+    torch.manual_seed(m + rows)
+    x = torch.randn(m, cols, device="cuda").half()
+    dy = torch.randn(m, rows, device="cuda").half()
+    out = {}
+    for prepared in (True, False):
+        nf4.PREPARED_SCALES = prepared
+        try:
+            packed, state = synthetic_weight(rows, cols, nested, seed=5, device="cuda")
+            y = nf4.linear_forward(x, packed, None, state)
+            dx = nf4.linear_backward_dx(dy, packed, state)
+            ref = nf4.weight_ref(packed.reshape(-1), state)
+            assert (ref.scales16 is not None) == prepared
+            out[prepared] = (y, dx)
+        finally:
+            nf4.PREPARED_SCALES = True
+    assert torch.equal(out[True][0], out[False][0])
+    assert torch.equal(out[True][1], out[False][1])
+
+
+def test_gather_path_vs_oracle(gather_only):
+    """The per-call gather path against the CPU oracle (the default path is covered by the other
+    parity tests)."""
+    from hackaton_b200 import nf4
+    from oracle import nf4_oracle
+
+    m, rows, cols = 200, 520, 1024
+    packed, state = synthetic_weight(rows, cols, True, seed=9, device="cuda")
+    torch.manual_seed(1)
+    x = torch.randn(m, cols, device="cuda").half()
+    dy = torch.randn(m, rows, device="cuda").half()
+    y = nf4.linear_forward(x, packed, None, state)
+    dx = nf4.linear_backward_dx(dy, packed, state)
+    assert nf4.weight_ref(packed.reshape(-1), state).scales16 is None
+    w = oracle_weight(packed, state)
+    assert nf4_oracle.max_rel_err(y.cpu(), nf4_oracle.linear_fwd(x.cpu(), w)) <= 1e-2
+    assert nf4_oracle.max_rel_err(dx.cpu(), nf4_oracle.linear_bwd(dy.cpu(), w)) <= 1e-2
+
+
+def test_group_without_tables(gather_only):
+    from hackaton_b200.group import linear_forward_group, linear_backward_dx_group
+    from hackaton_b200 import nf4
+
+    m, cols = 512, 1536
+    torch.manual_seed(2)
+    x = torch.randn(m, cols, device="cuda").half()
+    ws = [synthetic_weight(r, cols, True, seed=20 + i, device="cuda") for i, r in enumerate((1536, 256, 256))]
+    ys = linear_forward_group(x, ws)
+    singles = [nf4.linear_forward(x, p, None, s) for p, s in ws]
+    for a, b in zip(ys, singles):
+        assert torch.equal(a, b)
+    dys = [torch.randn(m, r, device="cuda").half() for r in (1536, 256, 256)]
+    dx = linear_backward_dx_group(dys, ws)
+    want = sum(nf4.linear_backward_dx(d, p, s).float() for d, (p, s) in zip(dys, ws))
+    assert (dx.float() - want).abs().max() <= 2e-2 * want.abs().max()
