@@ -858,7 +858,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                     for (int b = 0; b < CHUNKS_PER_GRP / 2; ++b) {
                         const int t0 = grp * CHUNKS_PER_GRP + 2 * b;
                         const int acc = t0 / (BN / 32), ch0 = t0 % (BN / 32);
-#pragma unroll
+#pragma unroll 1
                         for (int h = 0; h < 2; ++h) {
                             uint32_t r[32];
                             tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN +
