@@ -233,9 +233,23 @@ def step_functional(layer, acts):
     return outs
 
 
-# kernels of this library per step: 4 GEMM launches + 3 split-K reductions (q/k/v outputs) + 1 (o)
-# + 1 (down) forward; 4 GEMM launches + 3 reductions backward; 4 lora_down; 4 lora_grad
-KERNELS_PER_STEP = 4 + 5 + 4 + 3 + 4 + 4
+def kernels_per_step(shapes, m):
+    """Kernels of this library that one step launches: a fused GEMM per group and direction, one
+    split-K reduction per output wherever the library's plan slices the contraction (it does when
+    the call needs scratch), and lora_down / lora_grad twice each per LoRA projection."""
+    import ctypes
+
+    from hackaton_b200 import _lib
+
+    n = 0
+    for group in GROUPS:
+        rows = [shapes[g][0] for g in group]
+        cols = shapes[group[0]][1]
+        arr = (ctypes.c_int64 * len(rows))(*rows)
+        for backward in (0, 1):
+            need = int(_lib.lib().nf4b200_workspace_bytes_group(len(rows), arr, cols, m, backward))
+            n += 1 + (0 if need <= 0 else (1 if backward else len(rows)))
+    return n + 4 * len(LORA_ON)
 
 
 def step_autograd(layer, acts_dev):
@@ -585,7 +599,7 @@ def run_single(args):
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": 4, "steps": e2e_steps,
                 "ms_per_step": e2e_wall / e2e_steps * 1e3},
-        "gpu_launches": KERNELS_PER_STEP * args.steps, "clocks": clocks,
+        "gpu_launches": kernels_per_step(shapes, m) * args.steps, "clocks": clocks,
     }
     print(json.dumps(line), flush=True)
 

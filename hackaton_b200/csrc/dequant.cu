@@ -13,6 +13,7 @@
 
 #include "decode.cuh"
 #include "kernels.h"
+#include "ptx.cuh"
 
 namespace nf4 {
 
@@ -60,6 +61,8 @@ nf4_dequant_kernel(const uint32_t* __restrict__ codes, const void* __restrict__ 
                    const float* __restrict__ offset_ptr, const float* __restrict__ code16,
                    T* __restrict__ out, long long n_words, int words_per_block,
                    int nested_blocksize) {
+    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
+    grid_dep_launch();
     __shared__ float table[16];
     __shared__ float table2[256];
     if (threadIdx.x < 16) table[threadIdx.x] = code16[threadIdx.x];
@@ -116,15 +119,16 @@ static cudaError_t launch_t(const DequantArgs& a, cudaStream_t stream) {
     if (blocks < 1) blocks = 1;
     const int wpb = a.blocksize / 8;
     if (a.nested) {
-        nf4_dequant_kernel<T, true><<<(unsigned)blocks, DEQ_THREADS, 0, stream>>>(
-            static_cast<const uint32_t*>(a.codes), a.absmax, a.code2, a.absmax2, a.offset,
-            a.code16, static_cast<T*>(a.out), n_words, wpb, a.nested_blocksize);
-    } else {
-        nf4_dequant_kernel<T, false><<<(unsigned)blocks, DEQ_THREADS, 0, stream>>>(
-            static_cast<const uint32_t*>(a.codes), a.absmax, nullptr, nullptr, nullptr, a.code16,
-            static_cast<T*>(a.out), n_words, wpb, 1);
+        return launch_pdl(nf4_dequant_kernel<T, true>, dim3((unsigned)blocks), dim3(DEQ_THREADS), 0,
+                          stream, static_cast<const uint32_t*>(a.codes), a.absmax, a.code2, a.absmax2,
+                          a.offset, a.code16, static_cast<T*>(a.out), n_words, wpb,
+                          a.nested_blocksize);
     }
-    return cudaGetLastError();
+    return launch_pdl(nf4_dequant_kernel<T, false>, dim3((unsigned)blocks), dim3(DEQ_THREADS), 0,
+                      stream, static_cast<const uint32_t*>(a.codes), a.absmax,
+                      static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
+                      static_cast<const float*>(nullptr), a.code16, static_cast<T*>(a.out), n_words,
+                      wpb, 1);
 }
 
 cudaError_t launch_dequant(const DequantArgs& a, cudaStream_t stream) {
@@ -144,6 +148,8 @@ prepare_scales_kernel(const void* __restrict__ absmax, const float* __restrict__
                       const float* __restrict__ absmax2, const float* __restrict__ offset,
                       long long n_rows, long long bpr, int nested, int nested_blocksize,
                       __half* __restrict__ out) {
+    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
+    grid_dep_launch();
     const long long total = n_rows * bpr;
     const float off = nested ? __ldg(offset) : 0.f;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -169,9 +175,8 @@ cudaError_t launch_prepare_scales(const void* absmax, const float* code2, const 
     const long long cap = (long long)sm_count * 8;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    prepare_scales_kernel<<<(unsigned)blocks, 256, 0, stream>>>(absmax, code2, absmax2, offset, n_rows,
-                                                               bpr, nested, nested_blocksize, out);
-    return cudaGetLastError();
+    return launch_pdl(prepare_scales_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, absmax,
+                      code2, absmax2, offset, n_rows, bpr, nested, nested_blocksize, out);
 }
 
 }  // namespace nf4

@@ -354,7 +354,11 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
             tmem_relinquish();
         }
     }
-    if (threadIdx.x < 256) {
+    // Everything above touched only shared memory, TMEM and kernel parameters, and may have run
+    // while the previous kernel of the stream was still draining; global memory comes after this.
+    grid_dep_wait();
+    grid_dep_launch();
+    if (threadIdx.x < 256 && !p.prepared) {
         for (int i = 0; i < L::TABLES && i < p.n_prob; ++i)
             if (p.prob[i].nested) table2[i * 256 + threadIdx.x] = p.prob[i].code2[threadIdx.x];
     }
@@ -976,6 +980,8 @@ __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ ws, long long m, long long n_out, long long ldp,
                      int splits, const __half* __restrict__ bias, __half* __restrict__ out,
                      long long ld_out, int vec_ok) {
+    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
+    grid_dep_launch();
     const long long groups_per_row = (n_out + 7) / 8;
     const long long total = m * groups_per_row;
     const size_t plane = (size_t)m * (size_t)ldp;
@@ -1064,6 +1070,15 @@ static bool make_map_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* ba
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = std::getenv("NF4B200_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on != 0;
+}
+
 static int debug_flags() {
     static int flags = -1;
     if (flags < 0) {
@@ -1089,8 +1104,7 @@ GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long
             force_splits = b;
         }
     }
-    const int rows = 128 * pl.cg * pl.nacc;
-    pl.m_tiles = (int)((m + rows - 1) / rows);
+    bool forced = (debug_flags() & 16) != 0 || std::getenv("NF4B200_PLAN") != nullptr;
     int n_tiles = 0, nkb = 0;
     size_t ws_floats = 0;
     for (int i = 0; i < count; ++i) {
@@ -1111,8 +1125,17 @@ GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long
     }
     pl.n_tiles = n_tiles;
     pl.nkb = nkb;
-    const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
     const int slots = sm_count / pl.cg;  // units that run at the same time
+    // Short contractions whose 512-row tiles would fill less than half of the pairs (q/k/v and o
+    // at 2048 tokens): 256-row tiles in a single wave, no split-K and no reduction pass, measured
+    // 2 to 8 us faster than slices + reduce up to 24 k-blocks; longer contractions keep the slices.
+    if (!forced && pl.cg == 2 && pl.nacc == 2 && nkb <= 24) {
+        const long long tiles2 = ((m + 511) / 512) * n_tiles, tiles1 = ((m + 255) / 256) * n_tiles;
+        if (tiles2 * 2 <= slots && tiles1 <= slots) pl.nacc = 1;
+    }
+    const int rows = 128 * pl.cg * pl.nacc;
+    pl.m_tiles = (int)((m + rows - 1) / rows);
+    const long long tiles = (long long)pl.m_tiles * pl.n_tiles;
     int splits = 1;
     if (tiles * 2 <= slots && nkb >= 8) {
         splits = (int)(slots / tiles);
@@ -1234,13 +1257,15 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
     cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
     cfg.dynamicSmemBytes = L::DYNAMIC_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CG;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = CG;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = CG == 2 ? 1 : 0;
+    cfg.numAttrs = CG == 2 ? 2 : 1;
 
     // Units that can be resident at once: one CTA per SM; pairs must sit in one GPC, so ask the
     // runtime how many clusters fit (once per configuration).
@@ -1271,10 +1296,10 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
             const long long cap = (long long)a0.sm_count * 8;
             if (blocks > cap) blocks = cap;
             const int vec_ok = (a.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15) == 0);
-            splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
-                p.prob[i].ws, m, n_out, p.prob[i].ldp, p.splits, TRANS_W ? nullptr : a.bias, a.out,
-                a.ld_out, vec_ok);
-            e = cudaGetLastError();
+            e = launch_pdl(splitk_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, stream,
+                           p.prob[i].ws, (long long)m, (long long)n_out, (long long)p.prob[i].ldp,
+                           p.splits, TRANS_W ? static_cast<const __half*>(nullptr) : a.bias, a.out,
+                           (long long)a.ld_out, vec_ok);
             if (e != cudaSuccess) { *why = "split-K reduce launch"; return e; }
         }
     }

@@ -8,6 +8,28 @@
 
 namespace nf4 {
 
+// True unless NF4B200_PDL=0: kernels are launched with programmatic stream serialization allowed, so
+// that a kernel's set-up overlaps the tail of its predecessor (every kernel of the library calls
+// griddepcontrol.wait before its first global-memory access).
+bool pdl_enabled();
+
+// <<<grid, block, smem, stream>>> with that attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 struct DequantArgs {
     const void* codes;
     const void* absmax;

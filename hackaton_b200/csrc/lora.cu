@@ -9,6 +9,7 @@
 #include <cuda_fp16.h>
 
 #include "kernels.h"
+#include "ptx.cuh"
 
 namespace nf4 {
 
@@ -48,6 +49,8 @@ template <bool RANK_MAJOR>  // P is row-major [16, C] (true) or row-major [C, 16
 __global__ void __launch_bounds__(LD_THREADS)
 lora_down_kernel(const __half* __restrict__ in, long long m, long long c, long long ld_in,
                  const __half* __restrict__ p, float scaling, __half* __restrict__ out) {
+    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
+    grid_dep_launch();
     __shared__ float part[LD_WARPS][16][17];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -108,6 +111,8 @@ __global__ void __launch_bounds__(256)
 lora_down_generic_kernel(const __half* __restrict__ in, long long m, long long c, long long ld_in,
                          const __half* __restrict__ p, long long p_stride_r, long long p_stride_c,
                          float scaling, __half* __restrict__ out) {
+    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
+    grid_dep_launch();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= m * 16) return;
     const long long row = i / 16;
@@ -126,17 +131,17 @@ cudaError_t launch_lora_down(const LoraDownArgs& a, cudaStream_t stream) {
                          ((reinterpret_cast<uintptr_t>(a.p) & 15) == 0);
     const unsigned blocks = (unsigned)((a.m + LD_ROWS - 1) / LD_ROWS);
     if (aligned && a.p_stride_c == 1 && a.p_stride_r == a.c) {
-        lora_down_kernel<true><<<blocks, LD_THREADS, 0, stream>>>(a.in, a.m, a.c, a.ld_in, a.p,
-                                                                   a.scaling, a.out);
+        return launch_pdl(lora_down_kernel<true>, dim3(blocks), dim3(LD_THREADS), 0, stream, a.in, a.m,
+                          a.c, a.ld_in, a.p, a.scaling, a.out);
     } else if (aligned && a.p_stride_r == 1 && a.p_stride_c == 16) {
-        lora_down_kernel<false><<<blocks, LD_THREADS, 0, stream>>>(a.in, a.m, a.c, a.ld_in, a.p,
-                                                                    a.scaling, a.out);
+        return launch_pdl(lora_down_kernel<false>, dim3(blocks), dim3(LD_THREADS), 0, stream, a.in,
+                          a.m, a.c, a.ld_in, a.p, a.scaling, a.out);
     } else {
         const long long total = a.m * 16;
-        lora_down_generic_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-            a.in, a.m, a.c, a.ld_in, a.p, a.p_stride_r, a.p_stride_c, a.scaling, a.out);
+        return launch_pdl(lora_down_generic_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0,
+                          stream, a.in, a.m, a.c, a.ld_in, a.p, a.p_stride_r, a.p_stride_c,
+                          a.scaling, a.out);
     }
-    return cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------------ lora_grad
@@ -152,6 +157,8 @@ __global__ void __launch_bounds__(LG_THREADS)
 lora_grad_kernel(const __half* __restrict__ z, long long m, long long c, long long ld_z,
                  const __half* __restrict__ s, float* __restrict__ out, long long o_stride_r,
                  long long o_stride_c, int vec_ok) {
+    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
+    grid_dep_launch();
     __shared__ __align__(16) float s_s[LG_ROWS][16];                 // 8 KB
     __shared__ __align__(16) float red[LG_WARPS / 2][64][32 + 1];    // 33 KB: [warp][value][lane]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -246,6 +253,8 @@ __global__ void __launch_bounds__(LGM_THREADS)
 lora_grad_mma_kernel(const __half* __restrict__ z, long long m, long long c, long long ld_z,
                      const __half* __restrict__ s, float* __restrict__ out, long long o_stride_r,
                      long long o_stride_c) {
+    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
+    grid_dep_launch();
     __shared__ __align__(16) __half zt[2][LGM_CHUNK][LGM_ZP];
     __shared__ __align__(16) __half st[2][LGM_CHUNK][LGM_SP];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -326,15 +335,13 @@ cudaError_t launch_lora_grad(const LoraGradArgs& a, cudaStream_t stream) {
     if (aligned) {
         dim3 grid_mma((unsigned)((a.c + LGM_COLS - 1) / LGM_COLS),
                       (unsigned)((a.m + LGM_ROWS - 1) / LGM_ROWS));
-        lora_grad_mma_kernel<<<grid_mma, LGM_THREADS, 0, stream>>>(a.z, a.m, a.c, a.ld_z, a.s, a.out,
-                                                                   a.o_stride_r, a.o_stride_c);
-        return cudaGetLastError();
+        return launch_pdl(lora_grad_mma_kernel, grid_mma, dim3(LGM_THREADS), 0, stream, a.z, a.m, a.c,
+                          a.ld_z, a.s, a.out, a.o_stride_r, a.o_stride_c);
     }
     dim3 grid((unsigned)((a.c + LG_COLS - 1) / LG_COLS), (unsigned)((a.m + LG_ROWS - 1) / LG_ROWS));
     const int vec_ok = (a.ld_z % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.z) & 7) == 0);
-    lora_grad_kernel<<<grid, LG_THREADS, 0, stream>>>(a.z, a.m, a.c, a.ld_z, a.s, a.out,
-                                                      a.o_stride_r, a.o_stride_c, vec_ok);
-    return cudaGetLastError();
+    return launch_pdl(lora_grad_kernel, grid, dim3(LG_THREADS), 0, stream, a.z, a.m, a.c, a.ld_z, a.s,
+                      a.out, a.o_stride_r, a.o_stride_c, vec_ok);
 }
 
 }  // namespace nf4

@@ -82,6 +82,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return true;
 }
 
+// ------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the "programmatic stream serialization" attribute may be scheduled while
+// its predecessor in the stream is still draining. grid_dep_wait() blocks until the predecessor
+// has completed and its memory is visible (a no-op for an ordinary launch): nothing before it may
+// touch global memory. grid_dep_launch() lets the successor be scheduled as soon as every CTA of
+// this grid has got this far.
+__device__ __forceinline__ void grid_dep_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_dep_launch() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------------- fences
 // Makes this thread's generic-proxy shared-memory writes visible to the async proxy
 // (tcgen05.mma operand fetch, TMA).

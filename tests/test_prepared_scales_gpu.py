@@ -112,8 +112,8 @@ def test_group_without_tables(gather_only):
     ws = [synthetic_weight(r, cols, True, seed=20 + i, device="cuda") for i, r in enumerate((1536, 256, 256))]
     ys = linear_forward_group(x, ws)
     singles = [nf4.linear_forward(x, p, None, s) for p, s in ws]
-    for a, b in zip(ys, singles):
-        assert torch.equal(a, b)
+    for a, b in zip(ys, singles):  # the group may tile / slice differently: fp32 sums reorder
+        assert (a.float() - b.float()).abs().max() <= 2e-3 * b.float().abs().max()
     dys = [torch.randn(m, r, device="cuda").half() for r in (1536, 256, 256)]
     dx = linear_backward_dx_group(dys, ws)
     want = sum(nf4.linear_backward_dx(d, p, s).float() for d, (p, s) in zip(dys, ws))
