@@ -469,4 +469,59 @@ int nf4b200_lora_grad(const void* z, int64_t m, int64_t c, int64_t ld_z, const v
     return NF4B200_OK;
 }
 
+int nf4b200_lora_down_batch(int count, const void* const* in, int64_t m, const int64_t* c,
+                            const int64_t* ld_in, const void* const* p, const int64_t* p_stride_r,
+                            const int64_t* p_stride_c, const float* scaling, void* const* out,
+                            void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (count < 1 || count > nf4::LORA_MAX_BATCH)
+        return fail(NF4B200_EINVAL, "lora_down_batch: count %d not in 1..%d", count, nf4::LORA_MAX_BATCH);
+    if (!in || !c || !ld_in || !p || !p_stride_r || !p_stride_c || !scaling || !out)
+        return fail(NF4B200_EINVAL, "lora_down_batch: NULL array");
+    nf4::LoraDownBatch b;
+    b.count = count;
+    for (int i = 0; i < count; ++i) {
+        if (!in[i] || !p[i] || !out[i]) return fail(NF4B200_EINVAL, "lora_down_batch: NULL pointer");
+        if (m <= 0 || c[i] <= 0 || ld_in[i] < c[i])
+            return fail(NF4B200_EINVAL, "lora_down_batch: bad shape in problem %d", i);
+        if ((reinterpret_cast<uintptr_t>(out[i]) & 3u) != 0)
+            return fail(NF4B200_EINVAL, "lora_down_batch: out is not 4-byte aligned");
+        b.item[i] = nf4::LoraDownArgs{static_cast<const __half*>(in[i]), m, c[i], ld_in[i],
+                                      static_cast<const __half*>(p[i]), p_stride_r[i],
+                                      p_stride_c[i], scaling[i], static_cast<__half*>(out[i])};
+    }
+    for (int i = count; i < nf4::LORA_MAX_BATCH; ++i) b.item[i] = b.item[0];
+    cudaError_t e = nf4::launch_lora_down_batch(b, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "lora_down_batch launch: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_lora_grad_batch(int count, const void* const* z, const int64_t* m, const int64_t* c,
+                            const int64_t* ld_z, const void* const* s, float* const* out,
+                            const int64_t* o_stride_r, const int64_t* o_stride_c, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (count < 1 || count > nf4::LORA_MAX_BATCH)
+        return fail(NF4B200_EINVAL, "lora_grad_batch: count %d not in 1..%d", count, nf4::LORA_MAX_BATCH);
+    if (!z || !m || !c || !ld_z || !s || !out || !o_stride_r || !o_stride_c)
+        return fail(NF4B200_EINVAL, "lora_grad_batch: NULL array");
+    nf4::LoraGradBatch b;
+    b.count = count;
+    for (int i = 0; i < count; ++i) {
+        if (!z[i] || !s[i] || !out[i]) return fail(NF4B200_EINVAL, "lora_grad_batch: NULL pointer");
+        if (m[i] <= 0 || c[i] <= 0 || ld_z[i] < c[i])
+            return fail(NF4B200_EINVAL, "lora_grad_batch: bad shape in problem %d", i);
+        b.item[i] = nf4::LoraGradArgs{static_cast<const __half*>(z[i]), m[i], c[i], ld_z[i],
+                                      static_cast<const __half*>(s[i]), out[i], o_stride_r[i],
+                                      o_stride_c[i], d->sms};
+    }
+    for (int i = count; i < nf4::LORA_MAX_BATCH; ++i) b.item[i] = b.item[0];
+    cudaError_t e = nf4::launch_lora_grad_batch(b, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "lora_grad_batch launch: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
 }  // extern "C"

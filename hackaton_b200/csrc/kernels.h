@@ -123,6 +123,14 @@ struct LoraDownArgs {
 };
 cudaError_t launch_lora_down(const LoraDownArgs& a, cudaStream_t stream);
 
+constexpr int LORA_MAX_BATCH = 8;
+struct LoraDownBatch {
+    LoraDownArgs item[LORA_MAX_BATCH];
+    int count;
+};
+// One launch when the problems share row count and layout of P; separate launches otherwise.
+cudaError_t launch_lora_down_batch(const LoraDownBatch& b, cudaStream_t stream);
+
 struct LoraGradArgs {
     const __half* z;
     long long m, c, ld_z;
@@ -132,6 +140,13 @@ struct LoraGradArgs {
     int sm_count;
 };
 cudaError_t launch_lora_grad(const LoraGradArgs& a, cudaStream_t stream);
+
+struct LoraGradBatch {
+    LoraGradArgs item[LORA_MAX_BATCH];
+    int count;
+};
+// One launch when every problem is on the tensor-core path; separate launches otherwise.
+cudaError_t launch_lora_grad_batch(const LoraGradBatch& b, cudaStream_t stream);
 
 // Records a message for nf4b200_last_error() on this thread and returns `code`.
 int set_error(int code, const char* fmt, ...);

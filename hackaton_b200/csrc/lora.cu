@@ -46,11 +46,10 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
 }
 
 template <bool RANK_MAJOR>  // P is row-major [16, C] (true) or row-major [C, 16] (false)
-__global__ void __launch_bounds__(LD_THREADS)
-lora_down_kernel(const __half* __restrict__ in, long long m, long long c, long long ld_in,
-                 const __half* __restrict__ p, float scaling, __half* __restrict__ out) {
-    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
-    grid_dep_launch();
+__device__ __forceinline__ void lora_down_block(const __half* __restrict__ in, long long m,
+                                                long long c, long long ld_in,
+                                                const __half* __restrict__ p, float scaling,
+                                                __half* __restrict__ out) {
     __shared__ float part[LD_WARPS][16][17];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -106,6 +105,25 @@ lora_down_kernel(const __half* __restrict__ in, long long m, long long c, long l
     }
 }
 
+template <bool RANK_MAJOR>
+__global__ void __launch_bounds__(LD_THREADS)
+lora_down_kernel(const __half* __restrict__ in, long long m, long long c, long long ld_in,
+                 const __half* __restrict__ p, float scaling, __half* __restrict__ out) {
+    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
+    grid_dep_launch();
+    lora_down_block<RANK_MAJOR>(in, m, c, ld_in, p, scaling, out);
+}
+
+// Several lora_down problems with the same row count in one launch: blockIdx.y picks the problem.
+template <bool RANK_MAJOR>
+__global__ void __launch_bounds__(LD_THREADS)
+lora_down_batch_kernel(const __grid_constant__ LoraDownBatch b) {
+    grid_dep_wait();
+    grid_dep_launch();
+    const LoraDownArgs& a = b.item[blockIdx.y];
+    lora_down_block<RANK_MAJOR>(a.in, a.m, a.c, a.ld_in, a.p, a.scaling, a.out);
+}
+
 // Layout-agnostic variant (any strides, any alignment): one thread per output element.
 __global__ void __launch_bounds__(256)
 lora_down_generic_kernel(const __half* __restrict__ in, long long m, long long c, long long ld_in,
@@ -142,6 +160,34 @@ cudaError_t launch_lora_down(const LoraDownArgs& a, cudaStream_t stream) {
                           stream, a.in, a.m, a.c, a.ld_in, a.p, a.p_stride_r, a.p_stride_c,
                           a.scaling, a.out);
     }
+}
+
+cudaError_t launch_lora_down_batch(const LoraDownBatch& b, cudaStream_t stream) {
+    // one launch when every problem has the same row count and the same (fast-path) layout of P
+    bool one_launch = b.count > 1;
+    bool rank_major = false;
+    for (int i = 0; i < b.count; ++i) {
+        const LoraDownArgs& a = b.item[i];
+        const bool aligned = (a.ld_in % 8 == 0) && (a.c % 8 == 0) &&
+                             ((reinterpret_cast<uintptr_t>(a.in) & 15) == 0) &&
+                             ((reinterpret_cast<uintptr_t>(a.p) & 15) == 0);
+        const bool rm = a.p_stride_c == 1 && a.p_stride_r == a.c;
+        const bool cm = a.p_stride_r == 1 && a.p_stride_c == 16;
+        if (!aligned || !(rm || cm) || a.m <= 0 || a.m != b.item[0].m) one_launch = false;
+        if (i == 0) rank_major = rm;
+        else if (rm != rank_major) one_launch = false;
+    }
+    if (!one_launch) {
+        for (int i = 0; i < b.count; ++i) {
+            cudaError_t e = launch_lora_down(b.item[i], stream);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
+    dim3 grid((unsigned)((b.item[0].m + LD_ROWS - 1) / LD_ROWS), (unsigned)b.count);
+    if (rank_major)
+        return launch_pdl(lora_down_batch_kernel<true>, grid, dim3(LD_THREADS), 0, stream, b);
+    return launch_pdl(lora_down_batch_kernel<false>, grid, dim3(LD_THREADS), 0, stream, b);
 }
 
 // ------------------------------------------------------------------------------------ lora_grad
@@ -249,12 +295,11 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, u
                  : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
 
-__global__ void __launch_bounds__(LGM_THREADS)
-lora_grad_mma_kernel(const __half* __restrict__ z, long long m, long long c, long long ld_z,
-                     const __half* __restrict__ s, float* __restrict__ out, long long o_stride_r,
-                     long long o_stride_c) {
-    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
-    grid_dep_launch();
+__device__ __forceinline__ void lora_grad_mma_block(const __half* __restrict__ z, long long m,
+                                                    long long c, long long ld_z,
+                                                    const __half* __restrict__ s,
+                                                    float* __restrict__ out, long long o_stride_r,
+                                                    long long o_stride_c) {
     __shared__ __align__(16) __half zt[2][LGM_CHUNK][LGM_ZP];
     __shared__ __align__(16) __half st[2][LGM_CHUNK][LGM_SP];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -325,6 +370,52 @@ lora_grad_mma_kernel(const __half* __restrict__ z, long long m, long long c, lon
             if (col < c) atomicAdd(out + col * o_stride_c + j * o_stride_r, d[e]);
         }
     }
+}
+
+__global__ void __launch_bounds__(LGM_THREADS)
+lora_grad_mma_kernel(const __half* __restrict__ z, long long m, long long c, long long ld_z,
+                     const __half* __restrict__ s, float* __restrict__ out, long long o_stride_r,
+                     long long o_stride_c) {
+    grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
+    grid_dep_launch();
+    lora_grad_mma_block(z, m, c, ld_z, s, out, o_stride_r, o_stride_c);
+}
+
+// Several lora_grad problems in one launch: blockIdx.z picks the problem; the grid is sized for
+// the widest one, blocks outside a narrower problem leave at once.
+__global__ void __launch_bounds__(LGM_THREADS)
+lora_grad_batch_kernel(const __grid_constant__ LoraGradBatch b) {
+    grid_dep_wait();
+    grid_dep_launch();
+    const LoraGradArgs& a = b.item[blockIdx.z];
+    if ((long long)blockIdx.x * LGM_COLS >= a.c || (long long)blockIdx.y * LGM_ROWS >= a.m) return;
+    lora_grad_mma_block(a.z, a.m, a.c, a.ld_z, a.s, a.out, a.o_stride_r, a.o_stride_c);
+}
+
+static bool lora_grad_aligned(const LoraGradArgs& a) {
+    return (a.ld_z % 8 == 0) && (a.c % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.z) & 15) == 0) &&
+           ((reinterpret_cast<uintptr_t>(a.s) & 15) == 0);
+}
+
+cudaError_t launch_lora_grad_batch(const LoraGradBatch& b, cudaStream_t stream) {
+    bool one_launch = b.count > 1;
+    long long max_c = 0, max_m = 0;
+    for (int i = 0; i < b.count; ++i) {
+        const LoraGradArgs& a = b.item[i];
+        if (a.m <= 0 || a.c <= 0 || !lora_grad_aligned(a)) one_launch = false;
+        max_c = a.c > max_c ? a.c : max_c;
+        max_m = a.m > max_m ? a.m : max_m;
+    }
+    if (!one_launch) {
+        for (int i = 0; i < b.count; ++i) {
+            cudaError_t e = launch_lora_grad(b.item[i], stream);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
+    dim3 grid((unsigned)((max_c + LGM_COLS - 1) / LGM_COLS), (unsigned)((max_m + LGM_ROWS - 1) / LGM_ROWS),
+              (unsigned)b.count);
+    return launch_pdl(lora_grad_batch_kernel, grid, dim3(LGM_THREADS), 0, stream, b);
 }
 
 cudaError_t launch_lora_grad(const LoraGradArgs& a, cudaStream_t stream) {

@@ -20,7 +20,7 @@ from typing import Optional, Sequence
 import torch
 
 from . import _lib
-from .lora import RANK, lora_down, lora_grad
+from .lora import RANK, lora_down_batch, lora_grad_batch
 from .nf4 import _require, _rows_view, _stream_ptr, _ws_buffers, weight_ref
 
 MAX_GROUP = 4
@@ -140,14 +140,14 @@ class NF4LinearGroup(torch.autograd.Function):
     def forward(ctx, x, projs, *params):
         n = len(projs)
         biases, las, lbs = params[0::3], params[1::3], params[2::3]
-        xas, b16 = [], []
-        for pr, a, b in zip(projs, las, lbs):
-            if a is None:
-                xas.append(None)
-                b16.append(None)
-            else:
-                xas.append(lora_down(x, a, True, pr.scaling))
-                b16.append(b.detach().to(torch.float16).contiguous())
+        xas, b16 = [None] * n, [None] * n
+        with_lora = [i for i, a in enumerate(las) if a is not None]
+        if with_lora:  # every adapter's scaling * x . Aᵀ in one launch
+            downs = lora_down_batch([x] * len(with_lora), [las[i] for i in with_lora], True,
+                                    [projs[i].scaling for i in with_lora])
+            for i, xa in zip(with_lora, downs):
+                xas[i] = xa
+                b16[i] = lbs[i].detach().to(torch.float16).contiguous()
         ys = linear_forward_group(x, [(pr.packed, pr.state) for pr in projs], biases, xas, b16)
         ctx.projs, ctx.n = projs, n
         ctx.bias_dtypes = [None if b is None else b.dtype for b in biases]
@@ -170,27 +170,39 @@ class NF4LinearGroup(torch.autograd.Function):
         grads = [g if g is not None else
                  torch.zeros(*x.shape[:-1], pr.state.shape[0], dtype=torch.float16, device=x.device)
                  for g, pr in zip(grads, projs)]
-        us, a16 = [], []
-        for g, pr, lo in zip(grads, projs, lora):
-            if lo is None:
-                us.append(None)
-                a16.append(None)
-            else:
-                us.append(lora_down(g, lo[1], False, pr.scaling))
-                a16.append(lo[0].detach().to(torch.float16).contiguous())
+        us, a16 = [None] * len(projs), [None] * len(projs)
+        with_lora = [i for i, lo in enumerate(lora) if lo is not None]
+        if with_lora:  # every adapter's scaling * dy . B in one launch
+            downs = lora_down_batch([grads[i] for i in with_lora], [lora[i][1] for i in with_lora],
+                                    False, [projs[i].scaling for i in with_lora])
+            for i, u in zip(with_lora, downs):
+                us[i] = u
+                a16[i] = lora[i][0].detach().to(torch.float16).contiguous()
         grad_x = None
         if ctx.needs_input_grad[0]:
             grad_x = linear_backward_dx_group(grads, [(pr.packed, pr.state) for pr in projs], us, a16)
+        # all LoRA weight gradients of the group in one launch
+        jobs = []  # (projection, "a" | "b", z, s, rank-major output)
+        for i in with_lora:
+            if ctx.needs_input_grad[3 + 3 * i]:
+                jobs.append((i, "a", x, us[i], True))
+            if ctx.needs_input_grad[4 + 3 * i]:
+                jobs.append((i, "b", grads[i], lora[i][2], False))
+        wgrads = {}
+        if jobs:
+            res = lora_grad_batch([j[2] for j in jobs], [j[3] for j in jobs], [j[4] for j in jobs])
+            for j, r in zip(jobs, res):
+                wgrads[(j[0], j[1])] = r
         out = [grad_x, None]
         for i, (g, pr, lo) in enumerate(zip(grads, projs, lora)):
             gb = ga = gbb = None
             if ctx.needs_input_grad[2 + 3 * i] and ctx.bias_dtypes[i] is not None:
                 gb = g.reshape(-1, g.shape[-1]).sum(0, dtype=ctx.bias_dtypes[i])
             if lo is not None:
-                if ctx.needs_input_grad[3 + 3 * i]:
-                    ga = lora_grad(x, us[i], True).to(lo[0].dtype)
-                if ctx.needs_input_grad[4 + 3 * i]:
-                    gbb = lora_grad(g, lo[2], False).to(lo[1].dtype)
+                if (i, "a") in wgrads:
+                    ga = wgrads[(i, "a")].to(lo[0].dtype)
+                if (i, "b") in wgrads:
+                    gbb = wgrads[(i, "b")].to(lo[1].dtype)
             out += [gb, ga, gbb]
         return tuple(out)
 

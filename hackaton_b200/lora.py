@@ -57,6 +57,69 @@ def lora_grad(z, s, rank_major_out):
     return out
 
 
+def _arr(ctype, values):
+    return (ctype * len(values))(*values)
+
+
+def lora_down_batch(inputs, ps, p_is_rank_major, scalings):
+    """lora_down for several (input, P) pairs with the same number of rows in one launch
+    (nf4b200_lora_down_batch). Returns the list of fp16 [M, 16] results."""
+    n = len(inputs)
+    if n == 1:
+        return [lora_down(inputs[0], ps[0], p_is_rank_major, scalings[0])]
+    i2s, p16s, cs = [], [], []
+    for inp, p in zip(inputs, ps):
+        c = inp.shape[-1]
+        i2s.append(_rows_view(inp, c))
+        p = p.detach()
+        if p.dtype != torch.float16 or not p.is_contiguous():
+            p = p.to(torch.float16).contiguous()
+        assert tuple(p.shape) == ((RANK, c) if p_is_rank_major else (c, RANK)), (p.shape, c)
+        p16s.append(p)
+        cs.append(c)
+    m = i2s[0].shape[0]
+    assert all(t.shape[0] == m for t in i2s)
+    device = inputs[0].device
+    out = torch.empty((n, m, RANK), dtype=torch.float16, device=device)
+    outs = [out[i] for i in range(n)]
+    stride_r = [c if p_is_rank_major else 1 for c in cs]
+    stride_c = [1 if p_is_rank_major else RANK for _ in cs]
+    vp, i64 = ctypes.c_void_p, ctypes.c_int64
+    with torch.cuda.device(device):
+        _lib.check(_lib.lib().nf4b200_lora_down_batch(
+            n, _arr(vp, [t.data_ptr() for t in i2s]), m, _arr(i64, cs),
+            _arr(i64, [t.stride(0) for t in i2s]), _arr(vp, [t.data_ptr() for t in p16s]),
+            _arr(i64, stride_r), _arr(i64, stride_c), _arr(ctypes.c_float, [float(v) for v in scalings]),
+            _arr(vp, [t.data_ptr() for t in outs]), _stream_ptr(device)))
+    return outs
+
+
+def lora_grad_batch(zs, ss, rank_major_outs):
+    """lora_grad for several (z, s) pairs in one launch (nf4b200_lora_grad_batch); one zeroed
+    fp32 buffer holds all results. Returns the list of gradients, [16, C] or [C, 16] each."""
+    n = len(zs)
+    if n == 1:
+        return [lora_grad(zs[0], ss[0], rank_major_outs[0])]
+    z2s = [_rows_view(z, z.shape[-1]) for z in zs]
+    cs = [z.shape[-1] for z in zs]
+    device = zs[0].device
+    sizes = [(c * RANK + 63) // 64 * 64 for c in cs]         # 256-byte aligned pieces
+    flat = torch.zeros(sum(sizes), dtype=torch.float32, device=device)
+    outs, at = [], 0
+    for c, size, rm in zip(cs, sizes, rank_major_outs):
+        outs.append(flat[at:at + c * RANK].view((RANK, c) if rm else (c, RANK)))
+        at += size
+    vp, i64 = ctypes.c_void_p, ctypes.c_int64
+    with torch.cuda.device(device):
+        _lib.check(_lib.lib().nf4b200_lora_grad_batch(
+            n, _arr(vp, [t.data_ptr() for t in z2s]), _arr(i64, [t.shape[0] for t in z2s]),
+            _arr(i64, cs), _arr(i64, [t.stride(0) for t in z2s]),
+            _arr(vp, [t.data_ptr() for t in ss]), _arr(vp, [t.data_ptr() for t in outs]),
+            _arr(i64, [c if rm else 1 for c, rm in zip(cs, rank_major_outs)]),
+            _arr(i64, [1 if rm else RANK for rm in rank_major_outs]), _stream_ptr(device)))
+    return outs
+
+
 class NF4LoRALinear(torch.autograd.Function):
     """Frozen NF4 base weight + trainable rank-16 A, B. `x_lora` is the input of the LoRA branch:
     pass `x` itself when there is no dropout (then the input gradient is one fused GEMM)."""

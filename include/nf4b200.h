@@ -187,6 +187,23 @@ int nf4b200_lora_down(const void* in, int64_t m, int64_t c, int64_t ld_in, const
 int nf4b200_lora_grad(const void* z, int64_t m, int64_t c, int64_t ld_z, const void* s,
                       float* out, int64_t o_stride_r, int64_t o_stride_c, void* stream);
 
+/*
+ * The two calls above for several problems (up to 8) in one launch each, with arrays in place of
+ * the per-problem arguments: a layer with LoRA on q_proj and v_proj needs lora_down for both
+ * adapters on the same hidden state, and four weight gradients per backward pass, each far too
+ * small to fill the GPU. lora_down_batch: all problems share the row count m. Problems that do
+ * not fit one launch (different layouts of p, unaligned pointers) are launched one by one; the
+ * results do not depend on the route. No counterpart in the reference (peft runs one small GEMM
+ * per adapter matrix).
+ */
+int nf4b200_lora_down_batch(int count, const void* const* in, int64_t m, const int64_t* c,
+                            const int64_t* ld_in, const void* const* p, const int64_t* p_stride_r,
+                            const int64_t* p_stride_c, const float* scaling, void* const* out,
+                            void* stream);
+int nf4b200_lora_grad_batch(int count, const void* const* z, const int64_t* m, const int64_t* c,
+                            const int64_t* ld_z, const void* const* s, float* const* out,
+                            const int64_t* o_stride_r, const int64_t* o_stride_c, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

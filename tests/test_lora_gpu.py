@@ -69,3 +69,37 @@ def test_lora_with_dropout_branch(cuda_lib):
     assert nf4_oracle.max_rel_err(xg.grad.cpu(), dy.float() @ w.float()) <= TOL
     dxl_ref = 2.0 * (dy.float() @ b.float()) @ a.float()
     assert nf4_oracle.max_rel_err(xlg.grad.cpu(), dxl_ref) <= TOL
+
+
+def test_batched_lora_kernels_match_single(cuda_lib):
+    """nf4b200_lora_down_batch / _grad_batch: same results as one call per problem."""
+    from hackaton_b200.lora import lora_down, lora_down_batch, lora_grad, lora_grad_batch
+
+    torch.manual_seed(11)
+    m = 777
+    x = torch.randn(m, 1536, device="cuda").half()
+    a_q = (torch.randn(16, 1536, device="cuda") * 0.05).half()
+    a_v = (torch.randn(16, 1536, device="cuda") * 0.05).half()
+    got = lora_down_batch([x, x], [a_q, a_v], True, [2.0, 0.5])
+    want = [lora_down(x, a_q, True, 2.0), lora_down(x, a_v, True, 0.5)]
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+
+    dy_q = torch.randn(m, 1536, device="cuda").half()
+    dy_v = torch.randn(m, 256, device="cuda").half()
+    b_q = (torch.randn(1536, 16, device="cuda") * 0.05).half()
+    b_v = (torch.randn(256, 16, device="cuda") * 0.05).half()
+    got = lora_down_batch([dy_q, dy_v], [b_q, b_v], False, [2.0, 2.0])
+    want = [lora_down(dy_q, b_q, False, 2.0), lora_down(dy_v, b_v, False, 2.0)]
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+
+    u_q, u_v = want
+    xa_q, xa_v = lora_down(x, a_q, True, 2.0), lora_down(x, a_v, True, 2.0)
+    got = lora_grad_batch([x, dy_q, x, dy_v], [u_q, xa_q, u_v, xa_v], [True, False, True, False])
+    want = [lora_grad(x, u_q, True), lora_grad(dy_q, xa_q, False), lora_grad(x, u_v, True),
+            lora_grad(dy_v, xa_v, False)]
+    for g, w in zip(got, want):
+        assert g.shape == w.shape
+        # fp32 atomics: the order of the block sums is not fixed
+        assert (g - w).abs().max() <= 1e-4 * w.abs().max().clamp_min(1.0)
