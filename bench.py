@@ -641,7 +641,15 @@ def run_multi(args):
     world = int(os.environ["WORLD_SIZE"])
     device = torch.device("cuda", local)
     torch.cuda.set_device(device)
+    # SMs left to NCCL next to the persistent GEMM grids (0 = none: collectives then wait for the
+    # GEMMs to finish); NCCL is told to stay within them
+    comm_sms = args.comm_sms
+    if comm_sms > 0:
+        os.environ.setdefault("NCCL_MAX_CTAS", str(comm_sms))
     dist.init_process_group("nccl", device_id=device)
+    if comm_sms > 0:
+        from hackaton_b200.sharded import reserve_comm_sms
+        reserve_comm_sms(comm_sms)
     shapes, m = SHAPES_7B, 8192
     pk = peaks()
     n_rot = 4
@@ -744,6 +752,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=28)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--comm-sms", type=int, default=0,
+                    help="multi-GPU: SMs kept free of the GEMM grids for NCCL kernels")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -19,6 +19,7 @@ EXPORTS = (
     "nf4b200_workspace_bytes", "nf4b200_linear_fwd_static", "nf4b200_linear_fwd_group",
     "nf4b200_linear_bwd_dx_group", "nf4b200_workspace_bytes_group", "nf4b200_scales16_bytes",
     "nf4b200_prepare_scales", "nf4b200_lora_down_batch", "nf4b200_lora_grad_batch",
+    "nf4b200_set_sm_limit",
 )
 
 F16, BF16, F32 = 0, 1, 2
@@ -90,6 +91,7 @@ def lib() -> ctypes.CDLL:
                                                pv, c_void_p]
     handle.nf4b200_lora_grad_batch.argtypes = [c_int, pv, pi64, pi64, pi64, pv, pv, pi64, pi64,
                                                c_void_p]
+    handle.nf4b200_set_sm_limit.argtypes = [c_int]
     handle.nf4b200_scales16_bytes.argtypes = [c_int64, c_int64]
     handle.nf4b200_scales16_bytes.restype = c_int64
     handle.nf4b200_prepare_scales.argtypes = [POINTER(Weight), c_void_p, c_void_p]
@@ -111,6 +113,14 @@ def query(device: int = 0) -> Props:
     props = Props()
     check(lib().nf4b200_query(device, ctypes.byref(props)))
     return props
+
+
+def set_sm_limit(sms: int) -> None:
+    """Caps the SMs the fused GEMM grids occupy (0 = all); see nf4b200_set_sm_limit."""
+    check(lib().nf4b200_set_sm_limit(int(sms)))
+    from . import group, nf4     # scratch sizes were computed for the old grid
+    nf4._ws_need.clear()
+    group._ws_need.clear()
 
 
 def device_status() -> int:

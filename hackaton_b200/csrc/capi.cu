@@ -3,6 +3,8 @@
 // codes plus a thread-local message.
 #include <cuda_runtime.h>
 
+#include <atomic>
+
 #include <cstdarg>
 #include <cstdio>
 #include <mutex>
@@ -74,6 +76,14 @@ int require_sm100(DeviceInfo** info) {
                     "there is no fallback path",
                     (*info)->major, (*info)->minor);
     return NF4B200_OK;
+}
+
+// SMs the fused GEMM kernels may occupy (nf4b200_set_sm_limit); 0 = all of them.
+std::atomic<int> g_sm_limit{0};
+
+int gemm_sms(const DeviceInfo* d) {
+    const int limit = g_sm_limit.load(std::memory_order_relaxed);
+    return (limit > 0 && limit < d->sms) ? limit : d->sms;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -238,6 +248,13 @@ int nf4b200_dequant(const nf4b200_weight* w, void* out, int out_dtype, void* str
     return NF4B200_OK;
 }
 
+int nf4b200_set_sm_limit(int sms) {
+    if (sms < 0) return fail(NF4B200_EINVAL, "set_sm_limit: %d", sms);
+    if (sms != 0 && sms < 2) sms = 2;
+    g_sm_limit.store(sms, std::memory_order_relaxed);
+    return NF4B200_OK;
+}
+
 int64_t nf4b200_scales16_bytes(int64_t n_rows, int64_t n_cols) {
     if (n_rows <= 0 || n_cols <= 0 || n_cols % 64 != 0 || n_rows % 8 != 0) return 0;
     return n_rows * (n_cols / 64) * 2;
@@ -279,7 +296,7 @@ int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_
     if (xa && (!aligned16(xa) || !aligned16(lora_b)))
         return fail(NF4B200_EINVAL, "xa / lora_b are not 16-byte aligned");
     nf4::GemmArgs g;
-    fill_gemm(g, w, d->sms);
+    fill_gemm(g, w, gemm_sms(d));
     g.act = static_cast<const __half*>(x); g.m = m; g.ld_act = ldx;
     g.out = static_cast<__half*>(y); g.ld_out = ldy;
     g.bias = static_cast<const __half*>(bias);
@@ -310,7 +327,7 @@ int nf4b200_linear_bwd_dx(const nf4b200_weight* w, const void* dy, int64_t m, in
     if (u && (!aligned16(u) || !aligned16(lora_a)))
         return fail(NF4B200_EINVAL, "u / lora_a are not 16-byte aligned");
     nf4::GemmArgs g;
-    fill_gemm(g, w, d->sms);
+    fill_gemm(g, w, gemm_sms(d));
     g.act = static_cast<const __half*>(dy); g.m = m; g.ld_act = lddy;
     g.out = static_cast<__half*>(dx); g.ld_out = lddx;
     g.bias = nullptr;
@@ -352,7 +369,7 @@ int nf4b200_linear_fwd_group(int count, const nf4b200_weight* const* w, const vo
         if (xa_i && (!aligned16(xa_i) || !aligned16(lb_i)))
             return fail(NF4B200_EINVAL, "fwd_group: xa / lora_b are not 16-byte aligned");
         nf4::GemmArgs& g = ga.item[i];
-        fill_gemm(g, w[i], d->sms);
+        fill_gemm(g, w[i], gemm_sms(d));
         g.act = static_cast<const __half*>(x); g.m = m; g.ld_act = ldx;
         g.out = static_cast<__half*>(y[i]); g.ld_out = ldy[i];
         g.bias = static_cast<const __half*>(bias ? bias[i] : nullptr);
@@ -393,7 +410,7 @@ int nf4b200_linear_bwd_dx_group(int count, const nf4b200_weight* const* w, const
         if (u_i && (!aligned16(u_i) || !aligned16(la_i)))
             return fail(NF4B200_EINVAL, "bwd_group: u / lora_a are not 16-byte aligned");
         nf4::GemmArgs& g = ga.item[i];
-        fill_gemm(g, w[i], d->sms);
+        fill_gemm(g, w[i], gemm_sms(d));
         g.act = static_cast<const __half*>(dy[i]); g.m = m; g.ld_act = lddy[i];
         g.out = static_cast<__half*>(dx); g.ld_out = lddx;
         g.bias = nullptr;
@@ -424,7 +441,7 @@ int64_t nf4b200_workspace_bytes_group(int count, const int64_t* n_rows, int64_t 
         if (n_rows[i] <= 0) return fail(NF4B200_EINVAL, "workspace_bytes_group: bad shape");
         rows[i] = n_rows[i];
     }
-    const nf4::GemmPlan pl = nf4::plan_gemm_group(m, rows, count, n_cols, backward != 0, d->sms);
+    const nf4::GemmPlan pl = nf4::plan_gemm_group(m, rows, count, n_cols, backward != 0, gemm_sms(d));
     return (int64_t)pl.ws_bytes;
 }
 
@@ -434,7 +451,7 @@ int64_t nf4b200_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int b
     if (rc != NF4B200_OK) return rc;
     if (n_rows <= 0 || n_cols <= 0 || m <= 0)
         return fail(NF4B200_EINVAL, "workspace_bytes: bad shape");
-    const nf4::GemmPlan pl = nf4::plan_gemm(m, n_rows, n_cols, backward != 0, d->sms);
+    const nf4::GemmPlan pl = nf4::plan_gemm(m, n_rows, n_cols, backward != 0, gemm_sms(d));
     return (int64_t)pl.ws_bytes;
 }
 

@@ -25,6 +25,19 @@ from .nf4 import linear_backward_dx, linear_forward
 from .quantize import quantize_nf4
 
 
+def reserve_comm_sms(n_sms: int) -> int:
+    """Keeps `n_sms` SMs of the current device out of the fused GEMMs' persistent grids, so that the
+    NCCL kernel of one projection can run next to the GEMM of the next one (a grid that occupies
+    every SM leaves a collective nothing to start on). 0 gives all SMs back. Returns the number of
+    SMs the GEMMs use from now on. Pair it with NCCL's own CTA cap (`NCCL_MAX_CTAS`)."""
+    from . import _lib
+
+    total = _lib.query(torch.cuda.current_device()).sm_count
+    use = total if n_sms <= 0 else max(2, total - int(n_sms))
+    _lib.set_sm_limit(0 if use == total else use)
+    return use
+
+
 def shard_rows(n_rows: int, world: int, rank: int):
     """Row range of `rank`; N must split evenly so every shard has the same shape."""
     if n_rows % world != 0:

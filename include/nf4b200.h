@@ -62,6 +62,15 @@ int nf4b200_query(int device, nf4b200_props* out);
 const char* nf4b200_last_error(void);
 
 /*
+ * Caps the number of SMs the fused GEMM kernels of this process occupy (their persistent grids
+ * otherwise take every SM); 0 restores "all". For callers that run communication kernels next to
+ * the GEMMs (tensor-parallel shards: the collective of projection i overlaps the GEMM of
+ * projection i+1 only if some SMs are left for it). Affects later calls, including
+ * nf4b200_workspace_bytes*. No counterpart in the reference (single GPU).
+ */
+int nf4b200_set_sm_limit(int sms);
+
+/*
  * Optional set-up step for the fused GEMM entry points. Writes the block scales of `w` (the
  * (double-)dequantised absmax, rounded to fp16 exactly as the GEMM's decode rounds them) as an
  * fp16 table [n_cols / 64][n_rows] into `scales16` (nf4b200_scales16_bytes(...) bytes, 16-byte
