@@ -1312,6 +1312,25 @@ cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, cons
     long long n_w[GEMM_MAX_GROUP];
     for (int i = 0; i < ga.count; ++i) n_w[i] = ga.item[i].n_w;
     const GemmArgs& a = ga.item[0];
+    // A handful of token rows: stream the weights through the small-M kernel, one launch per
+    // weight (NF4B200_DEBUG bit 7 keeps them on the tensor-core kernel, for comparison).
+    if (!a.trans_w && a.m <= 64 && !(debug_flags() & 128)) {
+        bool all = true;
+        for (int i = 0; i < ga.count; ++i) {
+            GemmArgs it = ga.item[i];
+            it.act = a.act; it.m = a.m; it.ld_act = a.ld_act; it.trans_w = false;
+            if (!gemv_eligible(it)) all = false;
+        }
+        if (all) {
+            for (int i = 0; i < ga.count; ++i) {
+                GemmArgs it = ga.item[i];
+                it.act = a.act; it.m = a.m; it.ld_act = a.ld_act; it.trans_w = false;
+                cudaError_t e = launch_gemv(it, stream);
+                if (e != cudaSuccess) { *why = "small-M kernel launch"; return e; }
+            }
+            return cudaSuccess;
+        }
+    }
     const GemmPlan pl = plan_gemm_group(a.m, n_w, ga.count, a.k_w, a.trans_w, a.sm_count);
     // Two alternating groups of 8 decoding warps measured faster for the forward form, one group
     // of 16 for the backward form (NF4B200_DEBUG bit 5 swaps the choice, for tuning).

@@ -113,6 +113,10 @@ struct GemmGroupArgs {
 cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why);
 cudaError_t launch_gemm_group(const GemmGroupArgs& a, cudaStream_t stream, const char** why);
 
+// Weight-streaming forward kernel for M <= 64 (gemv.cu); launch_gemm* route eligible calls to it.
+bool gemv_eligible(const GemmArgs& a);
+cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t stream);
+
 struct LoraDownArgs {
     const __half* in;
     long long m, c, ld_in;

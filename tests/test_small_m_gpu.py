@@ -1,0 +1,62 @@
+"""GPU: the weight-streaming forward kernel that serves M <= 64 (the decode shapes of
+BASELINE.json's config 3: M in {1, 4, 16, 64}) against the oracle, with bias and the LoRA term, and
+against the tensor-core kernel it replaces at these sizes."""
+
+import pytest
+import torch
+
+from oracle import nf4_oracle
+from tests.util import oracle_weight, synthetic_weight
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+@pytest.mark.parametrize("m", [1, 4, 5, 16, 33, 64])
+@pytest.mark.parametrize("n,k", [(1536, 1536), (256, 1536), (1536, 8960), (8960, 1536), (48, 64)])
+def test_small_m_forward_vs_oracle(cuda_lib, m, n, k):
+    from hackaton_b200.nf4 import linear_forward
+
+    packed, state = synthetic_weight(n, k, True, seed=n + m, device="cuda")
+    w = oracle_weight(packed, state)
+    g = torch.Generator().manual_seed(m)
+    x = torch.randn(m, k, generator=g).half()
+    bias = torch.randn(n, generator=g).half()
+    y = linear_forward(x.cuda(), packed, bias.cuda(), state)
+    assert nf4_oracle.max_rel_err(y.cpu(), nf4_oracle.linear_fwd(x, w, bias)) <= TOL
+    cuda_lib.device_status()
+
+
+@pytest.mark.parametrize("m", [1, 16, 64])
+def test_small_m_lora_term(cuda_lib, m):
+    from hackaton_b200 import nf4_lora_linear
+
+    n, k = 1536, 1536
+    packed, state = synthetic_weight(n, k, True, seed=7, device="cuda")
+    w = oracle_weight(packed, state)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(m, k, generator=g).half()
+    a = ((torch.rand(16, k, generator=g) * 2 - 1) / k ** 0.5).half()
+    b = (torch.randn(n, 16, generator=g) * 0.2).half()
+    y = nf4_lora_linear(x.cuda(), packed, None, state, a.cuda(), b.cuda(), 2.0)
+    y_ref, _ = nf4_oracle.lora_fwd(x, w, a, b, 2.0)
+    assert nf4_oracle.max_rel_err(y.cpu(), y_ref) <= TOL
+    assert nf4_oracle.max_rel_err(nf4_oracle.linear_fwd(x, w), y_ref) > 5 * TOL  # term is visible
+
+
+def test_small_m_matches_tensor_core_kernel(cuda_lib):
+    """Same weight, M = 16: the streaming kernel (scale table present) and the tcgen05 kernel
+    (no table, so the call is not eligible for the streaming kernel) agree to fp16 rounding."""
+    from hackaton_b200 import nf4
+
+    n, k, m = 1536, 1536, 16
+    x = torch.randn(m, k, device="cuda").half()
+    outs = []
+    for prepared in (True, False):
+        nf4.PREPARED_SCALES = prepared
+        try:
+            packed, state = synthetic_weight(n, k, True, seed=5, device="cuda")
+            outs.append(nf4.linear_forward(x, packed, None, state).float())
+        finally:
+            nf4.PREPARED_SCALES = True
+    assert (outs[0] - outs[1]).abs().max() <= 2e-3 * outs[1].abs().max()
