@@ -10,7 +10,7 @@
 // the 64-deep k-blocks; each CTA holds 128*NACC of its rows (activations in shared memory,
 // accumulators in its own TMEM) and decodes only half of the weight tile, which the tensor cores
 // of both SMs then read. With CG = 1 (token counts up to 128) a single CTA owns a 128 x 256 tile.
-// Roles inside a CTA (19 warps):
+// Roles inside a CTA (20 warps):
 //   warps 0..15  producers: read the packed codes and the block scale of their piece from the code
 //                ring, expand the codes through a register-resident fp16 table (byte permutes, no
 //                shared-memory lookups), wait for the operand slot to be free and write the fp16
@@ -24,7 +24,9 @@
 //   warp 17      allocates TMEM; in the leader CTA one lane issues the MMAs (N = 256, K = 16) and
 //                commits each k-block to the ring's "empty" barriers and each unit to
 //                "accumulators full" (multicast to both CTAs of a pair). In the peer CTA one lane
-//                forwards "activation tile landed" to the leader.
+//                forwards "activation tile landed" to the leader. With two accumulators, warp 19
+//                holds a second issuing thread: each feeds one accumulator, and while one checks
+//                the next stage's barriers the other keeps the (shallow) MMA queue filled.
 //   warp 18      feeds the code ring (NC slots, deeper than the operand ring, so that HBM latency
 //                stays out of the operand ring's cycle): per k-block one TMA for this CTA's code
 //                tile and the tile's block scales. With a ready-made scale table (see
@@ -67,10 +69,11 @@ namespace nf4 {
 
 constexpr int PRODUCER_WARPS = 16;
 constexpr int PRODUCER_THREADS = PRODUCER_WARPS * 32;
-constexpr int GEMM_THREADS = PRODUCER_THREADS + 96;
+constexpr int GEMM_THREADS = PRODUCER_THREADS + 128;
 constexpr int TMA_WARP = PRODUCER_WARPS;
 constexpr int MMA_WARP = PRODUCER_WARPS + 1;
 constexpr int AUX_WARP = PRODUCER_WARPS + 2;
+constexpr int MMA2_WARP = PRODUCER_WARPS + 3;  // second MMA issuer (NACC = 2: one per accumulator)
 constexpr int BK = 64;   // k-block depth = one quantisation block
 constexpr int BN = 256;  // output-tile width
 
@@ -299,6 +302,10 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
     // vouches for its activation tile
     constexpr uint32_t W_ARRIVALS = CG * DW + (CG == 2 ? 1 : 0);
     constexpr int NC = L::NC;
+    // With two accumulators each has its own issuing thread (warps 17 and 19, different
+    // schedulers): the tensor pipe queues only a couple of MMAs, so the barrier checks one
+    // thread makes between two k-blocks would leave it idle; the other thread issues meanwhile.
+    constexpr int ISSUERS = NACC;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -332,13 +339,13 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full_tma(s), 1);
             mbar_init(bar_full_w(s), W_ARRIVALS);
-            mbar_init(bar_empty(s), 1);
+            mbar_init(bar_empty(s), ISSUERS);  // one commit per MMA issuer
         }
         for (int c = 0; c < NC; ++c) {
             mbar_init(bar_full_c(c), 33);   // the TMA's expect_tx arrive + 32 lanes' scale copies
             mbar_init(bar_empty_c(c), DW);  // every decoding warp has read its share
         }
-        mbar_init(bar_tmem_full, 1);
+        mbar_init(bar_tmem_full, ISSUERS);
         mbar_init(bar_tmem_empty, ARRIVALS);
         *abort_flag = 0;
         fence_barrier_init();
@@ -377,12 +384,13 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
 
     // Warp-wide waits: one lane polls the barrier, the others sleep at the warp vote. Keeps the
     // shared-memory pipe free of 31 redundant polls per warp.
+    const uint32_t WAIT_SLEEP_NS = (p.debug >> 12) ? (uint32_t)(p.debug >> 12) : 64u;  // tuning
     auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool {
         if (mbar_try_wait(bar, parity)) return true;
         const unsigned long long t0 = globaltimer_ns();
         uint32_t polls = 0;
         while (!mbar_try_wait(bar, parity)) {
-            __nanosleep(64);
+            __nanosleep(WAIT_SLEEP_NS);
             if ((++polls & 63u) == 0u) {
                 if (*abort_flag) return false;
                 if (globaltimer_ns() - t0 > WAIT_TIMEOUT_NS) { *abort_flag = 1; return false; }
@@ -395,7 +403,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         const unsigned long long t0 = globaltimer_ns();
         uint32_t polls = 0;
         while (!mbar_test_wait_cluster(bar, parity)) {
-            __nanosleep(64);
+            __nanosleep(WAIT_SLEEP_NS);
             if ((++polls & 63u) == 0u) {
                 if (*abort_flag) return false;
                 if (globaltimer_ns() - t0 > WAIT_TIMEOUT_NS) { *abort_flag = 1; return false; }
@@ -434,9 +442,10 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                 }
             }
         }
-    } else if (warp == MMA_WARP) {
-        // ------------------------------------------------------------------ MMA issuer (leader)
-        if (lane == 0 && rank == 0) {
+    } else if (warp == MMA_WARP || warp == MMA2_WARP) {
+        // ------------------------------------------------------------------ MMA issuers (leader)
+        const int acc = warp == MMA_WARP ? 0 : 1;  // the accumulator this thread feeds
+        if (lane == 0 && rank == 0 && acc < NACC) {
             // This single thread feeds the tensor cores of the whole pair, next to four busy decoding
             // warps on its scheduler: the loop is written for a minimal instruction count. The ring
             // loop is unrolled over the stages, so every descriptor is "constant + one add".
@@ -483,23 +492,18 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                     } else if (it < w.nkb) {
                         const uint32_t first = it > 0 ? 1u : 0u;
 #pragma unroll
-                        for (int k = 0; k < BK / 16; ++k) {
-#pragma unroll
-                            for (int a = 0; a < NACC; ++a)
-                                umma_f16_words<CG>(
-                                    tmem_base + a * BN,
-                                    a4 + (uint32_t)(A_MAIN & 0xFFFFFFFFu) + a * ((128 * BK * 2) >> 4) + 2 * k,
-                                    (uint32_t)(A_MAIN >> 32),
-                                    w4 + (uint32_t)(B_MAIN & 0xFFFFFFFFu) + B_KSTEP * k,
-                                    (uint32_t)(B_MAIN >> 32), idesc, k > 0 ? 1u : first);
-                        }
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_f16_words<CG>(
+                                tmem_base + acc * BN,
+                                a4 + (uint32_t)(A_MAIN & 0xFFFFFFFFu) + acc * ((128 * BK * 2) >> 4) + 2 * k,
+                                (uint32_t)(A_MAIN >> 32),
+                                w4 + (uint32_t)(B_MAIN & 0xFFFFFFFFu) + B_KSTEP * k,
+                                (uint32_t)(B_MAIN >> 32), idesc, k > 0 ? 1u : first);
                     } else {
-#pragma unroll
-                        for (int a = 0; a < NACC; ++a)
-                            umma_f16_words<CG>(tmem_base + a * BN,
-                                               a4 + (uint32_t)(A_EXT & 0xFFFFFFFFu) + a * ((128 * BK * 2) >> 4),
-                                               (uint32_t)(A_EXT >> 32), w4 + (uint32_t)(B_EXT & 0xFFFFFFFFu),
-                                               (uint32_t)(B_EXT >> 32), idesc, it > 0 ? 1u : 0u);
+                        umma_f16_words<CG>(tmem_base + acc * BN,
+                                           a4 + (uint32_t)(A_EXT & 0xFFFFFFFFu) + acc * ((128 * BK * 2) >> 4),
+                                           (uint32_t)(A_EXT >> 32), w4 + (uint32_t)(B_EXT & 0xFFFFFFFFu),
+                                           (uint32_t)(B_EXT >> 32), idesc, it > 0 ? 1u : 0u);
                     }
                     if (CG == 2) umma_commit_pair(bar_empty(s), (uint16_t)3);
                     else         umma_commit(bar_empty(s));
@@ -525,7 +529,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                     if (s == STAGES - 1) ph ^= 1u;
                 }
             }
-        } else if (CG == 2 && lane == 0) {
+        } else if (CG == 2 && lane == 0 && warp == MMA_WARP) {
             // Peer CTA: tell the leader when this CTA's activation tile of a step has landed.
             uint32_t g = 0;
             for (int u = pair; u < total_units && !fail; u += n_pairs) {
@@ -740,13 +744,16 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                     // hand the ring slot back, then wait for the operand slot to be free
                     if (!warp_wait(bar_full_c(c), cph)) { fail = 4; break; }
                     if (pt == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(1, it); }
-                    uint4 v[WORDS];
+                    // codes and scale go into registers and the code-ring slot goes back at once;
+                    // the expansion itself waits for the operand slot (holding the expanded tile
+                    // in registers across that wait costs spills under the 96-register cap)
+                    uint32_t cw[WORDS];
+                    __half2 scale2 = __half2half2(__ushort_as_half((unsigned short)0));
                     if (!(p.debug & 1)) {
                         if (L::TABLES > 1 && p.n_prob > 1) {
                             const int pi = (int)lds32(smem_base + L::META_OFF + 4u * c);
                             if (pi != lut_prob) load_lut(pi);
                         }
-                        __half2 scale2;
                         if (p.prepared) {
                             const uint32_t h = lds16(prep_off + c * L::S_BYTES);
                             const uint32_t hh = __byte_perm(h, 0u, 0x1010u);
@@ -765,15 +772,11 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                             scale2 = __float2half2_rn(sc);
                         }
                         if (WORDS == 4) {
-                            const uint4 cw = lds128(src_off + c * L::C_BYTES);
-                            v[0] = decode_word_reg(cw.x, lut, scale2);
-                            v[1] = decode_word_reg(cw.y, lut, scale2);
-                            v[WORDS - 2] = decode_word_reg(cw.z, lut, scale2);
-                            v[WORDS - 1] = decode_word_reg(cw.w, lut, scale2);
+                            const uint4 q = lds128(src_off + c * L::C_BYTES);
+                            cw[0] = q.x; cw[1] = q.y; cw[WORDS - 2] = q.z; cw[WORDS - 1] = q.w;
                         } else {
-                            const uint2 cw = lds64(src_off + c * L::C_BYTES);
-                            v[0] = decode_word_reg(cw.x, lut, scale2);
-                            v[1] = decode_word_reg(cw.y, lut, scale2);
+                            const uint2 q = lds64(src_off + c * L::C_BYTES);
+                            cw[0] = q.x; cw[1] = q.y;
                         }
                     }
                     __syncwarp();
@@ -782,7 +785,8 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                     if (pt == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(7, it); }
                     if (!(p.debug & 1)) {
 #pragma unroll
-                        for (int i = 0; i < WORDS; ++i) sts128(dst_off[i] + stage_off, v[i]);
+                        for (int i = 0; i < WORDS; ++i)
+                            sts128(dst_off[i] + stage_off, decode_word_reg(cw[i], lut, scale2));
                     }
                 } else {
                     // K extension operands, unswizzled core-matrix layout (see the MMA branch).
@@ -1332,9 +1336,9 @@ cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, cons
         }
     }
     const GemmPlan pl = plan_gemm_group(a.m, n_w, ga.count, a.k_w, a.trans_w, a.sm_count);
-    // Two alternating groups of 8 decoding warps measured faster for the forward form, one group
-    // of 16 for the backward form (NF4B200_DEBUG bit 5 swaps the choice, for tuning).
-    const bool dw8 = ((debug_flags() & 32) != 0) != !a.trans_w;
+    // Two alternating groups of 8 decoding warps measured faster than one group of 16 in both
+    // directions (NF4B200_DEBUG bit 5 selects the single group, for tuning).
+    const bool dw8 = (debug_flags() & 32) == 0;
     if (pl.cg == 2 && pl.nacc == 2) {
         if (dw8)
             return a.trans_w ? launch_cfg<2, 2, true, 4, 8, MAXP>(ga, pl, stream, why)
