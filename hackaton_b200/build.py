@@ -46,6 +46,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     if not force and not _stale():
         return LIB
     flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+    flags += os.environ.get("NF4B200_NVCC_FLAGS", "").split()   # e.g. -DNF4B200_TRACE for tuning
     if verbose:
         flags += ["-Xptxas", "-v"]
     objs = []

@@ -110,7 +110,7 @@ struct GemmParams {
     int nkb_total;           // k-blocks of the whole contraction
     int m_tiles, n_tiles, splits, kb_per_split;
     int prepared;            // every problem comes with a ready-made fp16 block-scale table
-    int debug;               // bit 0: producers skip the decode, bit 1: phase trace (tuning only)
+    int debug;               // NF4B200_DEBUG; the kernel looks at it only in -DNF4B200_TRACE builds
 };
 
 struct GemmMaps {
@@ -206,8 +206,10 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// Optional phase timestamps for tuning (NF4B200_DEBUG bit 1): producer thread 0 of each CTA records
-// %globaltimer at fixed points of its first TRACE_UNITS units.
+// Phase timestamps for tuning, compiled in only with -DNF4B200_TRACE (then switched on at run time
+// by NF4B200_DEBUG bit 1): producer thread 0 of each CTA records %globaltimer at fixed points of
+// its first TRACE_UNITS units. A normal build carries none of it.
+#ifdef NF4B200_TRACE
 constexpr int TRACE_CTAS = 160, TRACE_UNITS = 4, TRACE_STAMPS = 8;
 __device__ unsigned long long g_trace[TRACE_CTAS * TRACE_UNITS * TRACE_STAMPS];
 
@@ -231,6 +233,12 @@ __device__ unsigned long long g_trace2[2 * TRACE2_EVENTS * TRACE2_ITERS];
         if ((p.debug & 2) && blockIdx.x < 2 && unit_iter2 == 0 && (it_) < TRACE2_ITERS)         \
             g_trace2[(blockIdx.x * TRACE2_EVENTS + (ev)) * TRACE2_ITERS + (it_)] = globaltimer_ns(); \
     } while (0)
+#define NF4_TUNE(bit) ((p.debug & (bit)) != 0)  // tuning switches: skip decode (1), skip MMAs (4)
+#else
+#define NF4_TRACE(slot) do { } while (0)
+#define NF4_TRACE2(ev, it_) do { (void)unit_iter2; } while (0)
+#define NF4_TUNE(bit) false
+#endif
 
 // One work unit of the persistent loop.
 struct Unit {
@@ -300,7 +308,8 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
     constexpr uint32_t ARRIVALS = CG * PRODUCER_WARPS;  // "TMEM drained" arrivals (all warps)
     // "operands ready" arrivals: the decoding warps of both CTAs, plus one from the peer CTA that
     // vouches for its activation tile
-    constexpr uint32_t W_ARRIVALS = CG * DW + (CG == 2 ? 1 : 0);
+    // plus the leader's own TMA (its expect_tx arrive), so the issuers watch a single barrier
+    constexpr uint32_t W_ARRIVALS = CG * DW + (CG == 2 ? 1 : 0) + 1;
     constexpr int NC = L::NC;
     // With two accumulators each has its own issuing thread (warps 17 and 19, different
     // schedulers): the tensor pipe queues only a couple of MMAs, so the barrier checks one
@@ -384,7 +393,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
 
     // Warp-wide waits: one lane polls the barrier, the others sleep at the warp vote. Keeps the
     // shared-memory pipe free of 31 redundant polls per warp.
-    const uint32_t WAIT_SLEEP_NS = (p.debug >> 12) ? (uint32_t)(p.debug >> 12) : 64u;  // tuning
+    constexpr uint32_t WAIT_SLEEP_NS = 64u;
     auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool {
         if (mbar_try_wait(bar, parity)) return true;
         const unsigned long long t0 = globaltimer_ns();
@@ -431,13 +440,15 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                         const int kbg = w.kb_begin + it;                 // group-wide k-block
                         const int pi = TRANS_W ? find_problem(p, kbg) : w.prob;
                         const int kb = TRANS_W ? kbg - p.prob[pi].first : kbg;
-                        mbar_arrive_expect_tx(bar_full_tma(s), L::A_BYTES);
+                        const uint32_t landed = rank == 0 ? bar_full_w(s) : bar_full_tma(s);
+                        mbar_arrive_expect_tx(landed, L::A_BYTES);
 #pragma unroll
                         for (int a = 0; a < NACC; ++a)
                             tma_load_2d(sa + a * (128 * BK * 2), &maps.act[TRANS_W ? pi : 0], kb * BK,
-                                        w.m0 + a * (128 * CG) + (int)rank * 128, bar_full_tma(s));
+                                        w.m0 + a * (128 * CG) + (int)rank * 128, landed);
                     } else {
-                        mbar_arrive(bar_full_tma(s));  // extension step: producers bring operands
+                        // extension step: the producers bring the operands
+                        mbar_arrive(rank == 0 ? bar_full_w(s) : bar_full_tma(s));
                     }
                 }
             }
@@ -480,14 +491,12 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                 for (int s = 0; s < STAGES; ++s) {
                     if (!have) continue;
                     const uint32_t unit_iter2 = unit_iter;
-                    if (!mbar_wait(bar_full_tma(s), ph, abort_flag)) { fail = 2; have = false; continue; }
-                    NF4_TRACE2(3, it);
                     if (!mbar_wait_cluster(bar_full_w(s), ph, abort_flag)) { fail = 3; have = false; continue; }
                     NF4_TRACE2(4, it);
                     tc_fence_after_sync();
                     const uint32_t a4 = base4 + (uint32_t)s * (L::STAGE_BYTES >> 4);
                     const uint32_t w4 = a4 + (L::A_BYTES >> 4);
-                    if (p.debug & 4) {
+                    if (NF4_TUNE(4)) {
                         // tuning aid: no MMAs, the commits below fire at once
                     } else if (it < w.nkb) {
                         const uint32_t first = it > 0 ? 1u : 0u;
@@ -749,7 +758,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                     // in registers across that wait costs spills under the 96-register cap)
                     uint32_t cw[WORDS];
                     __half2 scale2 = __half2half2(__ushort_as_half((unsigned short)0));
-                    if (!(p.debug & 1)) {
+                    if (!NF4_TUNE(1)) {
                         if (L::TABLES > 1 && p.n_prob > 1) {
                             const int pi = (int)lds32(smem_base + L::META_OFF + 4u * c);
                             if (pi != lut_prob) load_lut(pi);
@@ -783,7 +792,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                     if (lane == 0) mbar_arrive(bar_empty_c(c));
                     if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
                     if (pt == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(7, it); }
-                    if (!(p.debug & 1)) {
+                    if (!NF4_TUNE(1)) {
 #pragma unroll
                         for (int i = 0; i < WORDS; ++i)
                             sts128(dst_off[i] + stage_off, decode_word_reg(cw[i], lut, scale2));
@@ -1368,6 +1377,7 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why
 
 }  // namespace nf4
 
+#ifdef NF4B200_TRACE
 // Tuning aid, not part of the public ABI: copies the phase timestamps to the host.
 extern "C" int nf4dbg_read_trace(unsigned long long* dst, int max_entries) {
     const int n = nf4::TRACE_CTAS * nf4::TRACE_UNITS * nf4::TRACE_STAMPS;
@@ -1386,3 +1396,4 @@ extern "C" int nf4dbg_read_trace2(unsigned long long* dst, int max_entries) {
         return -3;
     return n;
 }
+#endif  // NF4B200_TRACE
