@@ -289,9 +289,12 @@ __device__ __forceinline__ int ext_problem(const GemmParams& p, int e) {
     return r;
 }
 
-template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES>
+// PREP = true: every problem comes with its scale table (known at compile time, so the hot loops
+// carry no trace of the gather path); PREP = false decides at run time from p.prepared.
+template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmParams p) {
+    const bool prepared = PREP || p.prepared != 0;
     using L = SmemLayout<CG, NACC, STAGES, TABLES>;
     constexpr int NB = L::NB;
     // The 16 producer warps form 16 / DW groups of DW warps that take the k-blocks in turn (all 16
@@ -374,7 +377,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
     // while the previous kernel of the stream was still draining; global memory comes after this.
     grid_dep_wait();
     grid_dep_launch();
-    if (threadIdx.x < 256 && !p.prepared) {
+    if (threadIdx.x < 256 && !prepared) {
         for (int i = 0; i < L::TABLES && i < p.n_prob; ++i)
             if (p.prob[i].nested) table2[i * 256 + threadIdx.x] = p.prob[i].code2[threadIdx.x];
     }
@@ -607,10 +610,10 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                 if (lane == 0) {
                     const uint32_t dst = smem_base + L::CODES_OFF + (uint32_t)c * L::C_BYTES;
                     if (L::TABLES > 1) sts32(smem_base + L::META_OFF + 4u * c, (uint32_t)pi);
-                    mbar_arrive_expect_tx(bar_full_c(c), L::C_BYTES + (p.prepared ? NB * 2 : 0));
+                    mbar_arrive_expect_tx(bar_full_c(c), L::C_BYTES + (prepared ? NB * 2 : 0));
                     if (TRANS_W) tma_load_2d(dst, &maps.codes[pi], nb0 / 2, kb * BK, bar_full_c(c));
                     else         tma_load_2d(dst, &maps.codes[pi], kb * (BK / 2), nb0, bar_full_c(c));
-                    if (p.prepared) {
+                    if (prepared) {
                         // ready-made fp16 scales of the tile: forward NB rows of column kb,
                         // backward 64 rows x CB column blocks
                         const uint32_t sd = smem_base + L::SCALE_OFF + (uint32_t)c * L::S_BYTES;
@@ -618,7 +621,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                         else         tma_load_2d(sd, &maps.scales[pi], nb0, kb, bar_full_c(c));
                     }
                 }
-                if (p.prepared) {
+                if (prepared) {
                     mbar_arrive(bar_full_c(c));  // (the barrier counts one arrival per lane)
                     if (++c == NC) { c = 0; cph ^= 1u; }
                     continue;
@@ -763,7 +766,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                             const int pi = (int)lds32(smem_base + L::META_OFF + 4u * c);
                             if (pi != lut_prob) load_lut(pi);
                         }
-                        if (p.prepared) {
+                        if (prepared) {
                             const uint32_t h = lds16(prep_off + c * L::S_BYTES);
                             const uint32_t hh = __byte_perm(h, 0u, 0x1010u);
                             scale2 = *reinterpret_cast<const __half2*>(&hh);
@@ -788,9 +791,12 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                             cw[0] = q.x; cw[1] = q.y;
                         }
                     }
+                    if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
+                    // The code-ring slot goes back only now, with the operand slot in hand. Handing
+                    // it back before that wait gave intermittently wrong weight rows in the
+                    // single-CTA kernel (first calls on a new weight, M <= 128).
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_empty_c(c));
-                    if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
                     if (pt == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(7, it); }
                     if (!NF4_TUNE(1)) {
 #pragma unroll
@@ -1172,11 +1178,11 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
     return plan_gemm_group(m, &n_w, 1, k_w, trans_w, sm_count);
 }
 
-template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES>
+template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP = false>
 static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaStream_t stream,
                               const char** why) {
     using L = SmemLayout<CG, NACC, STAGES, TABLES>;
-    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW, TABLES>;
+    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW, TABLES, PREP>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::DYNAMIC_BYTES);
     if (e != cudaSuccess) { *why = "cudaFuncSetAttribute(shared memory)"; return e; }
@@ -1345,19 +1351,26 @@ cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, cons
         }
     }
     const GemmPlan pl = plan_gemm_group(a.m, n_w, ga.count, a.k_w, a.trans_w, a.sm_count);
-    // Two alternating groups of 8 decoding warps measured faster than one group of 16 in both
-    // directions (NF4B200_DEBUG bit 5 selects the single group, for tuning).
-    const bool dw8 = (debug_flags() & 32) == 0;
+    // Pair kernels: two alternating groups of 8 decoding warps for the 512-row tiles (measured
+    // faster than one group of 16 in both directions), one group of 16 for the 256-row tiles; each
+    // in a variant specialised for "every weight brings its scale table".
+    bool prep = true;
+    for (int i = 0; i < ga.count; ++i)
+        if (ga.item[i].scales16 == nullptr) prep = false;
     if (pl.cg == 2 && pl.nacc == 2) {
-        if (dw8)
-            return a.trans_w ? launch_cfg<2, 2, true, 4, 8, MAXP>(ga, pl, stream, why)
-                             : launch_cfg<2, 2, false, 4, 8, MAXP>(ga, pl, stream, why);
-        return a.trans_w ? launch_cfg<2, 2, true, 4, 16, MAXP>(ga, pl, stream, why)
-                         : launch_cfg<2, 2, false, 4, 16, MAXP>(ga, pl, stream, why);
+        if (prep)
+            return a.trans_w ? launch_cfg<2, 2, true, 4, 8, MAXP, true>(ga, pl, stream, why)
+                             : launch_cfg<2, 2, false, 4, 8, MAXP, true>(ga, pl, stream, why);
+        return a.trans_w ? launch_cfg<2, 2, true, 4, 8, MAXP>(ga, pl, stream, why)
+                         : launch_cfg<2, 2, false, 4, 8, MAXP>(ga, pl, stream, why);
     }
-    if (pl.cg == 2)
+    if (pl.cg == 2) {
+        if (prep)
+            return a.trans_w ? launch_cfg<2, 1, true, 6, 16, MAXP, true>(ga, pl, stream, why)
+                             : launch_cfg<2, 1, false, 6, 16, MAXP, true>(ga, pl, stream, why);
         return a.trans_w ? launch_cfg<2, 1, true, 6, 16, MAXP>(ga, pl, stream, why)
                          : launch_cfg<2, 1, false, 6, 16, MAXP>(ga, pl, stream, why);
+    }
     if (pl.nacc == 2)
         return a.trans_w ? launch_cfg<1, 2, true, 3, 16, 1>(ga, pl, stream, why)
                          : launch_cfg<1, 2, false, 3, 16, 1>(ga, pl, stream, why);

@@ -149,3 +149,24 @@ def test_split_k_equals_single_pass_and_is_deterministic(cuda_lib, monkeypatch):
     w = oracle_weight(packed, state)
     assert rel(y1, nf4_oracle.linear_fwd(x.cpu(), w, bias.cpu())) <= TOL
     cuda_lib.device_status()
+
+
+def test_sm_limit_keeps_results(cuda_lib):
+    """nf4b200_set_sm_limit: fewer SMs for the persistent grids, same numbers."""
+    from hackaton_b200 import _lib
+    from hackaton_b200.nf4 import linear_backward_dx, linear_forward
+
+    packed, state = synthetic_weight(1536, 1536, True, seed=4, device="cuda")
+    w = oracle_weight(packed, state)
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(700, 1536, generator=g).half()
+    dy = torch.randn(700, 1536, generator=g).half()
+    try:
+        _lib.set_sm_limit(64)
+        y = linear_forward(x.cuda(), packed, None, state)
+        dx = linear_backward_dx(dy.cuda(), packed, state)
+    finally:
+        _lib.set_sm_limit(0)
+    assert rel(y, nf4_oracle.linear_fwd(x, w)) <= TOL
+    assert rel(dx, nf4_oracle.linear_bwd(dy, w)) <= TOL
+    cuda_lib.device_status()

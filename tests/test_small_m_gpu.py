@@ -60,3 +60,21 @@ def test_small_m_matches_tensor_core_kernel(cuda_lib):
         finally:
             nf4.PREPARED_SCALES = True
     assert (outs[0] - outs[1]).abs().max() <= 2e-3 * outs[1].abs().max()
+
+
+def test_fresh_weights_repeatable(cuda_lib):
+    """First calls on freshly created weights (cold caches, scale table just built), M <= 128 with
+    split-K: two calls in a row must give the same bits, for several weights in a row. Guards the
+    hand-back order of the code ring (a slot released before the operand slot was obtained gave
+    intermittently wrong weight rows in the single-CTA kernel)."""
+    from hackaton_b200.nf4 import linear_forward
+
+    n, k = 1536, 8960
+    for rep in range(6):
+        for m in (33, 64, 20, 128):
+            packed, state = synthetic_weight(n, k, True, seed=100 + rep * 7 + m, device="cuda")
+            x = torch.randn(m, k, device="cuda").half()
+            y1 = linear_forward(x, packed, None, state)
+            y2 = linear_forward(x, packed, None, state)
+            assert torch.equal(y1, y2), (rep, m)
+    cuda_lib.device_status()
