@@ -539,9 +539,9 @@ def run_single(args):
         "bound": "tensor", "achieved": achieved, "peak": pk["tflops_sustained"], "unit": "TFLOP/s",
         "frac": achieved / pk["tflops_sustained"],
         # dram__bytes_read.sum + dram__bytes_write.sum of one gate_proj forward launch in an ncu
-        # capture of this benchmark (13.69 MB + 0.25 MB; the algorithmic input is 13.82 MB: codes,
+        # capture of this benchmark (13.67 MB + 0.13 MB; the algorithmic input is 13.82 MB: codes,
         # fp16 scale table and X)
-        "traffic": 13.94e6, "traffic_unit": "bytes per launch, from an ncu capture of this command",
+        "traffic": 13.80e6, "traffic_unit": "bytes per launch, from an ncu capture of this command",
         "kernel": "nf4_gemm_kernel<CG=2,NACC=2,fwd> (CTA pairs, 512x256 tiles) on gate_proj (M=2048, N=8960, K=1536)",
         "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
         "timing": f"CUDA events around a graph of {reps} launches over the rotating layers"
