@@ -98,6 +98,110 @@ def patch_peft_lora():
     cls.forward = lora_forward_for(cls.forward)
 
 
+class SiblingGroup:
+    """Projections that are fed the same tensor (q/k/v of an attention block, gate/up of an MLP:
+    the call sites solution/patches.py:32-41 and :98-99 of the reference), run as one grouped
+    launch without touching the code that calls them.
+
+    After `install()`, the first of the modules to be called with a tensor x computes the outputs
+    of all of them (`nf4_linear_group`: one fused kernel forward, one summed dX backward) and
+    keeps the siblings' shares; when a sibling is then called with the very same x it returns its
+    share. Anything the grouped kernel does not cover (a call with extra arguments, an input that
+    is not eligible, an adapter with active dropout, merged or disabled adapters, a rank other
+    than 16) goes to the module's own forward, as everywhere in this file.
+
+    Members may be bitsandbytes `Linear4bit` modules or peft LoRA wrappers around them
+    (attributes as in `lora_forward_for`)."""
+
+    def __init__(self, modules):
+        self.modules = list(modules)
+        self.originals = [m.forward for m in self.modules]
+        self._x = None
+        self._shares = {}
+
+    def install(self):
+        for i, m in enumerate(self.modules):
+            m.forward = self._forward_for(i)
+        return self
+
+    def remove(self):
+        for m, f in zip(self.modules, self.originals):
+            m.forward = f
+        self._x, self._shares = None, {}
+
+    def _forward_for(self, index):
+        def forward(x, *args, **kwargs):
+            return self._call(index, x, *args, **kwargs)
+        forward._nf4b200 = True
+        return forward
+
+    def _projection(self, module, x):
+        from .group import Projection
+
+        base = getattr(module, "base_layer", module)
+        weight = getattr(base, "weight", None)
+        state = getattr(weight, "quant_state", None)
+        bias = getattr(base, "bias", None)
+        if weight is None or not _eligible(x, state, weight, bias):
+            return None
+        if not hasattr(module, "lora_A"):
+            return Projection(weight, state, bias)
+        adapters = list(getattr(module, "active_adapters", ()))
+        if (getattr(module, "disable_adapters", False) or getattr(module, "merged", False)
+                or len(adapters) != 1 or adapters[0] not in module.lora_A):
+            return None
+        name = adapters[0]
+        lora_a, lora_b = module.lora_A[name].weight, module.lora_B[name].weight
+        dropout = module.lora_dropout[name]
+        if (lora_a.shape[0] != RANK or getattr(module.lora_A[name], "bias", None) is not None
+                or getattr(module.lora_B[name], "bias", None) is not None
+                or (getattr(dropout, "training", False) and getattr(dropout, "p", 0.0) > 0.0)):
+            return None
+        return Projection(weight, state, bias, lora_a, lora_b, float(module.scaling[name]))
+
+    def _call(self, index, x, *args, **kwargs):
+        if args or kwargs:
+            return self.originals[index](x, *args, **kwargs)
+        if self._x is x and index in self._shares:
+            y = self._shares.pop(index)
+            if not self._shares:
+                self._x = None
+            return y
+        projections = [self._projection(m, x) for m in self.modules]
+        if any(p is None for p in projections):
+            return self.originals[index](x)
+        from . import group as _group
+        ys = _group.nf4_linear_group(x, projections)
+        self._x = x
+        self._shares = {i: y for i, y in enumerate(ys) if i != index}
+        return ys[index]
+
+
+SIBLINGS = (("q_proj", "k_proj", "v_proj"), ("gate_proj", "up_proj"))
+
+
+def patch_sibling_projections(model):
+    """Walks `model.modules()` and groups, inside every block that has them, q_proj/k_proj/v_proj
+    and gate_proj/up_proj (the attribute names of transformers' Qwen2 attention and MLP blocks)
+    when all members are 4-bit linears or LoRA wrappers around 4-bit linears with the same number
+    of input features. Returns the installed groups (call `.remove()` on them to undo)."""
+    groups = []
+    for block in model.modules():
+        for names in SIBLINGS:
+            members = [getattr(block, n, None) for n in names]
+            if any(m is None for m in members):
+                continue
+            bases = [getattr(m, "base_layer", m) for m in members]
+            if not all(_is_4bit_linear(b) for b in bases):
+                continue
+            if len({getattr(b, "in_features", None) for b in bases}) != 1:
+                continue
+            if any(getattr(m.forward, "_nf4b200", False) for m in members):
+                continue   # already grouped
+            groups.append(SiblingGroup(members).install())
+    return groups
+
+
 def apply():
     """The entry point the reference's harness calls once before the model is built
     (solution/__init__.py:23-33), restricted to the NF4 path."""

@@ -118,7 +118,7 @@ def lora_bwd(grad_y, x, weight, lora_a, lora_b, scaling):
 
 def max_rel_err(got, want):
     """max |got - want| / max |want| : the error measure of the fp16 tolerance (<= 1e-2)."""
-    got, want = got.float(), want.float()
+    got, want = got.detach().float(), want.detach().float()
     denom = want.abs().max().clamp_min(1e-30)
     return float((got - want).abs().max() / denom)
 

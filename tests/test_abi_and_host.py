@@ -104,3 +104,80 @@ def test_lora_patch_falls_through_to_original():
     module = types.SimpleNamespace(active_adapters=["default"], disable_adapters=True,
                                    merged=False, base_layer=None, lora_A={}, lora_B={})
     assert forward(module, torch.zeros(2, 64)) == "orig" and seen == [1]
+
+
+def test_sibling_group_routes_one_launch(monkeypatch):
+    """q/k/v called one after the other with the same tensor: one grouped computation, every
+    module gets its own share; another tensor, or an ineligible input, starts over or falls
+    through to the module's own forward."""
+    import types
+
+    from hackaton_b200 import group, patches
+
+    class Lin(torch.nn.Module):
+        def __init__(self, tag):
+            super().__init__()
+            self.tag = tag
+            self.weight = types.SimpleNamespace(quant_state=object())
+            self.bias = None
+
+        def forward(self, x):
+            return ("own", self.tag)
+
+    calls = []
+
+    def fake_group(x, projections):
+        calls.append(len(projections))
+        return [("grouped", i, id(x)) for i in range(len(projections))]
+
+    eligible = {"ok": True}
+    monkeypatch.setattr(patches, "_eligible", lambda x, state, weight, bias: eligible["ok"])
+    monkeypatch.setattr(group, "nf4_linear_group", fake_group)
+    q, k, v = Lin("q"), Lin("k"), Lin("v")
+    g = patches.SiblingGroup([q, k, v]).install()
+    x = torch.zeros(2, 4)
+    assert q(x) == ("grouped", 0, id(x))
+    assert v(x) == ("grouped", 2, id(x))
+    assert k(x) == ("grouped", 1, id(x))
+    assert calls == [3]
+    x2 = torch.zeros(2, 4)
+    assert k(x2) == ("grouped", 1, id(x2)) and calls == [3, 3]
+    assert k(x2) == ("grouped", 1, id(x2)) and calls == [3, 3, 3]   # its share was already taken
+    eligible["ok"] = False
+    assert q(torch.zeros(2, 4)) == ("own", "q")
+    g.remove()
+    eligible["ok"] = True
+    assert q(x) == ("own", "q")
+
+
+def test_patch_sibling_projections_finds_blocks(monkeypatch):
+    import types
+
+    from hackaton_b200 import patches
+
+    class Lin(torch.nn.Module):
+        def __init__(self, n_in):
+            super().__init__()
+            self.in_features = n_in
+
+        def forward(self, x):
+            return x
+
+    monkeypatch.setattr(patches, "_is_4bit_linear", lambda m: isinstance(m, Lin))
+
+    class Attn(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q_proj, self.k_proj, self.v_proj, self.o_proj = Lin(8), Lin(8), Lin(8), Lin(8)
+
+    class Mlp(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj, self.up_proj, self.down_proj = Lin(8), Lin(8), Lin(16)
+
+    model = torch.nn.Sequential(Attn(), Mlp(), Attn())
+    groups = patches.patch_sibling_projections(model)
+    assert [len(g.modules) for g in groups] == [3, 2, 3]
+    assert patches.patch_sibling_projections(model) == []      # nothing left to group
+    for g in groups:
+        g.remove()

@@ -83,3 +83,74 @@ def test_group_equals_one_at_a_time(cuda_lib):
     dx = linear_backward_dx_group(dys, ws)
     ref = sum(linear_backward_dx(dy, p, s).float() for dy, (p, s) in zip(dys, ws))
     assert float((dx.float() - ref).abs().max() / ref.abs().max()) < 5e-3
+
+
+def test_sibling_modules_share_one_launch(cuda_lib):
+    """Module-level grouping: q/k/v-like modules patched with SiblingGroup give the same results
+    as calling each projection's own fused op, forward and backward, and LoRA wrappers with
+    attributes like peft's are followed."""
+    import types
+
+    from hackaton_b200 import nf4_linear, nf4_lora_linear
+    from hackaton_b200.patches import SiblingGroup
+
+    m, k, ns = 512, 1536, (1536, 256, 256)
+    g = torch.Generator(device="cuda").manual_seed(5)
+
+    class Base(torch.nn.Module):
+        def __init__(self, n, seed):
+            super().__init__()
+            packed, state = synthetic_weight(n, k, True, seed=seed, device="cuda")
+            self.weight = packed
+            self.weight.quant_state = state
+            self.bias = None
+            self.in_features = k
+
+        def forward(self, x):
+            return nf4_linear(x, self.weight, self.bias, self.weight.quant_state)
+
+    class Wrapped(torch.nn.Module):
+        def __init__(self, n, seed):
+            super().__init__()
+            self.base_layer = Base(n, seed)
+            a = ((torch.rand(16, k, generator=g, device="cuda") * 2 - 1) / k ** 0.5).half()
+            b = (torch.randn(n, 16, generator=g, device="cuda") * 0.2).half()
+            self.lora_A = {"default": types.SimpleNamespace(weight=a.requires_grad_(), bias=None)}
+            self.lora_B = {"default": types.SimpleNamespace(weight=b.requires_grad_(), bias=None)}
+            self.lora_dropout = {"default": torch.nn.Identity()}
+            self.scaling = {"default": 2.0}
+            self.active_adapters = ["default"]
+            self.disable_adapters = False
+            self.merged = False
+
+        def forward(self, x):
+            b = self.base_layer
+            return nf4_lora_linear(x, b.weight, b.bias, b.weight.quant_state,
+                                   self.lora_A["default"].weight, self.lora_B["default"].weight, 2.0)
+
+    mods = [Wrapped(ns[0], 70), Base(ns[1], 71), Wrapped(ns[2], 72)]
+    x = torch.randn(m, k, generator=g, device="cuda").half()
+    dys = [torch.randn(m, n, generator=g, device="cuda").half() for n in ns]
+
+    def run():
+        xg = x.clone().requires_grad_()
+        ys = [mod(xg) for mod in mods]
+        torch.autograd.backward(ys, dys)
+        grads = [xg.grad.clone()]
+        for mod in mods:
+            if hasattr(mod, "lora_A"):
+                for d in (mod.lora_A, mod.lora_B):
+                    grads.append(d["default"].weight.grad.clone())
+                    d["default"].weight.grad = None
+        return [y.detach() for y in ys], grads
+
+    ys_ref, grads_ref = run()
+    group = SiblingGroup(mods).install()
+    ys, grads = run()
+    assert group._shares == {} and group._x is None         # every share was collected
+    group.remove()
+    for y, r in zip(ys, ys_ref):
+        assert nf4_oracle.max_rel_err(y.cpu(), r.cpu()) <= 2e-3
+    for a, r in zip(grads, grads_ref):
+        assert nf4_oracle.max_rel_err(a.cpu(), r.cpu()) <= 1e-2
+    cuda_lib.device_status()
