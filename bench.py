@@ -497,10 +497,14 @@ def run_single(args):
     from hackaton_b200.nf4 import linear_forward, linear_backward_dx
     reps = 2 * N_LAYERS
 
-    def time_kernel(fn):
+    sustained = {}
+
+    def time_kernel(fn, sustain_key=None):
         """Average device time (ms) of one launch: `reps` launches over the rotating layers, as one
         CUDA graph between two events (eager launches of a ~55 us kernel are bound by the host's
-        launch rate, not by the kernel), median of five replays."""
+        launch rate, not by the kernel), median of five replays. With `sustain_key` the graph is
+        then replayed back to back for about three seconds and the last third is timed as well,
+        with the clocks sampled: the same kernel under the board's power limit."""
         for i in range(8):
             fn(i)
         torch.cuda.synchronize()
@@ -515,8 +519,17 @@ def run_single(args):
                 torch.cuda.current_stream().wait_stream(side)
                 g.replay()
                 _, per, _ = timed_steps(lambda i: g.replay(), 5)
+                burst = sorted(per)[2]
+                if sustain_key is not None:
+                    n = max(30, int(1000.0 / burst))      # replays per second
+                    smp = ClockSampler(0)
+                    smp.start()
+                    for _ in range(2 * n):
+                        g.replay()
+                    tot, _, _ = timed_steps(lambda i: g.replay(), n)
+                    sustained[sustain_key] = (tot / (n * reps), smp.stop())
                 del outs
-                return sorted(per)[2] / reps
+                return burst / reps
             except Exception as exc:
                 print(f"[bench] kernel graph capture failed ({exc!r}); timing eager launches",
                       file=sys.stderr)
@@ -526,7 +539,8 @@ def run_single(args):
     kern = {}
     x_mlp, x_down = acts["x_mlp"], acts["x_down"]
     kern["gate_fwd"] = time_kernel(lambda i: linear_forward(
-        x_mlp, layers[i % N_LAYERS]["gate"]["packed"], None, layers[i % N_LAYERS]["gate"]["state"]))
+        x_mlp, layers[i % N_LAYERS]["gate"]["packed"], None, layers[i % N_LAYERS]["gate"]["state"]),
+        sustain_key="gate_fwd")
     kern["down_fwd"] = time_kernel(lambda i: linear_forward(
         x_down, layers[i % N_LAYERS]["down"]["packed"], None, layers[i % N_LAYERS]["down"]["state"]))
     kern["gate_bwd"] = time_kernel(lambda i: linear_backward_dx(
@@ -535,20 +549,30 @@ def run_single(args):
         acts["dy_down"], layers[i % N_LAYERS]["down"]["packed"], layers[i % N_LAYERS]["down"]["state"]))
     gemm_flops = 2.0 * m * 8960 * 1536
     achieved = gemm_flops / (kern["gate_fwd"] * 1e-3) / 1e12
+    # The kernel is timed alone in bursts of a few milliseconds, at full clocks: the denominator is
+    # the burst figure of the measured cuBLAS peak. `sustained` is the same launch under the power
+    # limit, against the sustained figure.
     roofline = {
-        "bound": "tensor", "achieved": achieved, "peak": pk["tflops_sustained"], "unit": "TFLOP/s",
-        "frac": achieved / pk["tflops_sustained"],
+        "bound": "tensor", "achieved": achieved, "peak": pk["tflops_burst"], "unit": "TFLOP/s",
+        "frac": achieved / pk["tflops_burst"],
         # dram__bytes_read.sum + dram__bytes_write.sum of one gate_proj forward launch in an ncu
         # capture of this benchmark (13.67 MB + 0.13 MB; the algorithmic input is 13.82 MB: codes,
         # fp16 scale table and X)
         "traffic": 13.80e6, "traffic_unit": "bytes per launch, from an ncu capture of this command",
         "kernel": "nf4_gemm_kernel<CG=2,NACC=2,fwd> (CTA pairs, 512x256 tiles) on gate_proj (M=2048, N=8960, K=1536)",
-        "peak_source": pk["source"] + " (sustained cuBLAS bf16)",
+        "peak_source": pk["source"] + " (burst cuBLAS bf16; the kernel is timed alone)",
         "timing": f"CUDA events around a graph of {reps} launches over the rotating layers"
                   if use_graphs else "CUDA events around eager launches",
         "us_per_launch": {k: v * 1e3 for k, v in kern.items()},
         "tflops": {k: gemm_flops / (v * 1e-3) / 1e12 for k, v in kern.items()},
     }
+    if "gate_fwd" in sustained:
+        ms, clk = sustained["gate_fwd"]
+        a = gemm_flops / (ms * 1e-3) / 1e12
+        roofline["sustained"] = {
+            "achieved": a, "peak": pk["tflops_sustained"], "frac": a / pk["tflops_sustained"],
+            "us_per_launch": ms * 1e3, "clocks": clk,
+            "timing": "the same graph replayed back to back for ~3 s, last third timed"}
 
     # ---- end to end: public autograd API, inputs from pinned host memory every step.
     # Two sets of device buffers: the copy of step i+1's inputs (copy stream) runs under step i's
@@ -617,7 +641,8 @@ def run_single(args):
         "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(1),
         "weight_gbs": weight_bytes * args.steps / (total_ms * 1e-3) / 1e9,
-        "frac_of_tensor_peak": value / pk["tflops_sustained"],
+        "frac_of_tensor_peak": value / pk["tflops_burst"],
+        "frac_of_sustained_tensor_peak": value / pk["tflops_sustained"],
         "ms_per_28_layer_step": total_ms / args.steps * N_LAYERS,
         "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs,
         "step_ms_min_med_max": [min(per_step), statistics.median(per_step), max(per_step)],
@@ -725,13 +750,16 @@ def run_multi(args):
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": workload_config(world),
-            "frac_of_tensor_peak": value / (pk["tflops_sustained"] * world),
+            "frac_of_tensor_peak": value / (pk["tflops_burst"] * world),
+            "frac_of_sustained_tensor_peak": value / (pk["tflops_sustained"] * world),
             "gemm_only_ms_per_step": local_ms,
             "gemm_only_tflops": flops / (local_ms * 1e-3) / 1e12,
             "collective_bytes_per_step": {"all_gather_out": gathered, "all_reduce_dx": reduced},
             "roofline": {"bound": "tensor", "achieved": flops / (local_ms * 1e-3) / 1e12 / world,
-                         "peak": pk["tflops_sustained"], "unit": "TFLOP/s",
-                         "frac": flops / (local_ms * 1e-3) / 1e12 / world / pk["tflops_sustained"],
+                         "peak": pk["tflops_burst"], "unit": "TFLOP/s",
+                         "frac": flops / (local_ms * 1e-3) / 1e12 / world / pk["tflops_burst"],
+                         "peak_source": pk["source"] + " (burst cuBLAS bf16; timed regions of "
+                                        "tens of milliseconds)",
                          "traffic": None,
                          "kernel": "nf4_gemm_kernel, per GPU, local shards only (no collectives)"},
             "cpu_baseline": None,
