@@ -445,6 +445,112 @@ int64_t nf4b200_workspace_bytes_group(int count, const int64_t* n_rows, int64_t 
     return (int64_t)pl.ws_bytes;
 }
 
+// Bytes of one temporary [m, n_rows] fp16 array, rounded so that the next one stays aligned.
+static size_t swiglu_tmp_bytes(int64_t m, int64_t n_rows) {
+    return ((size_t)m * (size_t)n_rows * 2 + 255) / 256 * 256;
+}
+
+int64_t nf4b200_gate_up_swiglu_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int keep) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (n_rows <= 0 || n_cols <= 0 || m <= 0)
+        return fail(NF4B200_EINVAL, "gate_up_swiglu_workspace_bytes: bad shape");
+    if (m > 256) return 0;  // epilogue-fused kernel: no scratch
+    long long rows[2] = {n_rows, n_rows};
+    const nf4::GemmPlan pl = nf4::plan_gemm_group(m, rows, 2, n_cols, false, gemm_sms(d));
+    const size_t gemm_ws = (pl.ws_bytes + 255) / 256 * 256;
+    return (int64_t)(gemm_ws + (keep ? 0 : 2 * swiglu_tmp_bytes(m, n_rows)));
+}
+
+int nf4b200_gate_up_swiglu_fwd(const nf4b200_weight* gate_w, const nf4b200_weight* up_w,
+                               const void* x, int64_t m, int64_t ldx, void* gate_out, void* up_out,
+                               void* hidden, void* workspace, size_t workspace_bytes, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if ((rc = check_weight(gate_w, true)) != NF4B200_OK) return rc;
+    if ((rc = check_weight(up_w, true)) != NF4B200_OK) return rc;
+    if (gate_w->n_rows != up_w->n_rows || gate_w->n_cols != up_w->n_cols)
+        return fail(NF4B200_EINVAL, "gate_up_swiglu: gate and up weights differ in shape");
+    if ((gate_out == nullptr) != (up_out == nullptr))
+        return fail(NF4B200_EINVAL, "gate_up_swiglu: gate_out and up_out must both be given or NULL");
+    const int64_t n = gate_w->n_rows;
+    if (n % 8 != 0) return fail(NF4B200_EINVAL, "gate_up_swiglu: %lld output columns (multiple of 8 needed)", (long long)n);
+    if (!hidden || !aligned16(hidden) || (gate_out && (!aligned16(gate_out) || !aligned16(up_out))))
+        return fail(NF4B200_EINVAL, "gate_up_swiglu: outputs must be 16-byte aligned and hidden not NULL");
+    if ((rc = check_act("x", x, m, ldx, gate_w->n_cols)) != NF4B200_OK) return rc;
+    nf4::GemmGroupArgs ga;
+    ga.count = 2;
+    const nf4b200_weight* ws[2] = {gate_w, up_w};
+    void* outs[2] = {gate_out, up_out};
+    for (int i = 0; i < 2; ++i) {
+        nf4::GemmArgs& g = ga.item[i];
+        fill_gemm(g, ws[i], gemm_sms(d));
+        g.act = static_cast<const __half*>(x); g.m = m; g.ld_act = ldx;
+        g.out = static_cast<__half*>(outs[i]); g.ld_out = n;
+        g.bias = nullptr; g.ext_a = nullptr; g.ext_b = nullptr;
+        g.trans_w = false;
+        if ((rc = set_workspace(g, workspace, workspace_bytes)) != NF4B200_OK) return rc;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const char* why = "";
+    if (nf4::swiglu_fused_eligible(ga)) {
+        cudaError_t e = nf4::launch_gate_up_swiglu(ga, static_cast<__half*>(hidden), n, st, &why);
+        if (e != cudaSuccess)
+            return fail(NF4B200_ECUDA, "gate_up_swiglu: %s: %s", why, cudaGetErrorString(e));
+        return NF4B200_OK;
+    }
+    // few token rows: grouped GEMM, then the elementwise kernel; without gate_out / up_out the two
+    // arrays live at the end of the scratch
+    if (!gate_out) {
+        const size_t tmp = swiglu_tmp_bytes(m, n);
+        if (!workspace || workspace_bytes < 2 * tmp)
+            return fail(NF4B200_EINVAL, "gate_up_swiglu: workspace too small for the two temporaries "
+                                        "(nf4b200_gate_up_swiglu_workspace_bytes)");
+        uint8_t* base = static_cast<uint8_t*>(workspace) + (workspace_bytes - 2 * tmp) / 256 * 256;
+        for (int i = 0; i < 2; ++i) {
+            ga.item[i].out = reinterpret_cast<__half*>(base + i * tmp);
+            ga.item[i].workspace_bytes = (size_t)(base - static_cast<uint8_t*>(workspace));
+        }
+    }
+    cudaError_t e = nf4::launch_gemm_group(ga, st, &why);
+    if (e != cudaSuccess)
+        return fail(NF4B200_ECUDA, "gate_up_swiglu: %s: %s", why, cudaGetErrorString(e));
+    e = nf4::launch_swiglu_fwd(ga.item[0].out, ga.item[1].out, static_cast<__half*>(hidden), m * n,
+                               gemm_sms(d), st);
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "swiglu_fwd: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_swiglu_fwd(const void* gate, const void* up, void* hidden, int64_t n, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (n < 0 || (n > 0 && (!gate || !up || !hidden)))
+        return fail(NF4B200_EINVAL, "swiglu_fwd: NULL argument or negative size");
+    cudaError_t e = nf4::launch_swiglu_fwd(static_cast<const __half*>(gate), static_cast<const __half*>(up),
+                                           static_cast<__half*>(hidden), n, d->sms,
+                                           static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "swiglu_fwd: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_swiglu_bwd(const void* d_hidden, const void* gate, const void* up, void* d_gate,
+                       void* d_up, int64_t n, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (n < 0 || (n > 0 && (!d_hidden || !gate || !up || !d_gate || !d_up)))
+        return fail(NF4B200_EINVAL, "swiglu_bwd: NULL argument or negative size");
+    cudaError_t e = nf4::launch_swiglu_bwd(
+        static_cast<const __half*>(d_hidden), static_cast<const __half*>(gate),
+        static_cast<const __half*>(up), static_cast<__half*>(d_gate), static_cast<__half*>(d_up), n,
+        d->sms, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "swiglu_bwd: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
 int64_t nf4b200_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int backward) {
     DeviceInfo* d = nullptr;
     int rc = require_sm100(&d);

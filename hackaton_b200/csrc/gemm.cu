@@ -110,6 +110,8 @@ struct GemmParams {
     int nkb_total;           // k-blocks of the whole contraction
     int m_tiles, n_tiles, splits, kb_per_split;
     int prepared;            // every problem comes with a ready-made fp16 block-scale table
+    __half* hidden;          // SwiGLU epilogue only: silu(gate) * up, [m, n_w] with pitch ld_hidden
+    long long ld_hidden;
     int debug;               // NF4B200_DEBUG; the kernel looks at it only in -DNF4B200_TRACE builds
 };
 
@@ -259,13 +261,25 @@ __device__ __forceinline__ int find_problem(const GemmParams& p, int idx) {
     return r;
 }
 
-template <bool TRANS_W>
-__device__ __forceinline__ Unit make_unit(int u, const GemmParams& p, int rows_per_tile) {
+// EPI == 1 (SwiGLU epilogue, CTA pairs, forward): n-tile nt covers hidden columns nt*128 .. +127;
+// CTA 0 of the pair expands those rows of the gate weight (problem 0), CTA 1 the same rows of the
+// up weight (problem 1), so every token row finds gate in accumulator columns 0..127 and up in
+// 128..255. `prob` and `n0` are then per CTA: n0 + rank * 128 is the first weight row either way.
+template <bool TRANS_W, int EPI>
+__device__ __forceinline__ Unit make_unit(int u, const GemmParams& p, int rows_per_tile, int rank) {
     Unit w;
     const int tile = u / p.splits;
     w.slice = u % p.splits;
     const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
     w.m0 = mt * rows_per_tile;
+    if (EPI == 1) {
+        w.prob = rank;
+        w.n0 = nt * (BN / 2) - rank * (BN / 2);
+        w.kb_begin = 0;
+        w.nkb = p.nkb_total;
+        w.n_iter = w.nkb;
+        return w;
+    }
     w.prob = TRANS_W ? 0 : find_problem(p, nt);
     w.n0 = (nt - (TRANS_W ? 0 : p.prob[w.prob].first)) * BN;
     w.kb_begin = w.slice * p.kb_per_split;
@@ -291,7 +305,7 @@ __device__ __forceinline__ int ext_problem(const GemmParams& p, int e) {
 
 // PREP = true: every problem comes with its scale table (known at compile time, so the hot loops
 // carry no trace of the gather path); PREP = false decides at run time from p.prepared.
-template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP>
+template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP, int EPI = 0>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmParams p) {
     const bool prepared = PREP || p.prepared != 0;
@@ -307,6 +321,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
     static_assert(WORDS == 2 || WORDS == 4, "producer work split");
     constexpr uint32_t TMEM_COLS = NACC * BN;
     static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
+    static_assert(EPI == 0 || (CG == 2 && NACC == 2 && !TRANS_W), "SwiGLU epilogue: pair kernel, forward");
     constexpr int ROWS_PER_TILE = 128 * CG * NACC;  // token rows of a unit (whole pair)
     constexpr uint32_t ARRIVALS = CG * PRODUCER_WARPS;  // "TMEM drained" arrivals (all warps)
     // "operands ready" arrivals: the decoding warps of both CTAs, plus one from the peer CTA that
@@ -430,7 +445,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
             uint32_t g = 0;  // ring position, running across units
             uint32_t unit_iter2 = 0;
             for (int u = pair; u < total_units && !fail; u += n_pairs, ++unit_iter2) {
-                const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
+                const Unit w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
                 for (int it = 0; it < w.n_iter; ++it, ++g) {
                     const int s = (int)(g % STAGES);
                     const uint32_t ph = (g / STAGES) & 1u;
@@ -485,7 +500,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
             w.nkb = w.n_iter = 0;
             int it = 0;
             if (have) {
-                w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
+                w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
                 tc_fence_after_sync();
             }
             uint32_t ph = 0;
@@ -527,7 +542,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                         u += n_pairs;
                         have = u < total_units;
                         if (have) {
-                            w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
+                            w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
                             it = 0;
                             // the accumulators must have been drained (in both CTAs)
                             if (!mbar_wait_cluster(bar_tmem_empty, unit_iter & 1u, abort_flag)) {
@@ -545,7 +560,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
             // Peer CTA: tell the leader when this CTA's activation tile of a step has landed.
             uint32_t g = 0;
             for (int u = pair; u < total_units && !fail; u += n_pairs) {
-                const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
+                const Unit w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
                 for (int it = 0; it < w.n_iter; ++it, ++g) {
                     const int s = (int)(g % STAGES);
                     if (!mbar_wait(bar_full_tma(s), (g / STAGES) & 1u, abort_flag)) { fail = 8; break; }
@@ -570,7 +585,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         int c = 0;          // slot of the code ring
         uint32_t cph = 0;   // its phase
         for (int u = pair; u < total_units && !fail; u += n_pairs) {
-            const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
+            const Unit w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
             const int nb0 = w.n0 + (int)rank * NB;
             int cur_prob = -1, n_w_cur = 0, first_cur = 0, sh = 0;
             bool nested_cur = false;
@@ -733,7 +748,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         uint32_t cslot = 0, cphase = 0;  // position in the code ring
         uint32_t unit_iter = 0;
         for (int u = pair; u < total_units; u += n_pairs, ++unit_iter) {
-            const Unit w = make_unit<TRANS_W>(u, p, ROWS_PER_TILE);
+            const Unit w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
             NF4_TRACE(0);
             const int nb0 = w.n0 + (int)rank * NB;  // first weight-tile column of this CTA
             // Byte of the copied absmax word that holds this thread's first-level entry: block
@@ -874,7 +889,88 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                         else         mbar_arrive(bar_tmem_empty);
                     }
                 };
-                if (!split) {
+                if constexpr (EPI == 1) {
+                    // SwiGLU: this warp owns 32 token rows x 64 hidden columns of one accumulator;
+                    // gate sits in accumulator columns hc0.., up in 128 + hc0.. . Both are rounded
+                    // to fp16 first (the values an unfused linear would have written), the
+                    // product is formed in fp32 and rounded once.
+                    const int acc = grp >> 1, hc0 = (grp & 1) * 64;
+                    const uint32_t trow = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+                    const int col0 = w.n0 + (int)rank * NB + hc0;  // first hidden column of the box
+                    const int n_hidden = p.prob[0].n_w;
+                    const long long grow0 =
+                        (long long)w.m0 + acc * (128 * CG) + (int)rank * 128 + q * 32;
+                    auto store_box = [&](__half* base, long long ld) {
+                        const bool vec = (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(base) & 15) == 0);
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int rr = i * 4 + rd_row;
+                            const uint4 v = lds128(staging + rr * 128 + ((rd_chunk ^ (rr & 7)) << 4));
+                            const long long grow = grow0 + rr;
+                            const int colg = col0 + rd_chunk * 8;
+                            if (grow < p.m && colg < n_hidden) {
+                                __half* dst = base + grow * ld + colg;
+                                if (vec && colg + 8 <= n_hidden) {
+                                    *reinterpret_cast<uint4*>(dst) = v;
+                                } else {
+                                    const __half* hv = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e)
+                                        if (colg + e < n_hidden) dst[e] = hv[e];
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    };
+                    auto swiglu = [](uint32_t gbits, uint32_t ubits) {
+                        const float gf = __half2float(__float2half_rn(__uint_as_float(gbits)));
+                        const float uf = __half2float(__float2half_rn(__uint_as_float(ubits)));
+                        const float sig = __fdividef(1.f, 1.f + __expf(-gf));
+                        return gf * sig * uf;
+                    };
+#pragma unroll 1
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t gr[16], ur[16];
+                        tmem_ld_32x16(trow + hc0 + j * 16, gr);
+                        tmem_ld_32x16(trow + (BN / 2) + hc0 + j * 16, ur);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 2; ++i) {
+                            uint4 o;
+                            o.x = pack_half2(swiglu(gr[8 * i + 0], ur[8 * i + 0]), swiglu(gr[8 * i + 1], ur[8 * i + 1]));
+                            o.y = pack_half2(swiglu(gr[8 * i + 2], ur[8 * i + 2]), swiglu(gr[8 * i + 3], ur[8 * i + 3]));
+                            o.z = pack_half2(swiglu(gr[8 * i + 4], ur[8 * i + 4]), swiglu(gr[8 * i + 5], ur[8 * i + 5]));
+                            o.w = pack_half2(swiglu(gr[8 * i + 6], ur[8 * i + 6]), swiglu(gr[8 * i + 7], ur[8 * i + 7]));
+                            sts128(staging + lrow * 128 + (((j * 2 + i) ^ (lrow & 7)) << 4), o);
+                        }
+                    }
+                    const bool keep = p.prob[0].out != nullptr;  // training: gate and up as well
+                    if (!keep) release_tmem();
+                    store_box(p.hidden, p.ld_hidden);
+                    if (keep) {
+#pragma unroll 1
+                        for (int side = 0; side < 2; ++side) {
+#pragma unroll 1
+                            for (int h = 0; h < 2; ++h) {
+                                uint32_t r[32];
+                                tmem_ld_32x32(trow + side * (BN / 2) + hc0 + h * 32, r);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    uint4 o;
+                                    o.x = pack_half2(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+                                    o.y = pack_half2(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+                                    o.z = pack_half2(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+                                    o.w = pack_half2(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+                                    sts128(staging + lrow * 128 + (((h * 4 + i) ^ (lrow & 7)) << 4), o);
+                                }
+                            }
+                            if (side == 1) release_tmem();
+                            store_box(p.prob[side].out, p.prob[side].ld_out);
+                        }
+                    }
+                } else if (!split) {
                     // two 32-column chunks -> one [32 rows x 64 cols] fp16 box, written out as
                     // whole 128-byte lines
 #pragma unroll 1
@@ -1178,11 +1274,11 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
     return plan_gemm_group(m, &n_w, 1, k_w, trans_w, sm_count);
 }
 
-template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP = false>
+template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP = false, int EPI = 0>
 static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaStream_t stream,
-                              const char** why) {
+                              const char** why, __half* hidden = nullptr, long long ld_hidden = 0) {
     using L = SmemLayout<CG, NACC, STAGES, TABLES>;
-    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW, TABLES, PREP>;
+    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW, TABLES, PREP, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::DYNAMIC_BYTES);
     if (e != cudaSuccess) { *why = "cudaFuncSetAttribute(shared memory)"; return e; }
@@ -1248,6 +1344,8 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
         maps.codes[i] = maps.codes[0];
     }
     p.prepared = prepared ? 1 : 0;
+    p.hidden = hidden;
+    p.ld_hidden = ld_hidden;
     if (!TRANS_W)
         for (int i = 1; i < MAXP; ++i) maps.act[i] = maps.act[0];
     else
@@ -1323,6 +1421,35 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
         }
     }
     return e;
+}
+
+// gate / up projections with the SwiGLU product formed in the epilogue (EPI = 1). Eligible: two
+// weights of the same shape, no bias, no rank-16 term, more token rows than the single-CTA and
+// 256-row plans take, gate and up outputs both wanted or both left out.
+bool swiglu_fused_eligible(const GemmGroupArgs& ga) {
+    if (ga.count != 2) return false;
+    const GemmArgs &g = ga.item[0], &u = ga.item[1];
+    return !g.trans_w && g.m > 256 && g.n_w == u.n_w && g.k_w == u.k_w && g.bias == nullptr &&
+           u.bias == nullptr && g.ext_a == nullptr && u.ext_a == nullptr &&
+           (g.out == nullptr) == (u.out == nullptr) && !(debug_flags() & 16);
+}
+
+cudaError_t launch_gate_up_swiglu(const GemmGroupArgs& ga, __half* hidden, long long ld_hidden,
+                                  cudaStream_t stream, const char** why) {
+    *why = "";
+    if (!swiglu_fused_eligible(ga)) { *why = "SwiGLU epilogue: call not eligible"; return cudaErrorInvalidValue; }
+    const GemmArgs& a = ga.item[0];
+    GemmPlan pl = {};
+    pl.cg = 2;
+    pl.nacc = 2;
+    pl.m_tiles = (int)((a.m + 511) / 512);
+    pl.n_tiles = (int)((a.n_w + BN / 2 - 1) / (BN / 2));
+    pl.nkb = (int)((a.k_w + BK - 1) / BK);
+    pl.splits = 1;
+    pl.kb_per_split = pl.nkb;
+    if (a.scales16 != nullptr && ga.item[1].scales16 != nullptr)
+        return launch_cfg<2, 2, false, 4, 8, MAXP, true, 1>(ga, pl, stream, why, hidden, ld_hidden);
+    return launch_cfg<2, 2, false, 4, 8, MAXP, false, 1>(ga, pl, stream, why, hidden, ld_hidden);
 }
 
 cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, const char** why) {

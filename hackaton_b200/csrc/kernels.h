@@ -113,6 +113,20 @@ struct GemmGroupArgs {
 cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why);
 cudaError_t launch_gemm_group(const GemmGroupArgs& a, cudaStream_t stream, const char** why);
 
+// gate / up pair with hidden = silu(gate) * up formed in the GEMM epilogue (item[0] = gate,
+// item[1] = up; their `out` may both be null when only `hidden` is wanted). The caller checks
+// swiglu_fused_eligible first and otherwise runs launch_gemm_group + launch_swiglu_fwd.
+bool swiglu_fused_eligible(const GemmGroupArgs& ga);
+cudaError_t launch_gate_up_swiglu(const GemmGroupArgs& ga, __half* hidden, long long ld_hidden,
+                                  cudaStream_t stream, const char** why);
+// Elementwise SwiGLU on contiguous fp16 arrays (swiglu.cu): hidden = silu(gate) * up, and its
+// backward d_gate = d_hidden * up * sig * (1 + gate * (1 - sig)), d_up = d_hidden * gate * sig.
+cudaError_t launch_swiglu_fwd(const __half* gate, const __half* up, __half* hidden, long long n,
+                              int sm_count, cudaStream_t stream);
+cudaError_t launch_swiglu_bwd(const __half* d_hidden, const __half* gate, const __half* up,
+                              __half* d_gate, __half* d_up, long long n, int sm_count,
+                              cudaStream_t stream);
+
 // Weight-streaming forward kernel for M <= 64 (gemv.cu); launch_gemm* route eligible calls to it.
 bool gemv_eligible(const GemmArgs& a);
 cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t stream);

@@ -175,6 +175,32 @@ int64_t nf4b200_workspace_bytes_group(int count, const int64_t* n_rows, int64_t 
                                       int backward);
 
 /*
+ * SwiGLU, the step that follows the gate / up projections in the MLP (the reference's
+ * silu_mul_kernel and SiluMul, solution/kernels.py:39-96; call site solution/patches.py:39-41:
+ * `silu_mul(gate_proj(x16), up_proj(x16))`).
+ *
+ * nf4b200_gate_up_swiglu_fwd: gate = x . Wg^T, up = x . Wu^T, hidden = silu(gate) * up, all
+ *   [m, n_rows] fp16 without padding between rows. With more than 256 token rows this is ONE
+ *   kernel: each CTA pair expands 128 rows of Wg and the same 128 rows of Wu, so that a token's
+ *   gate and up values meet in one accumulator row and the product is formed while the tile is
+ *   drained; gate and up are rounded to fp16 first, so `hidden` holds what the two-step path
+ *   gives. gate_out and up_out may both be NULL (inference: only `hidden` is written, half the
+ *   output bytes of the plain grouped launch); training keeps them for the backward pass like
+ *   the reference does. With fewer rows it runs the grouped GEMM and nf4b200_swiglu_fwd; scratch
+ *   as nf4b200_gate_up_swiglu_workspace_bytes says (keep = 1 when gate_out / up_out are given).
+ * nf4b200_swiglu_fwd / nf4b200_swiglu_bwd: the elementwise form on n contiguous fp16 values:
+ *   hidden = gate * sigmoid(gate) * up;  d_up = d_hidden * gate * sig;
+ *   d_gate = d_hidden * up * sig * (1 + gate * (1 - sig)); fp32 arithmetic, one rounding.
+ */
+int nf4b200_gate_up_swiglu_fwd(const nf4b200_weight* gate_w, const nf4b200_weight* up_w,
+                               const void* x, int64_t m, int64_t ldx, void* gate_out, void* up_out,
+                               void* hidden, void* workspace, size_t workspace_bytes, void* stream);
+int64_t nf4b200_gate_up_swiglu_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int keep);
+int nf4b200_swiglu_fwd(const void* gate, const void* up, void* hidden, int64_t n, void* stream);
+int nf4b200_swiglu_bwd(const void* d_hidden, const void* gate, const void* up, void* d_gate,
+                       void* d_up, int64_t n, void* stream);
+
+/*
  * Rank-16 projection used by both passes of the LoRA update (peft's lora_A / lora_B linears;
  * third-party in the reference, configured at README.md:91 and task/task.yaml:18-21):
  *   out[m, 16] = scaling * in[m, c] . P        (fp16 in, fp32 accumulate, fp16 out)

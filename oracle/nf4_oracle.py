@@ -116,6 +116,24 @@ def lora_bwd(grad_y, x, weight, lora_a, lora_b, scaling):
     return dx.to(grad_y.dtype), da, db
 
 
+def swiglu_fwd(gate, up):
+    """hidden = silu(gate) * up as the reference's `silu_mul_kernel` forms it, mode 0
+    (solution/kernels.py:43-47): fp16 values widened to fp32, `gate * sigmoid(gate) * up`, one
+    rounding to the output type."""
+    g, u = gate.detach().float(), up.detach().float()
+    return (g * torch.sigmoid(g) * u).to(gate.dtype)
+
+
+def swiglu_bwd(d_hidden, gate, up):
+    """(d_gate, d_up), mode 1 of the same kernel (solution/kernels.py:48-57):
+    d_up = dout * gate * sig; d_gate = (dout * up) * sig * (1 + gate * (1 - sig))."""
+    d, g, u = d_hidden.detach().float(), gate.detach().float(), up.detach().float()
+    sig = torch.sigmoid(g)
+    d_up = d * g * sig
+    d_gate = (d * u) * sig * (1.0 + g * (1.0 - sig))
+    return d_gate.to(gate.dtype), d_up.to(up.dtype)
+
+
 def max_rel_err(got, want):
     """max |got - want| / max |want| : the error measure of the fp16 tolerance (<= 1e-2)."""
     got, want = got.detach().float(), want.detach().float()

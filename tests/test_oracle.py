@@ -118,3 +118,21 @@ def test_threaded_variant_equals_numpy(nested):
         kw = dict(code2=state.state2.code, absmax2=state.state2.absmax, offset=state.offset)
     got = nf4_oracle.dequant_torch(packed, state.absmax, state.code, (96, 320), **kw)
     assert torch.equal(got.view(torch.int16), oracle_weight(packed, state).view(torch.int16))
+
+
+@pytest.mark.parametrize("name", ["ragged", "blocks"])
+def test_swiglu_matches_reference_kernel(name):
+    """The oracle's SwiGLU against the outputs of the reference's silu_mul_kernel (both modes,
+    made under the Triton interpreter: tests/golden/make_golden_swiglu.py). Same fp32 formula,
+    but libm's and the interpreter's exp may differ in the last bit, so: at most one fp16 step,
+    and hardly anywhere."""
+    z = np.load(GOLDEN / "swiglu_small.npz")
+    gate, up, dout = (torch.from_numpy(z[f"{name}_{k}"]) for k in ("gate", "up", "dout"))
+    got = {"hidden": nf4_oracle.swiglu_fwd(gate, up)}
+    got["dgate"], got["dup"] = nf4_oracle.swiglu_bwd(dout, gate, up)
+    for key, val in got.items():
+        want = torch.from_numpy(z[f"{name}_{key}"])
+        steps = (val.view(torch.int16).int() - want.view(torch.int16).int()).abs()
+        same_sign = (val.view(torch.int16) ^ want.view(torch.int16)) >= 0
+        assert bool(((steps <= 1) | ~same_sign & (val.abs() + want.abs() < 1e-6)).all()), key
+        assert float((steps > 0).float().mean()) < 1e-3, key
