@@ -547,6 +547,38 @@ def run_single(args):
         acts["dy_gate"], layers[i % N_LAYERS]["gate"]["packed"], layers[i % N_LAYERS]["gate"]["state"]))
     kern["down_bwd"] = time_kernel(lambda i: linear_backward_dx(
         acts["dy_down"], layers[i % N_LAYERS]["down"]["packed"], layers[i % N_LAYERS]["down"]["state"]))
+    # ---- the step after gate / up: SwiGLU formed in the GEMM's epilogue against the two-step
+    # form (grouped GEMM, then the elementwise kernel), and the elementwise backward against the
+    # HBM roofline (5 arrays of m x 8960 fp16 per launch)
+    from hackaton_b200.group import linear_forward_group
+    from hackaton_b200.mlp import gate_up_swiglu_forward, swiglu_backward, swiglu_forward
+
+    def gu(i):
+        lay = layers[i % N_LAYERS]
+        return [(lay["gate"]["packed"], lay["gate"]["state"]), (lay["up"]["packed"], lay["up"]["state"])]
+
+    def two_step(i):
+        g_out, u_out = linear_forward_group(x_mlp, gu(i))
+        return swiglu_forward(g_out, u_out)
+
+    sw = {
+        "gate_up_then_swiglu_us": time_kernel(two_step) * 1e3,
+        "fused_keep_gate_up_us": time_kernel(lambda i: gate_up_swiglu_forward(x_mlp, *gu(i), True)) * 1e3,
+        "fused_hidden_only_us": time_kernel(lambda i: gate_up_swiglu_forward(x_mlp, *gu(i), False)) * 1e3,
+        "gate_up_group_alone_us": time_kernel(lambda i: linear_forward_group(x_mlp, gu(i))) * 1e3,
+    }
+    d_hidden = acts["dy_gate"]
+    sw_acts = [(torch.randn_like(d_hidden), torch.randn_like(d_hidden)) for _ in range(4)]  # 147 MB > L2
+    sw["backward_us"] = time_kernel(lambda i: swiglu_backward(d_hidden, *sw_acts[i % 4])) * 1e3
+    sw_bytes = 5.0 * d_hidden.numel() * 2
+    sw["backward_gbs"] = sw_bytes / (sw["backward_us"] * 1e-6) / 1e9
+    sw["backward_frac_of_hbm"] = sw["backward_gbs"] / pk["hbm_gbs"]
+    sw["hbm_peak_gbs"] = pk["hbm_gbs"]
+    sw["flops_gate_up"] = 2 * 2.0 * m * 8960 * 1536
+    sw["fused_keep_tflops"] = sw["flops_gate_up"] / (sw["fused_keep_gate_up_us"] * 1e-6) / 1e12
+    sw["fused_hidden_only_tflops"] = sw["flops_gate_up"] / (sw["fused_hidden_only_us"] * 1e-6) / 1e12
+    del sw_acts
+
     gemm_flops = 2.0 * m * 8960 * 1536
     achieved = gemm_flops / (kern["gate_fwd"] * 1e-3) / 1e12
     # The kernel is timed alone in bursts of a few milliseconds, at full clocks: the denominator is
@@ -644,7 +676,7 @@ def run_single(args):
         "frac_of_tensor_peak": value / pk["tflops_burst"],
         "frac_of_sustained_tensor_peak": value / pk["tflops_sustained"],
         "ms_per_28_layer_step": total_ms / args.steps * N_LAYERS,
-        "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs,
+        "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs, "swiglu": sw,
         "step_ms_min_med_max": [min(per_step), statistics.median(per_step), max(per_step)],
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,

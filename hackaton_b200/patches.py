@@ -202,6 +202,55 @@ def patch_sibling_projections(model):
     return groups
 
 
+def mlp_forward_for(original):
+    """Builds the replacement for `Qwen2MLP.forward` (the reference's `patch_qwen2_mlp`,
+    solution/patches.py:20-43): the input is cast to fp16 once, gate_proj, up_proj and the SwiGLU
+    product run as one fused kernel (`nf4_gate_up_swiglu`), down_proj takes the fp16 product, and
+    the result goes back to the stream's dtype. Same conditions as the reference (silu
+    activation, CUDA input, three plain 4-bit linears) plus this library's own (`_eligible`);
+    everything else runs the original forward."""
+    from .group import Projection
+    from . import mlp as _mlp
+
+    def forward(self, x):
+        gate_proj, up_proj, down_proj = self.gate_proj, self.up_proj, self.down_proj
+        act = getattr(getattr(self, "config", None), "hidden_act", "silu")
+        if (act != "silu" or not isinstance(x, torch.Tensor) or not x.is_cuda
+                or not all(_is_4bit_linear(m) for m in (gate_proj, up_proj, down_proj))):
+            return original(self, x)
+        compute = getattr(gate_proj, "compute_dtype", None) or torch.float16
+        if compute != torch.float16:
+            return original(self, x)
+        x16 = x.to(compute)
+        states = [getattr(m.weight, "quant_state", None) for m in (gate_proj, up_proj)]
+        if not all(_eligible(x16, st, m.weight, None) and getattr(m, "bias", None) is None
+                   for m, st in zip((gate_proj, up_proj), states)) \
+                or tuple(states[0].shape) != tuple(states[1].shape):
+            return original(self, x)
+        hidden = _mlp.nf4_gate_up_swiglu(x16, Projection(gate_proj.weight, states[0]),
+                                         Projection(up_proj.weight, states[1]))
+        return down_proj(hidden).to(x.dtype)
+
+    forward._nf4b200 = True
+    forward._original = original
+    return forward
+
+
+def patch_qwen2_mlp():
+    """Installs `mlp_forward_for` on transformers' Qwen2MLP. Not part of `apply()`: the reference
+    installs its MLP patch from `solution.apply()` together with a dozen others; here it is an
+    explicit opt-in next to the two patches of the GEMM path."""
+    try:
+        from transformers.models.qwen2 import modeling_qwen2
+    except ImportError:
+        return False
+    current = modeling_qwen2.Qwen2MLP.forward
+    if getattr(current, "_nf4b200", False):
+        return True
+    modeling_qwen2.Qwen2MLP.forward = mlp_forward_for(current)
+    return True
+
+
 def apply():
     """The entry point the reference's harness calls once before the model is built
     (solution/__init__.py:23-33), restricted to the NF4 path."""

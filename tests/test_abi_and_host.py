@@ -181,3 +181,59 @@ def test_patch_sibling_projections_finds_blocks(monkeypatch):
     assert patches.patch_sibling_projections(model) == []      # nothing left to group
     for g in groups:
         g.remove()
+
+
+def test_mlp_patch_routes_and_falls_through(monkeypatch):
+    """The Qwen2MLP replacement: eligible 4-bit gate/up go through the fused front half and
+    down_proj sees its fp16 result; another activation, or an ineligible input, runs the
+    original forward (solution/patches.py:32-41 has the same shape)."""
+    import types
+
+    from hackaton_b200 import mlp, patches
+
+    class Lin(torch.nn.Module):
+        def __init__(self, tag):
+            super().__init__()
+            self.tag = tag
+            self.weight = types.SimpleNamespace(quant_state=types.SimpleNamespace(shape=(8, 4)))
+            self.bias = None
+            self.compute_dtype = torch.float16
+
+        def forward(self, x):
+            return ("down", x)
+
+    class Mlp:
+        def __init__(self, act="silu"):
+            self.gate_proj, self.up_proj, self.down_proj = Lin("g"), Lin("u"), Lin("d")
+            self.config = types.SimpleNamespace(hidden_act=act)
+
+    class FakeCuda(torch.Tensor):
+        is_cuda = True
+
+    calls = []
+
+    def fake_front(x16, gate, up):
+        calls.append((x16.dtype, gate.packed, up.packed))
+        return torch.ones(2, 8, dtype=torch.float16)
+
+    class Out:
+        def __init__(self, v):
+            self.v = v
+
+        def to(self, dtype):
+            return ("cast", dtype, self.v)
+
+    monkeypatch.setattr(patches, "_is_4bit_linear", lambda m: isinstance(m, Lin))
+    monkeypatch.setattr(patches, "_eligible", lambda x, state, weight, bias: True)
+    monkeypatch.setattr(mlp, "nf4_gate_up_swiglu", fake_front)
+    monkeypatch.setattr(Lin, "forward", lambda self, x: Out(("down", tuple(x.shape), x.dtype)))
+    forward = patches.mlp_forward_for(lambda self, x: "original")
+    x = torch.zeros(2, 4, dtype=torch.float32).as_subclass(FakeCuda)
+    block = Mlp()
+    assert forward(block, x) == ("cast", torch.float32, ("down", (2, 8), torch.float16))
+    assert calls == [(torch.float16, block.gate_proj.weight, block.up_proj.weight)]
+    assert forward(Mlp("gelu"), x) == "original"
+    assert forward(block, torch.zeros(2, 4)) == "original"            # not on a GPU
+    monkeypatch.setattr(patches, "_eligible", lambda x, state, weight, bias: False)
+    assert forward(block, x) == "original"
+    assert len(calls) == 1
