@@ -570,6 +570,16 @@ def run_single(args):
     d_hidden = acts["dy_gate"]
     sw_acts = [(torch.randn_like(d_hidden), torch.randn_like(d_hidden)) for _ in range(4)]  # 147 MB > L2
     sw["backward_us"] = time_kernel(lambda i: swiglu_backward(d_hidden, *sw_acts[i % 4])) * 1e3
+    from hackaton_b200.mlp import linear_backward_dx_swiglu
+
+    def down_w(i):
+        lay = layers[i % N_LAYERS]["down"]
+        return lay["packed"], lay["state"]
+
+    sw["down_bwd_then_swiglu_bwd_us"] = time_kernel(lambda i: swiglu_backward(
+        linear_backward_dx(acts["dy_down"], *down_w(i)), *sw_acts[i % 4])) * 1e3
+    sw["down_bwd_fused_us"] = time_kernel(lambda i: linear_backward_dx_swiglu(
+        acts["dy_down"], down_w(i), *sw_acts[i % 4])) * 1e3
     sw_bytes = 5.0 * d_hidden.numel() * 2
     sw["backward_gbs"] = sw_bytes / (sw["backward_us"] * 1e-6) / 1e9
     sw["backward_frac_of_hbm"] = sw["backward_gbs"] / pk["hbm_gbs"]

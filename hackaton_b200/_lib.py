@@ -20,7 +20,8 @@ EXPORTS = (
     "nf4b200_linear_bwd_dx_group", "nf4b200_workspace_bytes_group", "nf4b200_scales16_bytes",
     "nf4b200_prepare_scales", "nf4b200_lora_down_batch", "nf4b200_lora_grad_batch",
     "nf4b200_set_sm_limit", "nf4b200_gate_up_swiglu_fwd", "nf4b200_gate_up_swiglu_workspace_bytes",
-    "nf4b200_swiglu_fwd", "nf4b200_swiglu_bwd",
+    "nf4b200_swiglu_fwd", "nf4b200_swiglu_bwd", "nf4b200_linear_bwd_dx_swiglu",
+    "nf4b200_linear_bwd_dx_swiglu_workspace_bytes",
 )
 
 F16, BF16, F32 = 0, 1, 2
@@ -101,13 +102,19 @@ def lib() -> ctypes.CDLL:
                                                   c_size_t, c_void_p]
     handle.nf4b200_gate_up_swiglu_workspace_bytes.argtypes = [c_int64, c_int64, c_int64, c_int]
     handle.nf4b200_gate_up_swiglu_workspace_bytes.restype = c_int64
+    handle.nf4b200_linear_bwd_dx_swiglu.argtypes = [POINTER(Weight), c_void_p, c_int64, c_int64, c_void_p,
+                                                    c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                                    c_void_p]
+    handle.nf4b200_linear_bwd_dx_swiglu_workspace_bytes.argtypes = [c_int64, c_int64, c_int64]
+    handle.nf4b200_linear_bwd_dx_swiglu_workspace_bytes.restype = c_int64
     handle.nf4b200_swiglu_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
     handle.nf4b200_swiglu_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                           c_void_p]
     for name in EXPORTS:
         if name not in ("nf4b200_last_error", "nf4b200_workspace_bytes",
                         "nf4b200_workspace_bytes_group", "nf4b200_scales16_bytes",
-                        "nf4b200_gate_up_swiglu_workspace_bytes"):
+                        "nf4b200_gate_up_swiglu_workspace_bytes",
+                        "nf4b200_linear_bwd_dx_swiglu_workspace_bytes"):
             getattr(handle, name).restype = c_int
     handle.nf4b200_workspace_bytes.restype = c_int64
     _lib = handle

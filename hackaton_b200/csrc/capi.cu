@@ -523,6 +523,70 @@ int nf4b200_gate_up_swiglu_fwd(const nf4b200_weight* gate_w, const nf4b200_weigh
     return NF4B200_OK;
 }
 
+int64_t nf4b200_linear_bwd_dx_swiglu_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (n_rows <= 0 || n_cols <= 0 || m <= 0)
+        return fail(NF4B200_EINVAL, "linear_bwd_dx_swiglu_workspace_bytes: bad shape");
+    const nf4::GemmPlan pl = nf4::plan_gemm(m, n_rows, n_cols, true, gemm_sms(d));
+    if (pl.cg == 2 && pl.nacc == 2 && pl.splits == 1 && n_cols % 8 == 0) return 0;
+    return (int64_t)((pl.ws_bytes + 255) / 256 * 256 + swiglu_tmp_bytes(m, n_cols));
+}
+
+int nf4b200_linear_bwd_dx_swiglu(const nf4b200_weight* w, const void* dy, int64_t m, int64_t lddy,
+                                 const void* gate, const void* up, void* d_gate, void* d_up,
+                                 void* workspace, size_t workspace_bytes, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if ((rc = check_weight(w, true)) != NF4B200_OK) return rc;
+    if ((rc = check_act("dy", dy, m, lddy, w->n_rows)) != NF4B200_OK) return rc;
+    if (!gate || !up || !d_gate || !d_up)
+        return fail(NF4B200_EINVAL, "linear_bwd_dx_swiglu: NULL argument");
+    if (!aligned16(gate) || !aligned16(up) || !aligned16(d_gate) || !aligned16(d_up))
+        return fail(NF4B200_EINVAL, "linear_bwd_dx_swiglu: gate / up / d_gate / d_up must be 16-byte aligned");
+    const int64_t k = w->n_cols;
+    if (k % 8 != 0)
+        return fail(NF4B200_EINVAL, "linear_bwd_dx_swiglu: %lld columns (multiple of 8 needed)", (long long)k);
+    nf4::GemmArgs g;
+    fill_gemm(g, w, gemm_sms(d));
+    g.act = static_cast<const __half*>(dy); g.m = m; g.ld_act = lddy;
+    g.out = nullptr; g.ld_out = k;
+    g.bias = nullptr; g.ext_a = nullptr; g.ext_b = nullptr;
+    g.trans_w = true;
+    if ((rc = set_workspace(g, workspace, workspace_bytes)) != NF4B200_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const char* why = "";
+    if (nf4::swiglu_bwd_fused_eligible(g)) {
+        nf4::SwigluArgs epi = {};
+        epi.gate = static_cast<const __half*>(gate); epi.up = static_cast<const __half*>(up);
+        epi.d_gate = static_cast<__half*>(d_gate); epi.d_up = static_cast<__half*>(d_up);
+        epi.ld = k;
+        cudaError_t e = nf4::launch_bwd_dx_swiglu(g, epi, st, &why);
+        if (e != cudaSuccess)
+            return fail(NF4B200_ECUDA, "linear_bwd_dx_swiglu: %s: %s", why, cudaGetErrorString(e));
+        return NF4B200_OK;
+    }
+    // other plans (few rows, K-slices): d_hidden into the end of the scratch, then the
+    // elementwise kernel
+    const size_t tmp = swiglu_tmp_bytes(m, k);
+    if (!workspace || workspace_bytes < tmp)
+        return fail(NF4B200_EINVAL, "linear_bwd_dx_swiglu: workspace too small "
+                                    "(nf4b200_linear_bwd_dx_swiglu_workspace_bytes)");
+    uint8_t* base = static_cast<uint8_t*>(workspace) + (workspace_bytes - tmp) / 256 * 256;
+    g.out = reinterpret_cast<__half*>(base);
+    g.workspace_bytes = (size_t)(base - static_cast<uint8_t*>(workspace));
+    cudaError_t e = nf4::launch_gemm(g, st, &why);
+    if (e != cudaSuccess)
+        return fail(NF4B200_ECUDA, "linear_bwd_dx_swiglu: %s: %s", why, cudaGetErrorString(e));
+    e = nf4::launch_swiglu_bwd(g.out, static_cast<const __half*>(gate), static_cast<const __half*>(up),
+                               static_cast<__half*>(d_gate), static_cast<__half*>(d_up), m * k,
+                               gemm_sms(d), st);
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "swiglu_bwd: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
 int nf4b200_swiglu_fwd(const void* gate, const void* up, void* hidden, int64_t n, void* stream) {
     DeviceInfo* d = nullptr;
     int rc = require_sm100(&d);

@@ -64,6 +64,7 @@
 #include "decode.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
+#include "swiglu.cuh"
 
 namespace nf4 {
 
@@ -112,6 +113,14 @@ struct GemmParams {
     int prepared;            // every problem comes with a ready-made fp16 block-scale table
     __half* hidden;          // SwiGLU epilogue only: silu(gate) * up, [m, n_w] with pitch ld_hidden
     long long ld_hidden;
+    // SwiGLU-backward epilogue only (EPI = 2): the tile this GEMM produces is d_hidden; the
+    // epilogue reads gate and up at the same coordinates and writes d_gate and d_up instead.
+    // All four are [m, k_w] with pitch ld_sw.
+    const __half* sw_gate;
+    const __half* sw_up;
+    __half* sw_dgate;
+    __half* sw_dup;
+    long long ld_sw;
     int debug;               // NF4B200_DEBUG; the kernel looks at it only in -DNF4B200_TRACE builds
 };
 
@@ -321,7 +330,8 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
     static_assert(WORDS == 2 || WORDS == 4, "producer work split");
     constexpr uint32_t TMEM_COLS = NACC * BN;
     static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "TMEM columns");
-    static_assert(EPI == 0 || (CG == 2 && NACC == 2 && !TRANS_W), "SwiGLU epilogue: pair kernel, forward");
+    static_assert(EPI != 1 || (CG == 2 && NACC == 2 && !TRANS_W), "SwiGLU epilogue: pair kernel, forward");
+    static_assert(EPI != 2 || (CG == 2 && NACC == 2 && TRANS_W), "SwiGLU-backward epilogue: pair kernel, backward");
     constexpr int ROWS_PER_TILE = 128 * CG * NACC;  // token rows of a unit (whole pair)
     constexpr uint32_t ARRIVALS = CG * PRODUCER_WARPS;  // "TMEM drained" arrivals (all warps)
     // "operands ready" arrivals: the decoding warps of both CTAs, plus one from the peer CTA that
@@ -1005,6 +1015,42 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                         __syncwarp();
                         const long long grow0 =
                             (long long)w.m0 + acc * (128 * CG) + (int)rank * 128 + q * 32;
+                        if constexpr (EPI == 2) {
+                            // the staged values are d_hidden (already rounded to fp16, as a
+                            // separate dX launch would have stored them); gate and up of four rows
+                            // are requested before the first of them is used. k_w % 8 == 0.
+                            const int colg = w.n0 + ch0 * 32 + rd_chunk * 8;
+#pragma unroll 1
+                            for (int i0 = 0; i0 < 8; i0 += 4) {
+                                uint4 gv[4], uv[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const long long grow = grow0 + (i0 + i) * 4 + rd_row;
+                                    gv[i] = uv[i] = make_uint4(0u, 0u, 0u, 0u);
+                                    if (grow < p.m && colg < n_out) {
+                                        const long long off = grow * p.ld_sw + colg;
+                                        gv[i] = __ldcg(reinterpret_cast<const uint4*>(p.sw_gate + off));
+                                        uv[i] = __ldcg(reinterpret_cast<const uint4*>(p.sw_up + off));
+                                    }
+                                }
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int rr = (i0 + i) * 4 + rd_row;
+                                    const long long grow = grow0 + rr;
+                                    if (grow < p.m && colg < n_out) {
+                                        const uint4 v = lds128(staging + rr * 128 + ((rd_chunk ^ (rr & 7)) << 4));
+                                        const long long off = grow * p.ld_sw + colg;
+                                        uint4 dg, du;
+                                        swiglu_bwd2(v.x, gv[i].x, uv[i].x, dg.x, du.x);
+                                        swiglu_bwd2(v.y, gv[i].y, uv[i].y, dg.y, du.y);
+                                        swiglu_bwd2(v.z, gv[i].z, uv[i].z, dg.z, du.z);
+                                        swiglu_bwd2(v.w, gv[i].w, uv[i].w, dg.w, du.w);
+                                        *reinterpret_cast<uint4*>(p.sw_dgate + off) = dg;
+                                        *reinterpret_cast<uint4*>(p.sw_dup + off) = du;
+                                    }
+                                }
+                            }
+                        } else {
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int rr = i * 4 + rd_row;
@@ -1022,6 +1068,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                                         if (colg + e < n_out) dst[e] = hv[e];
                                 }
                             }
+                        }
                         }
                         __syncwarp();
                     }
@@ -1276,7 +1323,7 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
 
 template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP = false, int EPI = 0>
 static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaStream_t stream,
-                              const char** why, __half* hidden = nullptr, long long ld_hidden = 0) {
+                              const char** why, const SwigluArgs* epi = nullptr) {
     using L = SmemLayout<CG, NACC, STAGES, TABLES>;
     auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW, TABLES, PREP, EPI>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1344,8 +1391,13 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
         maps.codes[i] = maps.codes[0];
     }
     p.prepared = prepared ? 1 : 0;
-    p.hidden = hidden;
-    p.ld_hidden = ld_hidden;
+    p.hidden = nullptr; p.ld_hidden = 0;
+    p.sw_gate = p.sw_up = nullptr; p.sw_dgate = p.sw_dup = nullptr; p.ld_sw = 0;
+    if (epi != nullptr) {
+        p.hidden = epi->hidden; p.ld_hidden = epi->ld;
+        p.sw_gate = epi->gate; p.sw_up = epi->up; p.sw_dgate = epi->d_gate; p.sw_dup = epi->d_up;
+        p.ld_sw = epi->ld;
+    }
     if (!TRANS_W)
         for (int i = 1; i < MAXP; ++i) maps.act[i] = maps.act[0];
     else
@@ -1447,9 +1499,35 @@ cudaError_t launch_gate_up_swiglu(const GemmGroupArgs& ga, __half* hidden, long 
     pl.nkb = (int)((a.k_w + BK - 1) / BK);
     pl.splits = 1;
     pl.kb_per_split = pl.nkb;
+    SwigluArgs epi = {};
+    epi.hidden = hidden;
+    epi.ld = ld_hidden;
     if (a.scales16 != nullptr && ga.item[1].scales16 != nullptr)
-        return launch_cfg<2, 2, false, 4, 8, MAXP, true, 1>(ga, pl, stream, why, hidden, ld_hidden);
-    return launch_cfg<2, 2, false, 4, 8, MAXP, false, 1>(ga, pl, stream, why, hidden, ld_hidden);
+        return launch_cfg<2, 2, false, 4, 8, MAXP, true, 1>(ga, pl, stream, why, &epi);
+    return launch_cfg<2, 2, false, 4, 8, MAXP, false, 1>(ga, pl, stream, why, &epi);
+}
+
+// dX GEMM of the projection that consumes the SwiGLU product (down_proj), with the SwiGLU
+// backward applied to each tile while it is drained: d_gate and d_up are written instead of
+// d_hidden. Eligible when the plan is the pair kernel with 512-row tiles and no K-slices.
+bool swiglu_bwd_fused_eligible(const GemmArgs& a) {
+    if (!a.trans_w || a.ext_a != nullptr || a.k_w % 8 != 0 || (debug_flags() & 16)) return false;
+    const GemmPlan pl = plan_gemm(a.m, a.n_w, a.k_w, true, a.sm_count);
+    return pl.cg == 2 && pl.nacc == 2 && pl.splits == 1;
+}
+
+cudaError_t launch_bwd_dx_swiglu(const GemmArgs& a, const SwigluArgs& epi, cudaStream_t stream,
+                                 const char** why) {
+    *why = "";
+    if (!swiglu_bwd_fused_eligible(a)) { *why = "SwiGLU-backward epilogue: call not eligible"; return cudaErrorInvalidValue; }
+    GemmGroupArgs ga;
+    ga.count = 1;
+    ga.item[0] = a;
+    ga.item[0].out = nullptr;
+    const GemmPlan pl = plan_gemm(a.m, a.n_w, a.k_w, true, a.sm_count);
+    if (a.scales16 != nullptr)
+        return launch_cfg<2, 2, true, 4, 8, MAXP, true, 2>(ga, pl, stream, why, &epi);
+    return launch_cfg<2, 2, true, 4, 8, MAXP, false, 2>(ga, pl, stream, why, &epi);
 }
 
 cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, const char** why) {

@@ -116,7 +116,20 @@ cudaError_t launch_gemm_group(const GemmGroupArgs& a, cudaStream_t stream, const
 // gate / up pair with hidden = silu(gate) * up formed in the GEMM epilogue (item[0] = gate,
 // item[1] = up; their `out` may both be null when only `hidden` is wanted). The caller checks
 // swiglu_fused_eligible first and otherwise runs launch_gemm_group + launch_swiglu_fwd.
+struct SwigluArgs {
+    __half* hidden;        // forward epilogue: the product
+    const __half* gate;    // backward epilogue: saved gate / up, outputs d_gate / d_up
+    const __half* up;
+    __half* d_gate;
+    __half* d_up;
+    long long ld;          // row pitch of all of them
+};
 bool swiglu_fused_eligible(const GemmGroupArgs& ga);
+// dX GEMM (a.trans_w) whose result is d_hidden of a SwiGLU: writes d_gate / d_up instead, from
+// the saved gate / up (epi.gate, epi.up, epi.d_gate, epi.d_up: [m, k_w], pitch epi.ld).
+bool swiglu_bwd_fused_eligible(const GemmArgs& a);
+cudaError_t launch_bwd_dx_swiglu(const GemmArgs& a, const SwigluArgs& epi, cudaStream_t stream,
+                                 const char** why);
 cudaError_t launch_gate_up_swiglu(const GemmGroupArgs& ga, __half* hidden, long long ld_hidden,
                                   cudaStream_t stream, const char** why);
 // Elementwise SwiGLU on contiguous fp16 arrays (swiglu.cu): hidden = silu(gate) * up, and its

@@ -134,6 +134,11 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, i
                  : "memory");
 }
 
+// Asks for `bytes` (multiple of 16) at a 16-byte aligned global address to be brought into L2.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gptr, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gptr), "r"(bytes) : "memory");
+}
+
 // ---------------------------------------------------------------------------------- tcgen05
 // Allocates `ncols` (power of two, 32..512) TMEM columns; the base address lands in shared
 // memory at `dst`. Warp-collective.

@@ -145,6 +145,87 @@ class NF4GateUpSwiGLU(torch.autograd.Function):
         return dx, None, None
 
 
+def linear_backward_dx_swiglu(grad_out, down_w, gate, up):
+    """(d_gate, d_up) from the gradient of down_proj's output: d_hidden = grad_out . W_down never
+    reaches memory when the plan allows it (see nf4b200_linear_bwd_dx_swiglu). down_w: (packed,
+    state); gate, up: what the forward kept, [..., K_down] fp16."""
+    ref = _refs([down_w])[0]
+    _check_pair(gate, up)
+    if grad_out.dtype != torch.float16:
+        raise TypeError(f"hackaton_b200: the fused NF4 linear computes in fp16, got {grad_out.dtype}")
+    g2 = _rows_view(grad_out, ref.rows)
+    m = g2.shape[0]
+    gate, up = gate.contiguous(), up.contiguous()
+    if gate.numel() != m * ref.cols:
+        raise ValueError("hackaton_b200: gate / up do not match the gradient's rows and the weight's columns")
+    d_gate, d_up = torch.empty_like(gate), torch.empty_like(up)
+    if m == 0:
+        return d_gate, d_up
+    device = g2.device
+    key = (device.index, "bwd", ref.rows, ref.cols, m)
+    need = _ws_need.get(key)
+    if need is None:
+        with torch.cuda.device(device):
+            need = int(_lib.lib().nf4b200_linear_bwd_dx_swiglu_workspace_bytes(ref.rows, ref.cols, m))
+        if need < 0:
+            _lib.check(need)
+        _ws_need[key] = need
+    ws, ws_bytes = None, 0
+    if need:
+        skey = (device.index, torch.cuda.current_stream(device).cuda_stream)
+        buf = _ws_buffers.get(skey)
+        if buf is None or buf.numel() < need:
+            buf = torch.empty(max(need, 1 << 22), dtype=torch.uint8, device=device)
+            _ws_buffers[skey] = buf
+        ws, ws_bytes = buf.data_ptr(), need
+    with torch.cuda.device(device):
+        _lib.check(_lib.lib().nf4b200_linear_bwd_dx_swiglu(
+            ctypes.byref(ref.struct), g2.data_ptr(), m, g2.stride(0), gate.data_ptr(), up.data_ptr(),
+            d_gate.data_ptr(), d_up.data_ptr(), ws, ws_bytes, _stream_ptr(device)))
+    return d_gate, d_up
+
+
+class NF4SwiGLUMLP(torch.autograd.Function):
+    """y = (silu(x . Wgᵀ) * (x . Wuᵀ)) . Wdᵀ on three frozen NF4 weights: two kernels forward
+    (gate/up/product, down), two backward (down's dX with the SwiGLU backward in its epilogue,
+    then the grouped dX of gate and up). Keeps gate and up for the backward, not the product."""
+
+    @staticmethod
+    def forward(ctx, x, gate_w, up_w, down_w):
+        from .nf4 import linear_forward
+        keep = ctx.needs_input_grad[0]
+        hidden, gate, up = gate_up_swiglu_forward(x, gate_w, up_w, keep)
+        y = linear_forward(hidden, down_w[0], None, down_w[1])
+        if keep:
+            ctx.save_for_backward(gate, up)
+            ctx.weights = (gate_w, up_w, down_w)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        gate, up = ctx.saved_tensors
+        gate_w, up_w, down_w = ctx.weights
+        d_gate, d_up = linear_backward_dx_swiglu(grad_out.contiguous(), down_w, gate, up)
+        dx = linear_backward_dx_group([d_gate, d_up], [gate_w, up_w])
+        return dx, None, None, None
+
+
+def nf4_swiglu_mlp(x, gate_proj: Projection, up_proj: Projection, down_proj: Projection):
+    """The whole SwiGLU MLP of a Qwen2 block (solution/patches.py:32-41) on NF4 weights without
+    bias or LoRA pairs; other configurations go through `nf4_gate_up_swiglu` and the ordinary
+    linear."""
+    projs = (gate_proj, up_proj, down_proj)
+    if all(p.bias is None and p.lora_a is None and p.lora_b is None for p in projs):
+        return NF4SwiGLUMLP.apply(x, *[(p.packed, p.state) for p in projs])
+    from .lora import nf4_lora_linear
+    from .nf4 import nf4_linear
+    hidden = nf4_gate_up_swiglu(x, gate_proj, up_proj)
+    d = down_proj
+    if d.lora_a is not None:
+        return nf4_lora_linear(hidden, d.packed, d.bias, d.state, d.lora_a, d.lora_b, d.scaling)
+    return nf4_linear(hidden, d.packed, d.bias, d.state)
+
+
 def nf4_gate_up_swiglu(x, gate_proj: Projection, up_proj: Projection):
     """The front half of a SwiGLU MLP on NF4 weights. Projections with a bias or a LoRA pair are
     not covered by the fused kernel: they take the grouped launch followed by `silu_mul`."""

@@ -205,8 +205,10 @@ def patch_sibling_projections(model):
 def mlp_forward_for(original):
     """Builds the replacement for `Qwen2MLP.forward` (the reference's `patch_qwen2_mlp`,
     solution/patches.py:20-43): the input is cast to fp16 once, gate_proj, up_proj and the SwiGLU
-    product run as one fused kernel (`nf4_gate_up_swiglu`), down_proj takes the fp16 product, and
-    the result goes back to the stream's dtype. Same conditions as the reference (silu
+    product run as one fused kernel and down_proj takes the fp16 product (`nf4_swiglu_mlp`, whose
+    backward also folds the SwiGLU backward into down_proj's dX kernel; `nf4_gate_up_swiglu` +
+    the module's own forward when down_proj is not eligible), and the result goes back to the
+    stream's dtype. Same conditions as the reference (silu
     activation, CUDA input, three plain 4-bit linears) plus this library's own (`_eligible`);
     everything else runs the original forward."""
     from .group import Projection
@@ -227,8 +229,16 @@ def mlp_forward_for(original):
                    for m, st in zip((gate_proj, up_proj), states)) \
                 or tuple(states[0].shape) != tuple(states[1].shape):
             return original(self, x)
-        hidden = _mlp.nf4_gate_up_swiglu(x16, Projection(gate_proj.weight, states[0]),
-                                         Projection(up_proj.weight, states[1]))
+        gate_p, up_p = Projection(gate_proj.weight, states[0]), Projection(up_proj.weight, states[1])
+        down_state = getattr(down_proj.weight, "quant_state", None)
+        if (getattr(down_proj, "bias", None) is None and down_state is not None
+                and len(getattr(down_state, "shape", ())) == 2
+                and down_state.shape[1] == states[0].shape[0]
+                and _eligible(x16.new_empty((1, down_state.shape[1])), down_state,
+                              down_proj.weight, None)):
+            return _mlp.nf4_swiglu_mlp(x16, gate_p, up_p,
+                                       Projection(down_proj.weight, down_state)).to(x.dtype)
+        hidden = _mlp.nf4_gate_up_swiglu(x16, gate_p, up_p)
         return down_proj(hidden).to(x.dtype)
 
     forward._nf4b200 = True

@@ -196,6 +196,19 @@ int nf4b200_gate_up_swiglu_fwd(const nf4b200_weight* gate_w, const nf4b200_weigh
                                const void* x, int64_t m, int64_t ldx, void* gate_out, void* up_out,
                                void* hidden, void* workspace, size_t workspace_bytes, void* stream);
 int64_t nf4b200_gate_up_swiglu_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m, int keep);
+/*
+ * Backward of the projection that consumes the product (down_proj: d_hidden = dy . W_down) with the
+ * SwiGLU backward applied to every tile as it is drained: d_gate and d_up ([m, n_cols], no
+ * padding) are written instead of d_hidden, from the gate / up arrays the forward kept. One
+ * kernel when the plan has 512-row tiles and no K-slices (the training shapes); otherwise the dX
+ * GEMM writes d_hidden into the scratch and nf4b200_swiglu_bwd follows
+ * (nf4b200_linear_bwd_dx_swiglu_workspace_bytes). The reference runs SiluMul.backward
+ * (solution/kernels.py:78-91) as a separate kernel after NF4Linear.backward (solution/nf4.py:94-102).
+ */
+int nf4b200_linear_bwd_dx_swiglu(const nf4b200_weight* w, const void* dy, int64_t m, int64_t lddy,
+                                 const void* gate, const void* up, void* d_gate, void* d_up,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+int64_t nf4b200_linear_bwd_dx_swiglu_workspace_bytes(int64_t n_rows, int64_t n_cols, int64_t m);
 int nf4b200_swiglu_fwd(const void* gate, const void* up, void* hidden, int64_t n, void* stream);
 int nf4b200_swiglu_bwd(const void* d_hidden, const void* gate, const void* up, void* d_gate,
                        void* d_up, int64_t n, void* stream);

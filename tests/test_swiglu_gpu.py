@@ -120,3 +120,58 @@ def test_mlp_front_half_autograd(cuda_lib, m, k, n):
         again = nf4_gate_up_swiglu(x.cuda(), Projection(*wg), Projection(*wu))
     assert torch.equal(again, hidden.detach())
     cuda_lib.device_status()
+
+
+@pytest.mark.parametrize("m,n_down,k_down", [
+    (2048, 1536, 8960),     # down_proj of Qwen2.5-1.5B: one kernel (512-row tiles, no K-slices)
+    (700, 128, 320),        # ragged, still the pair kernel
+    (2048, 256, 512),       # few tiles: K-slices, so dX + elementwise kernel behind the same call
+    (100, 192, 384),        # few rows
+])
+def test_down_backward_with_swiglu_epilogue(cuda_lib, m, n_down, k_down):
+    from hackaton_b200.mlp import linear_backward_dx_swiglu, swiglu_backward
+    from hackaton_b200.nf4 import linear_backward_dx
+
+    g = torch.Generator().manual_seed(m + k_down)
+    wd = synthetic_weight(n_down, k_down, True, seed=5, device="cuda")
+    dy = torch.randn(m, n_down, generator=g).half()
+    gate = torch.randn(m, k_down, generator=g).half()
+    up = torch.randn(m, k_down, generator=g).half()
+    d_gate, d_up = linear_backward_dx_swiglu(dy.cuda(), wd, gate.cuda(), up.cuda())
+    torch.cuda.synchronize()
+    w = oracle_weight(*wd)
+    d_hidden = (dy.float() @ w.float()).half()
+    rg, ru = nf4_oracle.swiglu_bwd(d_hidden, gate, up)
+    assert nf4_oracle.max_rel_err(d_gate.cpu(), rg) <= TOL
+    assert nf4_oracle.max_rel_err(d_up.cpu(), ru) <= TOL
+    # against the two-step form on the GPU: the same d_hidden bits go into the same arithmetic
+    dh = linear_backward_dx(dy.cuda(), wd[0], wd[1])
+    g2, u2 = swiglu_backward(dh, gate.cuda(), up.cuda())
+    assert nf4_oracle.max_rel_err(d_gate.cpu(), g2.cpu()) <= 2e-3
+    assert nf4_oracle.max_rel_err(d_up.cpu(), u2.cpu()) <= 2e-3
+    cuda_lib.device_status()
+
+
+@pytest.mark.parametrize("m,hidden,inter", [(1024, 1536, 8960), (300, 192, 320), (64, 256, 512)])
+def test_whole_mlp_autograd(cuda_lib, m, hidden, inter):
+    from hackaton_b200 import Projection
+    from hackaton_b200.mlp import nf4_swiglu_mlp
+
+    x, wg, wu = mlp_case(m, hidden, inter, seed=3 * m + inter)
+    wd = synthetic_weight(hidden, inter, True, seed=17, device="cuda")
+    g = torch.Generator().manual_seed(123)
+    dy = torch.randn(m, hidden, generator=g).half()
+    xg = x.cuda().requires_grad_()
+    y = nf4_swiglu_mlp(xg, Projection(*wg), Projection(*wu), Projection(*wd))
+    y.backward(dy.cuda())
+    torch.cuda.synchronize()
+    w_gate, w_up, w_down = oracle_weight(*wg), oracle_weight(*wu), oracle_weight(*wd)
+    gate_ref, up_ref = nf4_oracle.linear_fwd(x, w_gate, None), nf4_oracle.linear_fwd(x, w_up, None)
+    h_ref = nf4_oracle.swiglu_fwd(gate_ref, up_ref)
+    y_ref = nf4_oracle.linear_fwd(h_ref, w_down, None)
+    assert nf4_oracle.max_rel_err(y.detach().cpu(), y_ref) <= TOL
+    d_hidden = (dy.float() @ w_down.float()).half()
+    d_gate, d_up = nf4_oracle.swiglu_bwd(d_hidden, gate_ref, up_ref)
+    dx_ref = d_gate.float() @ w_gate.float() + d_up.float() @ w_up.float()
+    assert nf4_oracle.max_rel_err(xg.grad.cpu(), dx_ref) <= TOL
+    cuda_lib.device_status()
