@@ -21,7 +21,7 @@ EXPORTS = (
     "nf4b200_prepare_scales", "nf4b200_lora_down_batch", "nf4b200_lora_grad_batch",
     "nf4b200_set_sm_limit", "nf4b200_gate_up_swiglu_fwd", "nf4b200_gate_up_swiglu_workspace_bytes",
     "nf4b200_swiglu_fwd", "nf4b200_swiglu_bwd", "nf4b200_linear_bwd_dx_swiglu",
-    "nf4b200_linear_bwd_dx_swiglu_workspace_bytes",
+    "nf4b200_linear_bwd_dx_swiglu_workspace_bytes", "nf4b200_rmsnorm_fwd", "nf4b200_rmsnorm_bwd",
 )
 
 F16, BF16, F32 = 0, 1, 2
@@ -107,6 +107,10 @@ def lib() -> ctypes.CDLL:
                                                     c_void_p]
     handle.nf4b200_linear_bwd_dx_swiglu_workspace_bytes.argtypes = [c_int64, c_int64, c_int64]
     handle.nf4b200_linear_bwd_dx_swiglu_workspace_bytes.restype = c_int64
+    handle.nf4b200_rmsnorm_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                           c_void_p, c_int64, c_int64, c_float, c_void_p]
+    handle.nf4b200_rmsnorm_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                           c_void_p, c_int64, c_int64, c_void_p]
     handle.nf4b200_swiglu_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
     handle.nf4b200_swiglu_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                           c_void_p]

@@ -587,6 +587,54 @@ int nf4b200_linear_bwd_dx_swiglu(const nf4b200_weight* w, const void* dy, int64_
     return NF4B200_OK;
 }
 
+int nf4b200_rmsnorm_fwd(const void* x, const void* delta, const void* weight, void* total, void* y,
+                        int y_dtype, void* rstd, int64_t rows, int64_t hidden, float eps,
+                        void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (rows < 0 || hidden <= 0 || hidden > 0x7FFFFFFF)
+        return fail(NF4B200_EINVAL, "rmsnorm_fwd: bad shape %lld x %lld", (long long)rows, (long long)hidden);
+    if (rows > 0 && (!x || !weight || !y || !rstd))
+        return fail(NF4B200_EINVAL, "rmsnorm_fwd: NULL argument");
+    if ((delta == nullptr) != (total == nullptr))
+        return fail(NF4B200_EINVAL, "rmsnorm_fwd: delta and total must both be given or both be NULL");
+    if (y_dtype != NF4B200_F16 && y_dtype != NF4B200_F32)
+        return fail(NF4B200_EINVAL, "rmsnorm_fwd: y must be fp16 or fp32");
+    nf4::RmsNormArgs a = {};
+    a.x = static_cast<const float*>(x); a.w = static_cast<const float*>(weight);
+    a.y = y; a.rstd = static_cast<float*>(rstd);
+    a.delta = delta; a.total = static_cast<float*>(total);
+    a.rows = rows; a.hidden = (int)hidden; a.mode = delta ? 2 : 0;
+    a.y_half = y_dtype == NF4B200_F16 ? 1 : 0; a.eps = eps;
+    cudaError_t e = nf4::launch_rmsnorm(a, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "rmsnorm_fwd: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_rmsnorm_bwd(const void* x, const void* weight, const void* rstd, const void* dy,
+                        int dy_dtype, const void* d_total, void* dx, int64_t rows, int64_t hidden,
+                        void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (rows < 0 || hidden <= 0 || hidden > 0x7FFFFFFF)
+        return fail(NF4B200_EINVAL, "rmsnorm_bwd: bad shape %lld x %lld", (long long)rows, (long long)hidden);
+    if (rows > 0 && (!x || !weight || !rstd || !dy || !dx))
+        return fail(NF4B200_EINVAL, "rmsnorm_bwd: NULL argument");
+    if (dy_dtype != NF4B200_F16 && dy_dtype != NF4B200_F32)
+        return fail(NF4B200_EINVAL, "rmsnorm_bwd: dy must be fp16 or fp32");
+    nf4::RmsNormArgs a = {};
+    a.x = static_cast<const float*>(x); a.w = static_cast<const float*>(weight);
+    a.rstd = const_cast<float*>(static_cast<const float*>(rstd));
+    a.dy = dy; a.dx = static_cast<float*>(dx); a.d_total = static_cast<const float*>(d_total);
+    a.rows = rows; a.hidden = (int)hidden; a.mode = d_total ? 3 : 1;
+    a.y_half = dy_dtype == NF4B200_F16 ? 1 : 0; a.eps = 0.f;
+    cudaError_t e = nf4::launch_rmsnorm(a, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "rmsnorm_bwd: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
 int nf4b200_swiglu_fwd(const void* gate, const void* up, void* hidden, int64_t n, void* stream) {
     DeviceInfo* d = nullptr;
     int rc = require_sm100(&d);

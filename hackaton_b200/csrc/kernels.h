@@ -140,6 +140,26 @@ cudaError_t launch_swiglu_bwd(const __half* d_hidden, const __half* gate, const 
                               __half* d_gate, __half* d_up, long long n, int sm_count,
                               cudaStream_t stream);
 
+// RMSNorm / add + RMSNorm on the fp32 stream (rmsnorm.cu); mode as in the reference kernel:
+// 0 forward, 1 backward, 2 add then forward, 3 backward plus the sum's own gradient.
+struct RmsNormArgs {
+    const float* x;        // [rows, hidden]: the input (modes 0, 1, 3: the tensor that was normalised)
+    const float* w;        // [hidden]
+    void* y;               // modes 0, 2: output, fp32 or fp16 (y_half)
+    float* rstd;           // [rows]: written by 0 / 2, read by 1 / 3
+    const void* dy;        // modes 1, 3: gradient of y, same type as y
+    float* dx;             // modes 1, 3
+    const void* delta;     // mode 2: fp16 [rows, hidden], added to x
+    float* total;          // mode 2: x + delta
+    const float* d_total;  // mode 3: gradient of the sum, added to dx
+    long long rows;
+    int hidden;
+    int mode;
+    int y_half;
+    float eps;
+};
+cudaError_t launch_rmsnorm(const RmsNormArgs& a, cudaStream_t stream);
+
 // Weight-streaming forward kernel for M <= 64 (gemv.cu); launch_gemm* route eligible calls to it.
 bool gemv_eligible(const GemmArgs& a);
 cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t stream);

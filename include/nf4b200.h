@@ -214,6 +214,27 @@ int nf4b200_swiglu_bwd(const void* d_hidden, const void* gate, const void* up, v
                        void* d_up, int64_t n, void* stream);
 
 /*
+ * RMSNorm on the fp32 residual stream, optionally with the residual add in the same pass: the
+ * reference's rmsnorm_kernel (solution/rmsnorm.py:17-49; modes 0-3) behind `rms_norm`
+ * (solution/rmsnorm.py:99-101) and `add_rms_norm` (:147-150), the producers of the fp16 X that
+ * q/k/v and gate/up read (solution/packed.py:88-115).
+ *   fwd: s = x (+ delta, fp16; then `total` receives s, fp32); rstd[r] = 1/sqrt(mean(s^2) + eps);
+ *        y = weight * (s * rstd), stored as fp32 or fp16 (y_dtype: NF4B200_F32 / NF4B200_F16).
+ *   bwd: x is the tensor that was normalised (the input, or `total`);
+ *        dx = rstd * (g - xhat * mean(g * xhat)) with g = dy * weight, xhat = x * rstd,
+ *        plus d_total (fp32, the gradient that reaches the sum directly) when it is not NULL.
+ * x, weight, total, rstd, dx, d_total are fp32; rows are contiguous ([rows, hidden]). The
+ * gradient of `weight`, which the task never needs (frozen norms), is left to the caller, as in
+ * the reference (solution/rmsnorm.py:93-95).
+ */
+int nf4b200_rmsnorm_fwd(const void* x, const void* delta, const void* weight, void* total, void* y,
+                        int y_dtype, void* rstd, int64_t rows, int64_t hidden, float eps,
+                        void* stream);
+int nf4b200_rmsnorm_bwd(const void* x, const void* weight, const void* rstd, const void* dy,
+                        int dy_dtype, const void* d_total, void* dx, int64_t rows, int64_t hidden,
+                        void* stream);
+
+/*
  * Rank-16 projection used by both passes of the LoRA update (peft's lora_A / lora_B linears;
  * third-party in the reference, configured at README.md:91 and task/task.yaml:18-21):
  *   out[m, 16] = scaling * in[m, c] . P        (fp16 in, fp32 accumulate, fp16 out)

@@ -134,6 +134,30 @@ def swiglu_bwd(d_hidden, gate, up):
     return d_gate.to(gate.dtype), d_up.to(up.dtype)
 
 
+def rmsnorm_fwd(x, weight, eps, delta=None, out_dtype=torch.float32):
+    """Modes 0 and 2 of the reference's rmsnorm_kernel (solution/rmsnorm.py:27-36): s = x (+ delta,
+    widened to fp32), rstd = 1 / sqrt(sum(s^2) / hidden + eps), y = w * (s * rstd) rounded to
+    `out_dtype`. Returns (y, rstd, s)."""
+    s = x.detach().float()
+    if delta is not None:
+        s = s + delta.detach().float()
+    rstd = 1.0 / torch.sqrt((s * s).sum(dim=-1) / s.shape[-1] + eps)
+    y = weight.detach().float() * (s * rstd[..., None])
+    return y.to(out_dtype), rstd, s
+
+
+def rmsnorm_bwd(x, weight, rstd, dy, d_total=None):
+    """Modes 1 and 3 (solution/rmsnorm.py:37-48): xhat = x * rstd, g = dy * w,
+    dx = rstd * (g - xhat * sum(g * xhat) / hidden) (+ d_total)."""
+    xhat = x.detach().float() * rstd[..., None]
+    g = dy.detach().float() * weight.detach().float()
+    mean_gx = (g * xhat).sum(dim=-1, keepdim=True) / x.shape[-1]
+    dx = rstd[..., None] * (g - xhat * mean_gx)
+    if d_total is not None:
+        dx = dx + d_total.detach().float()
+    return dx
+
+
 def max_rel_err(got, want):
     """max |got - want| / max |want| : the error measure of the fp16 tolerance (<= 1e-2)."""
     got, want = got.detach().float(), want.detach().float()

@@ -136,3 +136,26 @@ def test_swiglu_matches_reference_kernel(name):
         same_sign = (val.view(torch.int16) ^ want.view(torch.int16)) >= 0
         assert bool(((steps <= 1) | ~same_sign & (val.abs() + want.abs() < 1e-6)).all()), key
         assert float((steps > 0).float().mean()) < 1e-3, key
+
+
+@pytest.mark.parametrize("name", ["qwen", "odd"])
+@pytest.mark.parametrize("tag", ["f32", "f16"])
+def test_rmsnorm_matches_reference_kernel(name, tag):
+    """The oracle's RMSNorm against the reference's rmsnorm_kernel in its four modes
+    (tests/golden/make_golden_rmsnorm.py). The row sums are taken in another order than the
+    interpreter's tree, so: fp32 results within 2e-6 relative, fp16 outputs within one step."""
+    z = np.load(GOLDEN / "rmsnorm_small.npz")
+    t = lambda key: torch.from_numpy(z[f"{name}_{key}"])
+    dtype = torch.float32 if tag == "f32" else torch.float16
+    x, w, delta, d_total = t("x"), t("w"), t("delta"), t("d_total")
+    dy = t("dy").to(dtype)
+    tol = dict(rtol=2e-6, atol=2e-6) if tag == "f32" else dict(rtol=1e-3, atol=1e-3)
+    y, rstd, _ = nf4_oracle.rmsnorm_fwd(x, w, 1e-6, None, dtype)
+    torch.testing.assert_close(y.float(), t(f"{tag}_y").float(), **tol)
+    torch.testing.assert_close(rstd, t(f"{tag}_rstd"), rtol=2e-6, atol=0)
+    torch.testing.assert_close(nf4_oracle.rmsnorm_bwd(x, w, rstd, dy), t(f"{tag}_dx"), rtol=2e-5, atol=2e-6)
+    y2, rstd2, total = nf4_oracle.rmsnorm_fwd(x, w, 1e-6, delta, dtype)
+    assert torch.equal(total, t(f"{tag}_total"))          # the same fp32 addition
+    torch.testing.assert_close(y2.float(), t(f"{tag}_y_add").float(), **tol)
+    torch.testing.assert_close(nf4_oracle.rmsnorm_bwd(total, w, rstd2, dy, d_total), t(f"{tag}_dx_add"),
+                               rtol=2e-5, atol=2e-6)
