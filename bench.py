@@ -589,6 +589,28 @@ def run_single(args):
     sw["fused_hidden_only_tflops"] = sw["flops_gate_up"] / (sw["fused_hidden_only_us"] * 1e-6) / 1e12
     del sw_acts
 
+    # ---- the step before the projections: RMSNorm on the fp32 stream (fp16 output), against the
+    # HBM roofline. 16,384 rows x 1536 so that one launch moves more than the L2 holds; two
+    # sets of every input in turn.
+    from hackaton_b200.rmsnorm import _backward as rn_bwd, _forward as rn_fwd
+    rn_rows, rn_hidden = 16384, 1536
+    rn_x = [torch.randn(rn_rows, rn_hidden, device=device) for _ in range(2)]
+    rn_delta = [torch.randn(rn_rows, rn_hidden, device=device).half() for _ in range(2)]
+    rn_w = 1 + 0.1 * torch.randn(rn_hidden, device=device)
+    rn_dy = [torch.randn(rn_rows, rn_hidden, device=device).half() for _ in range(2)]
+    _, rn_rstd, _ = rn_fwd(rn_x[0], None, rn_w, 1e-6, True)
+    rn_elems = rn_rows * rn_hidden
+    rn = {"rows": rn_rows, "hidden": rn_hidden, "hbm_peak_gbs": pk["hbm_gbs"]}
+    for key, bytes_per_elem, fn in (
+            ("fwd_f16", 6, lambda i: rn_fwd(rn_x[i % 2], None, rn_w, 1e-6, True)),
+            ("add_fwd_f16", 12, lambda i: rn_fwd(rn_x[i % 2], rn_delta[i % 2], rn_w, 1e-6, True)),
+            ("bwd_f16", 10, lambda i: rn_bwd(rn_x[i % 2], rn_w, rn_rstd, rn_dy[i % 2], None)),
+            ("bwd_plus_sum_grad_f16", 14, lambda i: rn_bwd(rn_x[i % 2], rn_w, rn_rstd, rn_dy[i % 2], rn_x[(i + 1) % 2]))):
+        us = time_kernel(fn) * 1e3
+        gbs = rn_elems * bytes_per_elem / (us * 1e-6) / 1e9
+        rn[key] = {"us": us, "gbs": gbs, "frac_of_hbm": gbs / pk["hbm_gbs"], "bytes_per_element": bytes_per_elem}
+    del rn_x, rn_delta, rn_dy
+
     gemm_flops = 2.0 * m * 8960 * 1536
     achieved = gemm_flops / (kern["gate_fwd"] * 1e-3) / 1e12
     # The kernel is timed alone in bursts of a few milliseconds, at full clocks: the denominator is
@@ -686,7 +708,7 @@ def run_single(args):
         "frac_of_tensor_peak": value / pk["tflops_burst"],
         "frac_of_sustained_tensor_peak": value / pk["tflops_sustained"],
         "ms_per_28_layer_step": total_ms / args.steps * N_LAYERS,
-        "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs, "swiglu": sw,
+        "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs, "swiglu": sw, "rmsnorm": rn,
         "step_ms_min_med_max": [min(per_step), statistics.median(per_step), max(per_step)],
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,

@@ -9,7 +9,8 @@
 // flight together (hidden = 128 * NV floats; NV = 12 and 28 are the Qwen2.5 1.5B / 7B widths),
 // two warp reductions by shuffles, outputs written once. HBM bound: 6 to 14 bytes per element.
 // Any other width takes the generic kernel, which walks the row twice (the second time out of
-// L1 / L2).
+// L1 / L2). Inputs are read through the read-only path (ld.global.nc), which lets the compiler
+// issue a row's loads ahead of its stores: outputs must not overlap inputs.
 #include <cuda_fp16.h>
 
 #include "kernels.h"
@@ -27,23 +28,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 __device__ __forceinline__ float4 load4_any(const void* base, long long idx4, int half) {
     if (half) {
-        const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(base) + idx4);
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(base) + idx4);
         const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
         const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
         return make_float4(a.x, a.y, b.x, b.y);
     }
-    return __ldcs(reinterpret_cast<const float4*>(base) + idx4);
-}
-
-// Same with the default cache policy (the caller reads the data again soon).
-__device__ __forceinline__ float4 load4_keep(const void* base, long long idx4, int half) {
-    if (half) {
-        const uint2 raw = reinterpret_cast<const uint2*>(base)[idx4];
-        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-        return make_float4(a.x, a.y, b.x, b.y);
-    }
-    return reinterpret_cast<const float4*>(base)[idx4];
+    return __ldg(reinterpret_cast<const float4*>(base) + idx4);
 }
 
 __device__ __forceinline__ void store4_any(void* base, long long idx4, int half, float4 v) {
@@ -69,7 +59,7 @@ rmsnorm_rows_kernel(const RmsNormArgs a) {
     const long long base4 = row * (long long)(NV * 32);  // in units of 4 elements
     float4 x[NV];
 #pragma unroll
-    for (int i = 0; i < NV; ++i) x[i] = __ldcs(reinterpret_cast<const float4*>(a.x) + base4 + i * 32 + lane);
+    for (int i = 0; i < NV; ++i) x[i] = __ldg(reinterpret_cast<const float4*>(a.x) + base4 + i * 32 + lane);
     if (a.mode == 2) {
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
@@ -102,7 +92,7 @@ rmsnorm_rows_kernel(const RmsNormArgs a) {
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const float4 w = __ldg(reinterpret_cast<const float4*>(a.w) + i * 32 + lane);
-            const float4 dy = load4_keep(a.dy, base4 + i * 32 + lane, a.y_half);
+            const float4 dy = load4_any(a.dy, base4 + i * 32 + lane, a.y_half);
             x[i].x *= rstd; x[i].y *= rstd; x[i].z *= rstd; x[i].w *= rstd;  // xhat
             dot += dy.x * w.x * x[i].x + dy.y * w.y * x[i].y + dy.z * w.z * x[i].z + dy.w * w.w * x[i].w;
         }
@@ -110,11 +100,11 @@ rmsnorm_rows_kernel(const RmsNormArgs a) {
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const float4 w = __ldg(reinterpret_cast<const float4*>(a.w) + i * 32 + lane);
-            const float4 dy = load4_keep(a.dy, base4 + i * 32 + lane, a.y_half);
+            const float4 dy = load4_any(a.dy, base4 + i * 32 + lane, a.y_half);
             float4 dx = make_float4(rstd * (dy.x * w.x - x[i].x * mean_gx), rstd * (dy.y * w.y - x[i].y * mean_gx),
                                     rstd * (dy.z * w.z - x[i].z * mean_gx), rstd * (dy.w * w.w - x[i].w * mean_gx));
             if (a.mode == 3) {
-                const float4 t = __ldcs(reinterpret_cast<const float4*>(a.d_total) + base4 + i * 32 + lane);
+                const float4 t = __ldg(reinterpret_cast<const float4*>(a.d_total) + base4 + i * 32 + lane);
                 dx.x += t.x; dx.y += t.y; dx.z += t.z; dx.w += t.w;
             }
             reinterpret_cast<float4*>(a.dx)[base4 + i * 32 + lane] = dx;
