@@ -22,6 +22,7 @@ EXPORTS = (
     "nf4b200_set_sm_limit", "nf4b200_gate_up_swiglu_fwd", "nf4b200_gate_up_swiglu_workspace_bytes",
     "nf4b200_swiglu_fwd", "nf4b200_swiglu_bwd", "nf4b200_linear_bwd_dx_swiglu",
     "nf4b200_linear_bwd_dx_swiglu_workspace_bytes", "nf4b200_rmsnorm_fwd", "nf4b200_rmsnorm_bwd",
+    "nf4b200_qkv_rotate",
 )
 
 F16, BF16, F32 = 0, 1, 2
@@ -111,6 +112,9 @@ def lib() -> ctypes.CDLL:
                                            c_void_p, c_int64, c_int64, c_float, c_void_p]
     handle.nf4b200_rmsnorm_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                            c_void_p, c_int64, c_int64, c_void_p]
+    handle.nf4b200_qkv_rotate.argtypes = [c_void_p] * 8 + [c_int64, c_int64, c_void_p, c_void_p, c_int64,
+                                                           c_int64, c_int, c_int, c_int, c_int, c_int,
+                                                           c_int, c_void_p]
     handle.nf4b200_swiglu_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_int64, c_void_p]
     handle.nf4b200_swiglu_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                           c_void_p]

@@ -635,6 +635,42 @@ int nf4b200_rmsnorm_bwd(const void* x, const void* weight, const void* rstd, con
     return NF4B200_OK;
 }
 
+int nf4b200_qkv_rotate(const void* q, const void* k, const void* v, void* q_out, void* k_out,
+                       void* v_out, const void* cos, const void* sin, int64_t cos_stride_b,
+                       int64_t cos_stride_t, const void* b_idx, const void* t_idx, int64_t tokens,
+                       int64_t seq, int heads, int kv_heads, int dim, int padded, int backward,
+                       int proj_dtype, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (tokens < 0 || seq <= 0 || seq > 0x7FFFFFFF || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0)
+        return fail(NF4B200_EINVAL, "qkv_rotate: bad shape (tokens %lld, seq %lld, heads %d, kv heads %d)",
+                    (long long)tokens, (long long)seq, heads, kv_heads);
+    if (dim != 64 && dim != 128 && dim != 256)
+        return fail(NF4B200_EINVAL, "qkv_rotate: head size %d (64, 128 or 256)", dim);
+    if (proj_dtype != NF4B200_F16 && proj_dtype != NF4B200_F32)
+        return fail(NF4B200_EINVAL, "qkv_rotate: projections must be fp16 or fp32");
+    if (tokens > 0 && (!q || !k || !v || !q_out || !k_out || !v_out || !cos || !sin || !b_idx || !t_idx))
+        return fail(NF4B200_EINVAL, "qkv_rotate: NULL argument");
+    if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(q_out) || !aligned16(k_out) ||
+        !aligned16(v_out) || !aligned16(cos) || !aligned16(sin))
+        return fail(NF4B200_EINVAL, "qkv_rotate: arrays must be 16-byte aligned");
+    if (cos_stride_b % 4 != 0 || cos_stride_t % 4 != 0 || cos_stride_t < dim)
+        return fail(NF4B200_EINVAL, "qkv_rotate: cos / sin strides %lld, %lld", (long long)cos_stride_b,
+                    (long long)cos_stride_t);
+    nf4::RopeArgs a = {};
+    a.q = q; a.k = k; a.v = v; a.qo = q_out; a.ko = k_out; a.vo = v_out;
+    a.cos = static_cast<const float*>(cos); a.sin = static_cast<const float*>(sin);
+    a.b_idx = static_cast<const int*>(b_idx); a.t_idx = static_cast<const int*>(t_idx);
+    a.tokens = tokens; a.cos_stride_b = cos_stride_b; a.cos_stride_t = cos_stride_t;
+    a.seq = (int)seq; a.heads = heads; a.kv_heads = kv_heads; a.dim = dim;
+    a.padded = padded ? 1 : 0; a.backward = backward ? 1 : 0;
+    a.proj_f32 = proj_dtype == NF4B200_F32 ? 1 : 0;
+    cudaError_t e = nf4::launch_qkv_rotate(a, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "qkv_rotate: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
 int nf4b200_swiglu_fwd(const void* gate, const void* up, void* hidden, int64_t n, void* stream) {
     DeviceInfo* d = nullptr;
     int rc = require_sm100(&d);

@@ -160,6 +160,25 @@ struct RmsNormArgs {
 };
 cudaError_t launch_rmsnorm(const RmsNormArgs& a, cudaStream_t stream);
 
+// Rotary embedding + grouped-query expansion of the packed q / k / v projections (rope.cu).
+struct RopeArgs {
+    const void* q;          // forward: projections [tokens, heads*dim] / [tokens, kv_heads*dim]
+    const void* k;          //          (fp16, or fp32 when proj_f32);
+    const void* v;          // backward: gradients of the rotated heads (fp16, output layout)
+    void* qo;               // forward: rotated heads, fp16, packed (N, H, D) or padded (B, H, T, D)
+    void* ko;               // backward: gradients of the projections (their type)
+    void* vo;
+    const float* cos;       // [1 or B, T, dim] fp32
+    const float* sin;
+    const int* b_idx;       // [tokens]: sequence of each packed token
+    const int* t_idx;       // [tokens]: its position
+    long long tokens;
+    long long cos_stride_b, cos_stride_t;  // in elements (0 for a broadcast batch dimension)
+    int seq, heads, kv_heads, dim;
+    int padded, backward, proj_f32;
+};
+cudaError_t launch_qkv_rotate(const RopeArgs& a, cudaStream_t stream);
+
 // Weight-streaming forward kernel for M <= 64 (gemv.cu); launch_gemm* route eligible calls to it.
 bool gemv_eligible(const GemmArgs& a);
 cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t stream);

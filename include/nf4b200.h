@@ -235,6 +235,25 @@ int nf4b200_rmsnorm_bwd(const void* x, const void* weight, const void* rstd, con
                         void* stream);
 
 /*
+ * Rotary embedding + grouped-query expansion on the packed q / k / v projections: the step after
+ * the q/k/v GEMM (the reference's qkv_kernel / QKVRotate, solution/attention.py:36-192).
+ *   backward == 0: q [tokens, heads*dim], k, v [tokens, kv_heads*dim] (proj_dtype: fp16 or fp32)
+ *     -> q_out, k_out, v_out fp16, every k / v head written heads/kv_heads times; rows packed
+ *     (tokens, heads, dim) or, with `padded`, (batch, heads, seq, dim) at (b_idx, t_idx) (the
+ *     caller zero-fills the padded outputs first). y1 = x1*c1 - x2*s1, y2 = x2*c2 + x1*s2 over the
+ *     two halves of a head, fp32 arithmetic, one rounding.
+ *   backward != 0: q, k, v are the fp16 gradients of those outputs (same layout); q_out, k_out,
+ *     v_out receive the projections' gradients (proj_dtype), copies summed, rotation inverted.
+ * cos / sin: fp32 [1 or batch, seq, dim] with element strides (cos_stride_b = 0 for a broadcast
+ * batch dimension); b_idx, t_idx: int32 [tokens].
+ */
+int nf4b200_qkv_rotate(const void* q, const void* k, const void* v, void* q_out, void* k_out,
+                       void* v_out, const void* cos, const void* sin, int64_t cos_stride_b,
+                       int64_t cos_stride_t, const void* b_idx, const void* t_idx, int64_t tokens,
+                       int64_t seq, int heads, int kv_heads, int dim, int padded, int backward,
+                       int proj_dtype, void* stream);
+
+/*
  * Rank-16 projection used by both passes of the LoRA update (peft's lora_A / lora_B linears;
  * third-party in the reference, configured at README.md:91 and task/task.yaml:18-21):
  *   out[m, 16] = scaling * in[m, c] . P        (fp16 in, fp32 accumulate, fp16 out)

@@ -158,6 +158,59 @@ def rmsnorm_bwd(x, weight, rstd, dy, d_total=None):
     return dx
 
 
+def _rope_rows(cos, sin, b_idx, t_idx):
+    """cos / sin rows of each packed token: (1 or B, T, D) indexed by (b, t) (solution/attention.py:45-49)."""
+    b = b_idx.long() if cos.shape[0] > 1 else torch.zeros_like(b_idx.long())
+    return cos[b, t_idx.long()].float(), sin[b, t_idx.long()].float()
+
+
+def qkv_rotate_fwd(q, k, v, cos, sin, b_idx, t_idx, batch, seq, heads, kv_heads, padded):
+    """The reference's `_qkv_forward` (solution/attention.py:36-83): per head, over its two halves,
+    y1 = x1*c1 - x2*s1, y2 = x2*c2 + x1*s2 in fp32, rounded to fp16; k and v heads repeated
+    heads / kv_heads times; rows packed (N, H, D) or scattered into zeros (B, H, T, D)."""
+    n, dim = q.shape[0], q.shape[-1] // heads
+    half, rep = dim // 2, heads // kv_heads
+    c, s = _rope_rows(cos, sin, b_idx, t_idx)
+    c1, c2, s1, s2 = c[:, None, :half], c[:, None, half:], s[:, None, :half], s[:, None, half:]
+
+    def rotate(x, nh):
+        x = x.detach().float().reshape(n, nh, dim)
+        x1, x2 = x[..., :half], x[..., half:]
+        return torch.cat((x1 * c1 - x2 * s1, x2 * c2 + x1 * s2), dim=-1).half()
+
+    qo = rotate(q, heads)
+    ko = rotate(k, kv_heads).repeat_interleave(rep, dim=1)
+    vo = v.detach().reshape(n, kv_heads, dim).half().repeat_interleave(rep, dim=1)
+    if not padded:
+        return qo, ko, vo
+    outs = []
+    for x in (qo, ko, vo):
+        full = torch.zeros(batch, heads, seq, dim, dtype=torch.float16)
+        full[b_idx.long(), :, t_idx.long()] = x
+        outs.append(full)
+    return tuple(outs)
+
+
+def qkv_rotate_bwd(dq, dk, dv, cos, sin, b_idx, t_idx, heads, kv_heads, padded, dtype):
+    """The reference's `_qkv_backward` (solution/attention.py:86-133): the copies' gradients summed
+    in fp32, dx1 = dy1*c1 + dy2*s2, dx2 = dy2*c2 - dy1*s1, written (N, heads * D) in `dtype`."""
+    if padded:
+        dq, dk, dv = (g[b_idx.long(), :, t_idx.long()] for g in (dq, dk, dv))
+    n, dim = dq.shape[0], dq.shape[-1]
+    half, rep = dim // 2, heads // kv_heads
+    c, s = _rope_rows(cos, sin, b_idx, t_idx)
+    c1, c2, s1, s2 = c[:, None, :half], c[:, None, half:], s[:, None, :half], s[:, None, half:]
+
+    def unrotate(d):
+        d1, d2 = d[..., :half], d[..., half:]
+        return torch.cat((d1 * c1 + d2 * s2, d2 * c2 - d1 * s1), dim=-1)
+
+    dq = unrotate(dq.float()).reshape(n, heads * dim)
+    dk = unrotate(dk.float().reshape(n, kv_heads, rep, dim).sum(dim=2)).reshape(n, kv_heads * dim)
+    dv = dv.float().reshape(n, kv_heads, rep, dim).sum(dim=2).reshape(n, kv_heads * dim)
+    return dq.to(dtype), dk.to(dtype), dv.to(dtype)
+
+
 def max_rel_err(got, want):
     """max |got - want| / max |want| : the error measure of the fp16 tolerance (<= 1e-2)."""
     got, want = got.detach().float(), want.detach().float()

@@ -159,3 +159,31 @@ def test_rmsnorm_matches_reference_kernel(name, tag):
     torch.testing.assert_close(y2.float(), t(f"{tag}_y_add").float(), **tol)
     torch.testing.assert_close(nf4_oracle.rmsnorm_bwd(total, w, rstd2, dy, d_total), t(f"{tag}_dx_add"),
                                rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("tag", ["f16", "f32"])
+@pytest.mark.parametrize("layout", ["packed", "padded"])
+def test_qkv_rotate_matches_reference_kernel(tag, layout):
+    """The oracle's rotation + GQA expansion against the reference's qkv_kernel run through its
+    QKVRotate (tests/golden/make_golden_rope.py). Products and sums may be contracted differently
+    (one fp32 rounding), so fp16 outputs may differ by one step in a few places."""
+    z = np.load(GOLDEN / "rope_small.npz")
+    t = lambda key: torch.from_numpy(z[key])
+    batch, seq, heads, kv_heads, dim = (int(x) for x in z["meta"])
+    padded = layout == "padded"
+    args = (t("cos"), t("sin"), t("b_idx"), t("t_idx"))
+    outs = nf4_oracle.qkv_rotate_fwd(t(f"{tag}_q"), t(f"{tag}_k"), t(f"{tag}_v"), *args, batch, seq,
+                                     heads, kv_heads, padded)
+    for got, key in zip(outs, ("qo", "ko", "vo")):
+        want = t(f"{tag}_{layout}_{key}")
+        assert got.shape == want.shape and got.dtype == want.dtype
+        torch.testing.assert_close(got.float(), want.float(), rtol=1e-3, atol=1e-3)
+    assert torch.equal(outs[2], t(f"{tag}_{layout}_vo"))        # v is only copied
+    dtype = torch.float16 if tag == "f16" else torch.float32
+    grads = nf4_oracle.qkv_rotate_bwd(*(t(f"{tag}_{layout}_{k}") for k in ("gq", "gk", "gv")), *args,
+                                      heads, kv_heads, padded, dtype)
+    tol = dict(rtol=2e-3, atol=2e-3) if tag == "f16" else dict(rtol=1e-5, atol=1e-5)
+    for got, key in zip(grads, ("dq", "dk", "dv")):
+        want = t(f"{tag}_{layout}_{key}")
+        assert got.shape == want.shape and got.dtype == want.dtype
+        torch.testing.assert_close(got.float(), want.float(), **tol)
