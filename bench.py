@@ -611,6 +611,36 @@ def run_single(args):
         rn[key] = {"us": us, "gbs": gbs, "frac_of_hbm": gbs / pk["hbm_gbs"], "bytes_per_element": bytes_per_elem}
     del rn_x, rn_delta, rn_dy
 
+    # ---- the step after q/k/v: rotation + grouped-query expansion, against the HBM roofline
+    # (16,384 packed tokens of 4 sequences, 12 heads over 2 kv heads of 128: 218 MB per launch)
+    from hackaton_b200.rope import _launch as rope_launch
+    rp_n, rp_seq, rp_h, rp_kv, rp_d = 16384, 4096, 12, 2, 128
+    rp_in = [[torch.randn(rp_n, hd * rp_d, device=device).half() for hd in (rp_h, rp_kv, rp_kv)] for _ in range(2)]
+    rp_out = [[torch.empty(rp_n, rp_h, rp_d, device=device, dtype=torch.float16) for _ in range(3)] for _ in range(2)]
+    rp_grad = [torch.empty(rp_n, hd * rp_d, device=device, dtype=torch.float16) for hd in (rp_h, rp_kv, rp_kv)]
+    inv_freq = 1.0 / (1000000.0 ** (torch.arange(0, rp_d, 2, device=device).float() / rp_d))
+    emb = torch.arange(rp_seq, device=device).float()[:, None] * inv_freq[None]
+    emb = torch.cat((emb, emb), dim=-1)
+    rp_cos, rp_sin = emb.cos()[None].contiguous(), emb.sin()[None].contiguous()
+    rp_b = (torch.arange(rp_n, device=device) // rp_seq).to(torch.int32)
+    rp_t = (torch.arange(rp_n, device=device) % rp_seq).to(torch.int32)
+
+    def rope_call(i, backward):
+        src, dst = (rp_out[i % 2], rp_grad) if backward else (rp_in[i % 2], rp_out[i % 2])
+        rope_launch(*src, *dst, rp_cos, rp_sin, 0, rp_b, rp_t, rp_n, rp_seq, rp_h, rp_kv, rp_d, False,
+                    backward, torch.float16)
+
+    rope_call(0, False)
+    rope_call(1, False)
+    rp_bytes = rp_n * 2.0 * ((rp_h + 2 * rp_kv) * rp_d + 3 * rp_h * rp_d)
+    rp = {"tokens": rp_n, "heads": rp_h, "kv_heads": rp_kv, "head_dim": rp_d, "bytes_per_launch": rp_bytes,
+          "hbm_peak_gbs": pk["hbm_gbs"]}
+    for key, backward in (("fwd", False), ("bwd", True)):
+        us = time_kernel(lambda i: rope_call(i, backward)) * 1e3
+        gbs = rp_bytes / (us * 1e-6) / 1e9
+        rp[key] = {"us": us, "gbs": gbs, "frac_of_hbm": gbs / pk["hbm_gbs"]}
+    del rp_in, rp_out, rp_grad
+
     gemm_flops = 2.0 * m * 8960 * 1536
     achieved = gemm_flops / (kern["gate_fwd"] * 1e-3) / 1e12
     # The kernel is timed alone in bursts of a few milliseconds, at full clocks: the denominator is
@@ -708,7 +738,7 @@ def run_single(args):
         "frac_of_tensor_peak": value / pk["tflops_burst"],
         "frac_of_sustained_tensor_peak": value / pk["tflops_sustained"],
         "ms_per_28_layer_step": total_ms / args.steps * N_LAYERS,
-        "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs, "swiglu": sw, "rmsnorm": rn,
+        "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs, "swiglu": sw, "rmsnorm": rn, "rope": rp,
         "step_ms_min_med_max": [min(per_step), statistics.median(per_step), max(per_step)],
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,

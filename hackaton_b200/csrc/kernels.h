@@ -176,6 +176,7 @@ struct RopeArgs {
     long long cos_stride_b, cos_stride_t;  // in elements (0 for a broadcast batch dimension)
     int seq, heads, kv_heads, dim;
     int padded, backward, proj_f32;
+    int lps_shift;          // set by the launcher: log2(threads per work item)
 };
 cudaError_t launch_qkv_rotate(const RopeArgs& a, cudaStream_t stream);
 
