@@ -80,12 +80,28 @@ qkv_rotate_kernel(const RopeArgs a) {
     const int half = a.dim / 2;
     const unsigned slots = (unsigned)(a.heads + 2 * a.kv_heads);
     const unsigned gid = blockIdx.x * blockDim.x + threadIdx.x;
+    // Forward: a token's 16 slots side by side. Backward: every token's q heads first, then every
+    // token's k / v heads, so that a CTA holds either light items (q) or heavy ones (k / v read
+    // `rep` copies) and no warp idles in a CTA that waits for its one heavy warp (measured:
+    // 62 -> 54 us; the same order made the forward 4 % slower).
     const unsigned item = gid >> a.lps_shift;
-    const unsigned tok_u = item / slots;
-    if (tok_u >= (unsigned)a.tokens) return;
+    if (item >= (unsigned)a.tokens * slots) return;
+    const unsigned q_items = (unsigned)a.tokens * (unsigned)a.heads;
+    unsigned tok_u, slot_u;
+    if (!BACKWARD) {
+        tok_u = item / slots;
+        slot_u = item - tok_u * slots;
+    } else if (item < q_items) {
+        tok_u = item / (unsigned)a.heads;
+        slot_u = item - tok_u * (unsigned)a.heads;
+    } else {
+        const unsigned r = item - q_items, kv2 = 2u * (unsigned)a.kv_heads;
+        tok_u = r / kv2;
+        slot_u = (unsigned)a.heads + (r - tok_u * kv2);
+    }
     const int j = (int)(gid & ((1u << a.lps_shift) - 1u)) * 8;
     const long long tok = tok_u;
-    const int slot = (int)(item - tok_u * slots);
+    const int slot = (int)slot_u;
     const int b = a.b_idx[tok], t = a.t_idx[tok];
     const int rep = a.heads / a.kv_heads;
     // row (in units of heads) of output head h: packed (N, H, D) or padded (B, H, T, D)
