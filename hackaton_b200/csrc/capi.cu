@@ -671,6 +671,48 @@ int nf4b200_qkv_rotate(const void* q, const void* k, const void* v, void* q_out,
     return NF4B200_OK;
 }
 
+int nf4b200_ce_stats(const void* logits, int logits_dtype, const void* targets, void* lse, void* loss,
+                     void* entropy, void* argmax, int64_t rows, int64_t vocab, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (rows < 0 || vocab <= 0 || vocab > 0x7FFFFFFF)
+        return fail(NF4B200_EINVAL, "ce_stats: bad shape %lld x %lld", (long long)rows, (long long)vocab);
+    if (logits_dtype != NF4B200_F16 && logits_dtype != NF4B200_F32)
+        return fail(NF4B200_EINVAL, "ce_stats: logits must be fp16 or fp32");
+    if (rows > 0 && (!logits || !targets || !lse || !loss))
+        return fail(NF4B200_EINVAL, "ce_stats: NULL argument");
+    nf4::CeArgs a = {};
+    a.logits = logits; a.targets = static_cast<const long long*>(targets);
+    a.lse = static_cast<float*>(lse); a.loss = static_cast<float*>(loss);
+    a.entropy = static_cast<float*>(entropy); a.argmax = static_cast<long long*>(argmax);
+    a.rows = rows; a.vocab = vocab; a.f32 = logits_dtype == NF4B200_F32 ? 1 : 0;
+    cudaError_t e = nf4::launch_ce(a, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "ce_stats: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_ce_grad(const void* logits, int logits_dtype, const void* targets, const void* lse,
+                    const void* scale, void* grad, int64_t rows, int64_t vocab, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (rows < 0 || vocab <= 0 || vocab > 0x7FFFFFFF)
+        return fail(NF4B200_EINVAL, "ce_grad: bad shape %lld x %lld", (long long)rows, (long long)vocab);
+    if (logits_dtype != NF4B200_F16 && logits_dtype != NF4B200_F32)
+        return fail(NF4B200_EINVAL, "ce_grad: logits must be fp16 or fp32");
+    if (rows > 0 && (!logits || !targets || !lse || !scale || !grad))
+        return fail(NF4B200_EINVAL, "ce_grad: NULL argument");
+    nf4::CeArgs a = {};
+    a.logits = logits; a.targets = static_cast<const long long*>(targets);
+    a.lse = const_cast<float*>(static_cast<const float*>(lse));
+    a.scale = static_cast<const float*>(scale); a.grad = grad;
+    a.rows = rows; a.vocab = vocab; a.f32 = logits_dtype == NF4B200_F32 ? 1 : 0;
+    cudaError_t e = nf4::launch_ce(a, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "ce_grad: %s", cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
 int nf4b200_swiglu_fwd(const void* gate, const void* up, void* hidden, int64_t n, void* stream) {
     DeviceInfo* d = nullptr;
     int rc = require_sm100(&d);

@@ -180,6 +180,23 @@ struct RopeArgs {
 };
 cudaError_t launch_qkv_rotate(const RopeArgs& a, cudaStream_t stream);
 
+// Cross-entropy over the vocabulary (cross_entropy.cu). grad == null: statistics pass (lse and
+// loss always; entropy / argmax when not null); grad != null: gradient pass.
+struct CeArgs {
+    const void* logits;          // [rows, vocab] fp16, or fp32 when f32
+    const long long* targets;    // [rows], negative = ignored row
+    float* lse;                  // [rows]: written by the statistics pass, read by the gradient pass
+    float* loss;                 // [rows]
+    float* entropy;              // [rows] or null
+    long long* argmax;           // [rows] or null
+    const float* scale;          // gradient pass: one fp32 number on the device
+    void* grad;                  // gradient pass: [rows, vocab] in the logits' type (may be `logits`)
+    long long rows, vocab;
+    int f32;
+    int vec;                     // set by the launcher
+};
+cudaError_t launch_ce(const CeArgs& a, cudaStream_t stream);
+
 // Weight-streaming forward kernel for M <= 64 (gemv.cu); launch_gemm* route eligible calls to it.
 bool gemv_eligible(const GemmArgs& a);
 cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t stream);

@@ -254,6 +254,23 @@ int nf4b200_qkv_rotate(const void* q, const void* k, const void* v, void* q_out,
                        int proj_dtype, void* stream);
 
 /*
+ * Cross-entropy over the vocabulary from the lm_head's logits, the other large tensor of the step:
+ * the reference's ce_kernel (solution/kernels.py:106-170) behind `ce_stats` / `ce_grad`
+ * (:173-204), `fused_cross_entropy` (:207-238) and the chunked lm_head + loss
+ * (solution/lm_loss.py:27-62).
+ *   nf4b200_ce_stats: per row, in one pass over [rows, vocab] logits (fp16 or fp32): lse =
+ *     logsumexp (0 for rows with target < 0), loss = lse - logit[target] (0 for those rows);
+ *     entropy (= lse - E[x], may be NULL) and argmax (int64, first maximal index, may be NULL).
+ *   nf4b200_ce_grad: grad = scale[0] * (exp(logit - lse) - onehot(target)), 0 for rows with
+ *     target < 0, in the logits' type; `grad` may be `logits` (in place).
+ * targets: int64 [rows]; lse, loss, entropy, scale: fp32 on the device.
+ */
+int nf4b200_ce_stats(const void* logits, int logits_dtype, const void* targets, void* lse, void* loss,
+                     void* entropy, void* argmax, int64_t rows, int64_t vocab, void* stream);
+int nf4b200_ce_grad(const void* logits, int logits_dtype, const void* targets, const void* lse,
+                    const void* scale, void* grad, int64_t rows, int64_t vocab, void* stream);
+
+/*
  * Rank-16 projection used by both passes of the LoRA update (peft's lora_A / lora_B linears;
  * third-party in the reference, configured at README.md:91 and task/task.yaml:18-21):
  *   out[m, 16] = scaling * in[m, c] . P        (fp16 in, fp32 accumulate, fp16 out)

@@ -211,6 +211,33 @@ def qkv_rotate_bwd(dq, dk, dv, cos, sin, b_idx, t_idx, heads, kv_heads, padded, 
     return dq.to(dtype), dk.to(dtype), dv.to(dtype)
 
 
+def ce_stats(logits, targets):
+    """The statistics pass of the reference's ce_kernel (solution/kernels.py:106-146), per row of
+    fp32-widened logits: lse = logsumexp (0 for target < 0), loss = lse - logit[target] (0 for
+    those rows), entropy = lse - E_softmax[x], argmax = first maximal index."""
+    x = logits.detach().float()
+    lse = torch.logsumexp(x, dim=-1)
+    p = torch.softmax(x, dim=-1)
+    entropy = lse - (p * x).sum(dim=-1)
+    argmax = torch.argmax(x, dim=-1)                    # torch returns the first maximum
+    valid = targets >= 0
+    picked = x.gather(1, targets.clamp_min(0)[:, None])[:, 0]
+    zero = torch.zeros_like(lse)
+    return torch.where(valid, lse, zero), torch.where(valid, lse - picked, zero), entropy, argmax
+
+
+def ce_grad(logits, targets, lse, scale):
+    """The gradient pass (solution/kernels.py:149-165): scale * (exp(x - lse) - onehot(target)),
+    0 for rows with target < 0, rounded to the logits' type."""
+    x = logits.detach().float()
+    g = torch.exp(x - lse[:, None])
+    valid = targets >= 0
+    g[torch.arange(x.shape[0])[valid], targets[valid]] -= 1.0
+    g = g * float(scale)
+    g[~valid] = 0.0
+    return g.to(logits.dtype)
+
+
 def max_rel_err(got, want):
     """max |got - want| / max |want| : the error measure of the fp16 tolerance (<= 1e-2)."""
     got, want = got.detach().float(), want.detach().float()

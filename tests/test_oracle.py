@@ -187,3 +187,23 @@ def test_qkv_rotate_matches_reference_kernel(tag, layout):
         want = t(f"{tag}_{layout}_{key}")
         assert got.shape == want.shape and got.dtype == want.dtype
         torch.testing.assert_close(got.float(), want.float(), **tol)
+
+
+@pytest.mark.parametrize("name", ["ragged", "blocks"])
+@pytest.mark.parametrize("tag", ["f16", "f32"])
+def test_cross_entropy_matches_reference_kernel(name, tag):
+    """The oracle's cross-entropy against the reference's ce_kernel, both passes
+    (tests/golden/make_golden_ce.py): fp32 sums in another order, the argmax exact."""
+    z = np.load(GOLDEN / "ce_small.npz")
+    t = lambda key: torch.from_numpy(z[f"{name}_{tag}_{key}"])
+    logits, targets = t("logits"), torch.from_numpy(z[f"{name}_targets"])
+    lse, loss, entropy, argmax = nf4_oracle.ce_stats(logits, targets)
+    torch.testing.assert_close(lse, t("lse"), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(loss, t("loss"), rtol=1e-5, atol=1e-5)
+    torch.testing.assert_close(entropy, t("entropy"), rtol=1e-4, atol=1e-4)
+    assert torch.equal(argmax, t("argmax"))
+    assert float(lse[2]) == 0.0 and float(loss[2]) == 0.0          # the ignored row
+    grad = nf4_oracle.ce_grad(logits, targets, t("lse"), 0.37)
+    tol = dict(rtol=2e-3, atol=1e-6) if tag == "f16" else dict(rtol=1e-4, atol=1e-7)
+    torch.testing.assert_close(grad.float(), t("grad").float(), **tol)
+    assert not bool(t("grad")[2].any())
