@@ -641,6 +641,28 @@ def run_single(args):
         rp[key] = {"us": us, "gbs": gbs, "frac_of_hbm": gbs / pk["hbm_gbs"]}
     del rp_in, rp_out, rp_grad
 
+    # ---- the loss: cross-entropy statistics and gradient over 2048 rows of 151,936 fp16 logits
+    # (622 MB per pass, far more than the L2 holds), against the HBM roofline
+    from hackaton_b200.lm_loss import ce_grad, ce_stats
+    ce_rows, ce_vocab = 2048, 151936
+    ce_logits = torch.randn(ce_rows, ce_vocab, device=device, dtype=torch.float16)
+    ce_logits *= 3
+    ce_targets = torch.randint(0, ce_vocab, (ce_rows,), device=device)
+    ce_out = (torch.empty(ce_rows, device=device), torch.empty(ce_rows, device=device),
+              torch.empty(ce_rows, device=device), torch.empty(ce_rows, dtype=torch.int64, device=device))
+    ce_scale = torch.full((1,), 1.0 / ce_rows, device=device)
+    ce_grad_out = torch.empty_like(ce_logits)
+    ce_stats(ce_logits, ce_targets, True, out=ce_out)
+    ce_elems = float(ce_rows) * ce_vocab
+    ce = {"rows": ce_rows, "vocab": ce_vocab, "hbm_peak_gbs": pk["hbm_gbs"]}
+    for key, bytes_per_elem, fn in (
+            ("stats_all_outputs", 2, lambda i: ce_stats(ce_logits, ce_targets, True, out=ce_out)),
+            ("grad", 4, lambda i: ce_grad(ce_logits, ce_targets, ce_out[0], ce_scale, ce_grad_out))):
+        us = time_kernel(fn) * 1e3
+        gbs = ce_elems * bytes_per_elem / (us * 1e-6) / 1e9
+        ce[key] = {"us": us, "gbs": gbs, "frac_of_hbm": gbs / pk["hbm_gbs"], "bytes_per_element": bytes_per_elem}
+    del ce_logits, ce_grad_out
+
     gemm_flops = 2.0 * m * 8960 * 1536
     achieved = gemm_flops / (kern["gate_fwd"] * 1e-3) / 1e12
     # The kernel is timed alone in bursts of a few milliseconds, at full clocks: the denominator is
@@ -738,7 +760,7 @@ def run_single(args):
         "frac_of_tensor_peak": value / pk["tflops_burst"],
         "frac_of_sustained_tensor_peak": value / pk["tflops_sustained"],
         "ms_per_28_layer_step": total_ms / args.steps * N_LAYERS,
-        "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs, "swiglu": sw, "rmsnorm": rn, "rope": rp,
+        "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs, "swiglu": sw, "rmsnorm": rn, "rope": rp, "cross_entropy": ce,
         "step_ms_min_med_max": [min(per_step), statistics.median(per_step), max(per_step)],
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,

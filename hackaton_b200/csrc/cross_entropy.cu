@@ -18,6 +18,9 @@ namespace nf4 {
 constexpr int CE_THREADS = 256;
 constexpr float CE_NEG = -1.0e30f;  // finite "minus infinity", as in the reference (kernels.py:36)
 
+// Running statistics of the logits seen so far: maximum m, s = sum exp(x - m),
+// d = sum exp(x - m) * (x - m) (taken relative to m, so that the entropy log(s) - d / s does not
+// come out of the difference of two numbers as large as the logits), first index of the maximum.
 struct CeState {
     float m, s, d;
     int idx;
@@ -28,7 +31,7 @@ __device__ __forceinline__ CeState ce_merge(const CeState& a, const CeState& b) 
     r.m = fmaxf(a.m, b.m);
     const float fa = __expf(a.m - r.m), fb = __expf(b.m - r.m);
     r.s = a.s * fa + b.s * fb;
-    r.d = a.d * fa + b.d * fb;
+    r.d = fa * (a.d + a.s * (a.m - r.m)) + fb * (b.d + b.s * (b.m - r.m));
     r.idx = a.m > b.m ? a.idx : (b.m > a.m ? b.idx : min(a.idx, b.idx));
     return r;
 }
@@ -73,14 +76,16 @@ ce_stats_kernel(const CeArgs a) {
         float x[8];
         ce_load8<F32>(base, v * 8, x);
         float lm = x[0];
-        int li = 0;
 #pragma unroll
-        for (int e = 1; e < 8; ++e)
-            if (x[e] > lm) { lm = x[e]; li = e; }
-        if (lm > st.m) {
+        for (int e = 1; e < 8; ++e) lm = fmaxf(lm, x[e]);
+        if (lm > st.m) {  // rare after the first few vectors: only then look for the position
+            int li = 7;
+#pragma unroll
+            for (int e = 6; e >= 0; --e)
+                if (x[e] == lm) li = e;
             const float r = __expf(st.m - lm);
+            st.d = r * (st.d + st.s * (st.m - lm));
             st.s *= r;
-            st.d *= r;
             st.m = lm;
             st.idx = (int)(v * 8) + li;
         }
@@ -88,21 +93,21 @@ ce_stats_kernel(const CeArgs a) {
         for (int e = 0; e < 8; ++e) {
             const float w = __expf(x[e] - st.m);
             st.s += w;
-            st.d = fmaf(w, x[e], st.d);
+            st.d = fmaf(w, x[e] - st.m, st.d);
         }
     }
     for (long long i = n8 * 8 + threadIdx.x; i < a.vocab; i += CE_THREADS) {
         const float x = ce_load1<F32>(base, i);
         if (x > st.m) {
             const float r = __expf(st.m - x);
+            st.d = r * (st.d + st.s * (st.m - x));
             st.s *= r;
-            st.d *= r;
             st.m = x;
             st.idx = (int)i;
         }
         const float w = __expf(x - st.m);
         st.s += w;
-        st.d = fmaf(w, x, st.d);
+        st.d = fmaf(w, x - st.m, st.d);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -124,7 +129,7 @@ ce_stats_kernel(const CeArgs a) {
         const float picked = ce_load1<F32>(base, target > 0 ? target : 0);
         a.lse[row] = valid ? lse : 0.f;
         a.loss[row] = valid ? lse - picked : 0.f;
-        if (a.entropy != nullptr) a.entropy[row] = lse - t.d / t.s;
+        if (a.entropy != nullptr) a.entropy[row] = logf(t.s) - t.d / t.s;  // = lse - E[x]
         if (a.argmax != nullptr) a.argmax[row] = t.idx;
     }
 }

@@ -213,9 +213,9 @@ def qkv_rotate_bwd(dq, dk, dv, cos, sin, b_idx, t_idx, heads, kv_heads, padded, 
 
 def ce_stats(logits, targets):
     """The statistics pass of the reference's ce_kernel (solution/kernels.py:106-146), per row of
-    fp32-widened logits: lse = logsumexp (0 for target < 0), loss = lse - logit[target] (0 for
+    logits (here in float64, rounded to fp32 at the end): lse = logsumexp (0 for target < 0), loss = lse - logit[target] (0 for
     those rows), entropy = lse - E_softmax[x], argmax = first maximal index."""
-    x = logits.detach().float()
+    x = logits.detach().double()        # float64: the sums run over 10^5 terms
     lse = torch.logsumexp(x, dim=-1)
     p = torch.softmax(x, dim=-1)
     entropy = lse - (p * x).sum(dim=-1)
@@ -223,7 +223,8 @@ def ce_stats(logits, targets):
     valid = targets >= 0
     picked = x.gather(1, targets.clamp_min(0)[:, None])[:, 0]
     zero = torch.zeros_like(lse)
-    return torch.where(valid, lse, zero), torch.where(valid, lse - picked, zero), entropy, argmax
+    return (torch.where(valid, lse, zero).float(), torch.where(valid, lse - picked, zero).float(),
+            entropy.float(), argmax)
 
 
 def ce_grad(logits, targets, lse, scale):
