@@ -72,7 +72,9 @@ def as_numpy(t):
 
 
 def main():
-    ref = load_reference(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py /path/to/reference")
+    ref = load_reference(sys.argv[1])
     table = np.asarray(NF4_TABLE, dtype=np.float32)
 
     small = {"table": table}

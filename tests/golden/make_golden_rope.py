@@ -24,7 +24,9 @@ HERE = Path(__file__).resolve().parent
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden*.py /path/to/reference")
+    root = sys.argv[1]
     sys.path.insert(0, root)
     ref = importlib.import_module("solution.attention")
     lengths, seq, heads, kv_heads, dim = [5, 2, 4], 6, 4, 2, 64
