@@ -139,14 +139,20 @@ class ClockSampler:
 # synthetic layers
 # ------------------------------------------------------------------------------------------------
 
-def make_layer(shapes, seed, device, world=1, rank=0):
-    """One layer's quantised projections (this rank's row shard when world > 1) and LoRA pairs."""
+INPUT_SHARDED = ("o", "down")   # "paired" multi-GPU layout: these hold columns of W, the rest rows
+
+
+def make_layer(shapes, seed, device, world=1, rank=0, paired=False):
+    """One layer's quantised projections (this rank's shard when world > 1: rows of W, or columns
+    for the INPUT_SHARDED members of the paired layout) and LoRA pairs."""
     from hackaton_b200.quantize import quantize_nf4
 
     layer = {}
     for i, name in enumerate(ORDER):
         n, k = shapes[name]
         n_local = n // world
+        if paired and name in INPUT_SHARDED:
+            n_local, k = n, k // world
         g = torch.Generator(device=device).manual_seed(seed * 100 + i * 10 + rank)
         w = (torch.randn(n_local, k, generator=g, device=device) * 0.02).half()
         packed, state = quantize_nf4(w, blocksize=64, compress_statistics=True)
@@ -164,16 +170,21 @@ INPUT_OF = {"q": "x_attn", "k": "x_attn", "v": "x_attn", "o": "x_o", "gate": "x_
             "up": "x_mlp", "down": "x_down"}
 
 
-def make_activations(shapes, m, device, pinned=False, world=1):
-    """Inputs of the seven projections and their upstream gradients."""
+def make_activations(shapes, m, device, pinned=False, world=1, paired=False):
+    """Inputs of the seven projections and their upstream gradients (shards where the layout has
+    the rank hold only a shard: dY of output-sharded members, X of input-sharded ones)."""
     g = torch.Generator().manual_seed(1234)
     acts = {}
     widths = {"x_attn": shapes["q"][1], "x_o": shapes["o"][1], "x_mlp": shapes["gate"][1],
               "x_down": shapes["down"][1]}
+    if paired:
+        widths["x_o"] //= world
+        widths["x_down"] //= world
     for name, width in widths.items():
         acts[name] = torch.randn(m, width, generator=g).half()
     for name in ORDER:
-        acts["dy_" + name] = torch.randn(m, shapes[name][0] // world, generator=g).half()
+        cols = shapes[name][0] if paired and name in INPUT_SHARDED else shapes[name][0] // world
+        acts["dy_" + name] = torch.randn(m, cols, generator=g).half()
     if pinned:
         return {k: v.pin_memory() for k, v in acts.items()}
     return {k: v.to(device) for k, v in acts.items()}
@@ -295,6 +306,56 @@ def step_sharded(layer_mods, acts):
     return outs
 
 
+def step_paired(mods, acts):
+    """N > 1, paired layout: q/k/v and gate/up hold rows of W and keep their output shards (what
+    follows them works per head / per column), o and down hold columns of W and take those shards
+    as input. Four all-reduces of [M, hidden] per step, each issued asynchronously so that it
+    runs under the next GEMM; nothing is gathered."""
+    from hackaton_b200.sharded import backward_dx_group, forward_local_group
+
+    works, outs = [], []
+    outs += forward_local_group([mods[n] for n in ("q", "k", "v")], acts["x_attn"])
+    y, work = mods["o"].forward(acts["x_o"], async_op=True)
+    outs.append(y)
+    works.append(work)
+    outs += forward_local_group([mods[n] for n in ("gate", "up")], acts["x_mlp"])
+    y, work = mods["down"].forward(acts["x_down"], async_op=True)
+    outs.append(y)
+    works.append(work)
+    outs.append(mods["down"].backward_dx(acts["dy_down"])[0])
+    dx, work = backward_dx_group([mods[n] for n in ("gate", "up")],
+                                 [acts["dy_gate"], acts["dy_up"]], async_op=True)
+    outs.append(dx)
+    works.append(work)
+    outs.append(mods["o"].backward_dx(acts["dy_o"])[0])
+    dx, work = backward_dx_group([mods[n] for n in ("q", "k", "v")],
+                                 [acts["dy_q"], acts["dy_k"], acts["dy_v"]], async_op=True)
+    outs.append(dx)
+    works.append(work)
+    for w in works:
+        if w is not None:
+            w.wait()
+    return outs
+
+
+def step_paired_local(mods, acts):
+    """The GEMMs of step_paired without the exchanges."""
+    from hackaton_b200.group import linear_backward_dx_group, linear_forward_group
+    from hackaton_b200.nf4 import linear_backward_dx
+
+    def ws(names):
+        return [(mods[n].packed, mods[n].state) for n in names]
+
+    linear_forward_group(acts["x_attn"], ws(("q", "k", "v")))
+    mods["o"].forward_local(acts["x_o"])
+    linear_forward_group(acts["x_mlp"], ws(("gate", "up")))
+    mods["down"].forward_local(acts["x_down"])
+    linear_backward_dx(acts["dy_down"], mods["down"].packed, mods["down"].state)
+    linear_backward_dx_group([acts["dy_gate"], acts["dy_up"]], ws(("gate", "up")))
+    linear_backward_dx(acts["dy_o"], mods["o"].packed, mods["o"].state)
+    linear_backward_dx_group([acts["dy_q"], acts["dy_k"], acts["dy_v"]], ws(("q", "k", "v")))
+
+
 def step_cpu(layer_cpu, acts_cpu):
     """The reference's path on the host (solution/nf4.py:87-102): decode W, F.linear forward;
     decode W again, matmul backward; plus the plain LoRA products. Runs the oracle's threaded
@@ -400,13 +461,21 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus, m_override=None):
+def workload_config(n_gpus, m_override=None, layout="paired"):
     if n_gpus == 1:
         return {"workload": "Qwen2.5-1.5B decoder layer: 7 NF4 (double-quant) projections, "
                             "forward + backward, LoRA r=16 on q and v",
                 "tokens": m_override or 2048, "layers_rotated": N_LAYERS,
                 "l2": "each step touches ~290 MB of activations and the next of 28 layers' "
                       "weights (676 MB in rotation): larger than the 126 MB L2, no flush needed"}
+    if layout == "paired":
+        return {"workload": "Qwen2.5-7B-shaped decoder layer: 7 NF4 projections, forward + backward; "
+                            "q/k/v/gate/up sharded along output features, o/down along input "
+                            "features (they consume the others' shards), four NCCL all-reduces of "
+                            "[tokens, hidden] per step, nothing gathered",
+                "tokens": m_override or 8192, "parallelism": f"tp{n_gpus} (paired row / column shards)",
+                "layers_rotated": 4,
+                "l2": "each step touches > 1 GB of activations per GPU: larger than L2"}
     return {"workload": "Qwen2.5-7B-shaped decoder layer: 7 NF4 projections, forward + backward, "
                         "weights sharded along output features, NCCL all-gather of outputs and "
                         "all-reduce of input gradients",
@@ -775,7 +844,7 @@ def run_multi(args):
     import torch.distributed as dist
 
     from hackaton_b200 import _lib
-    from hackaton_b200.sharded import ShardedNF4Linear
+    from hackaton_b200.sharded import InputShardedNF4Linear, ShardedNF4Linear
 
     rank = int(os.environ["RANK"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -794,16 +863,20 @@ def run_multi(args):
     shapes, m = SHAPES_7B, 8192
     pk = peaks()
     n_rot = 4
+    paired = args.layout == "paired"
     layers = []
     for i in range(n_rot):
-        raw = make_layer(shapes, seed=i, device=device, world=world, rank=rank)
-        layers.append({name: ShardedNF4Linear(e["packed"], e["state"], shapes[name][0])
+        raw = make_layer(shapes, seed=i, device=device, world=world, rank=rank, paired=paired)
+        layers.append({name: (InputShardedNF4Linear(e["packed"], e["state"], shapes[name][1])
+                              if paired and name in INPUT_SHARDED
+                              else ShardedNF4Linear(e["packed"], e["state"], shapes[name][0]))
                        for name, e in raw.items()})
-    acts = make_activations(shapes, m, device, world=world)
+    acts = make_activations(shapes, m, device, world=world, paired=paired)
     flops = step_flops(shapes, m, lora=False)
+    step_fn = step_paired if paired else step_sharded
 
     def run(i):
-        step_sharded(layers[i % n_rot], acts)
+        step_fn(layers[i % n_rot], acts)
 
     for i in range(args.warmup):
         run(i)
@@ -821,6 +894,9 @@ def run_multi(args):
     # local GEMMs alone (no collectives), to separate kernel time from transfer time
     def run_local(i):
         mods = layers[i % n_rot]
+        if paired:
+            step_paired_local(mods, acts)
+            return
         for name in ORDER:
             mods[name].forward_local(acts[INPUT_OF[name]])
         from hackaton_b200.nf4 import linear_backward_dx
@@ -836,7 +912,7 @@ def run_multi(args):
     local_ms = float(t.item())
 
     # end to end: every step's inputs come from pinned host memory, a scalar goes back
-    host = make_activations(shapes, m, device, pinned=True, world=world)
+    host = make_activations(shapes, m, device, pinned=True, world=world, paired=paired)
     dev_in = {k: torch.empty_like(v, device=device) for k, v in host.items()}
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     metric_host = torch.empty((), dtype=torch.float32).pin_memory()
@@ -844,7 +920,7 @@ def run_multi(args):
     def run_e2e(i):
         for key, src in host.items():
             dev_in[key].copy_(src, non_blocking=True)
-        outs = step_sharded(layers[i % n_rot], dev_in)
+        outs = step_fn(layers[i % n_rot], dev_in)
         metric_host.copy_(outs[-1].float().mean(), non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
@@ -858,14 +934,18 @@ def run_multi(args):
 
     if rank == 0:
         value = flops * args.steps / (total_ms * 1e-3) / 1e12
-        gathered = 2.0 * m * sum(n for n, _ in shapes.values())
-        reduced = 2.0 * m * sum(k for _, k in shapes.values())
+        if paired:   # four all-reduces of [m, hidden]: o and down outputs, the two summed dX
+            gathered = 0.0
+            reduced = 2.0 * m * (shapes["o"][0] + shapes["down"][0] + shapes["gate"][1] + shapes["q"][1])
+        else:
+            gathered = 2.0 * m * sum(n for n, _ in shapes.values())
+            reduced = 2.0 * m * sum(k for _, k in shapes.values())
         line = {
             "metric": "fused NF4 dequant-GEMM TFLOP/s (fwd+bwd)", "value": value,
             "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": workload_config(world),
+            "config": workload_config(world, layout=args.layout),
             "frac_of_tensor_peak": value / (pk["tflops_burst"] * world),
             "frac_of_sustained_tensor_peak": value / (pk["tflops_sustained"] * world),
             "gemm_only_ms_per_step": local_ms,
@@ -882,7 +962,7 @@ def run_multi(args):
             "e2e": {"value": flops * e2e_steps / e2e_wall / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,
                     "steps": e2e_steps, "ms_per_step": e2e_wall / e2e_steps * 1e3},
-            "gpu_launches": 14 * args.steps, "clocks": clocks,
+            "gpu_launches": (8 if paired else 14) * args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     dist.barrier()
@@ -898,6 +978,10 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--comm-sms", type=int, default=0,
                     help="multi-GPU: SMs kept free of the GEMM grids for NCCL kernels")
+    ap.add_argument("--layout", default="paired", choices=["paired", "gathered"],
+                    help="multi-GPU: paired = o/down sharded along input features (four all-reduces "
+                         "per step); gathered = every weight sharded along output features "
+                         "(all-gather of outputs, all-reduce of dX)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
