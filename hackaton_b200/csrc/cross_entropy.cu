@@ -7,7 +7,7 @@
 //     written over the logits themselves (every element is read before it is replaced).
 // One CTA of 256 threads per row (a row of Qwen2.5's 151,936 logits is 297 KB), 16-byte loads.
 // A thread rescales its running sums once per 8 logits (when their maximum beats the running
-// one), not once per logit. HBM bound: 2 bytes per logit for the statistics, 4 for the gradient.
+// one), not once per logit, and works in the base-2 domain (one FMA + one ex2 per logit). HBM bound: 2 bytes per logit for the statistics, 4 for the gradient.
 #include <cuda_fp16.h>
 
 #include "kernels.h"
@@ -18,21 +18,34 @@ namespace nf4 {
 constexpr int CE_THREADS = 256;
 constexpr float CE_NEG = -1.0e30f;  // finite "minus infinity", as in the reference (kernels.py:36)
 
-// Running statistics of the logits seen so far: maximum m, s = sum exp(x - m),
-// d = sum exp(x - m) * (x - m) (taken relative to m, so that the entropy log(s) - d / s does not
-// come out of the difference of two numbers as large as the logits), first index of the maximum.
+// Running statistics of the logits seen so far, kept in the base-2 domain so that a logit costs
+// one fused multiply-add and one ex2: maximum m (and m2 = m * log2(e)), s = sum 2^(t) with
+// t = x * log2(e) - m2, d = sum 2^(t) * t (relative to the maximum, so that the entropy
+// ln(s) - d / (s * log2(e)) does not come out of the difference of two numbers as large as the
+// logits), first index of the maximum.
 struct CeState {
-    float m, s, d;
+    float m, m2, s, d;
     int idx;
 };
 
+constexpr float CE_LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2f(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ CeState ce_merge(const CeState& a, const CeState& b) {
     CeState r;
+    const bool a_wins = a.m > b.m || (a.m == b.m && a.idx <= b.idx);
     r.m = fmaxf(a.m, b.m);
-    const float fa = __expf(a.m - r.m), fb = __expf(b.m - r.m);
+    r.m2 = fmaxf(a.m2, b.m2);
+    const float ta = a.m2 - r.m2, tb = b.m2 - r.m2;  // <= 0
+    const float fa = ex2f(ta), fb = ex2f(tb);
     r.s = a.s * fa + b.s * fb;
-    r.d = fa * (a.d + a.s * (a.m - r.m)) + fb * (b.d + b.s * (b.m - r.m));
-    r.idx = a.m > b.m ? a.idx : (b.m > a.m ? b.idx : min(a.idx, b.idx));
+    r.d = fa * (a.d + a.s * ta) + fb * (b.d + b.s * tb);
+    r.idx = a.m == b.m ? min(a.idx, b.idx) : (a_wins ? a.idx : b.idx);
     return r;
 }
 
@@ -68,7 +81,7 @@ ce_stats_kernel(const CeArgs a) {
     const long long row = blockIdx.x;
     const void* base = F32 ? static_cast<const void*>(static_cast<const float*>(a.logits) + row * a.vocab)
                            : static_cast<const void*>(static_cast<const __half*>(a.logits) + row * a.vocab);
-    CeState st = {CE_NEG, 0.f, 0.f, 0};
+    CeState st = {CE_NEG, CE_NEG * CE_LOG2E, 0.f, 0.f, 0};
     const bool vec = a.vec != 0;
     const long long n8 = vec ? a.vocab / 8 : 0;
 #pragma unroll 4
@@ -83,36 +96,43 @@ ce_stats_kernel(const CeArgs a) {
 #pragma unroll
             for (int e = 6; e >= 0; --e)
                 if (x[e] == lm) li = e;
-            const float r = __expf(st.m - lm);
-            st.d = r * (st.d + st.s * (st.m - lm));
+            const float lm2 = lm * CE_LOG2E, t = st.m2 - lm2;
+            const float r = ex2f(t);
+            st.d = r * (st.d + st.s * t);
             st.s *= r;
             st.m = lm;
+            st.m2 = lm2;
             st.idx = (int)(v * 8) + li;
         }
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            const float w = __expf(x[e] - st.m);
+            const float t = fmaf(x[e], CE_LOG2E, -st.m2);
+            const float w = ex2f(t);
             st.s += w;
-            st.d = fmaf(w, x[e] - st.m, st.d);
+            st.d = fmaf(w, t, st.d);
         }
     }
     for (long long i = n8 * 8 + threadIdx.x; i < a.vocab; i += CE_THREADS) {
         const float x = ce_load1<F32>(base, i);
         if (x > st.m) {
-            const float r = __expf(st.m - x);
-            st.d = r * (st.d + st.s * (st.m - x));
+            const float x2 = x * CE_LOG2E, t = st.m2 - x2;
+            const float r = ex2f(t);
+            st.d = r * (st.d + st.s * t);
             st.s *= r;
             st.m = x;
+            st.m2 = x2;
             st.idx = (int)i;
         }
-        const float w = __expf(x - st.m);
+        const float t = fmaf(x, CE_LOG2E, -st.m2);
+        const float w = ex2f(t);
         st.s += w;
-        st.d = fmaf(w, x - st.m, st.d);
+        st.d = fmaf(w, t, st.d);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         CeState other;
         other.m = __shfl_xor_sync(0xffffffffu, st.m, o);
+        other.m2 = __shfl_xor_sync(0xffffffffu, st.m2, o);
         other.s = __shfl_xor_sync(0xffffffffu, st.s, o);
         other.d = __shfl_xor_sync(0xffffffffu, st.d, o);
         other.idx = __shfl_xor_sync(0xffffffffu, st.idx, o);
@@ -125,11 +145,12 @@ ce_stats_kernel(const CeArgs a) {
         for (int w = 1; w < CE_THREADS / 32; ++w) t = ce_merge(t, part[w]);
         const long long target = a.targets[row];
         const bool valid = target >= 0;
-        const float lse = t.m + logf(t.s);
+        const float ln_s = logf(t.s);
+        const float lse = t.m + ln_s;
         const float picked = ce_load1<F32>(base, target > 0 ? target : 0);
         a.lse[row] = valid ? lse : 0.f;
         a.loss[row] = valid ? lse - picked : 0.f;
-        if (a.entropy != nullptr) a.entropy[row] = logf(t.s) - t.d / t.s;  // = lse - E[x]
+        if (a.entropy != nullptr) a.entropy[row] = ln_s - t.d / (t.s * CE_LOG2E);  // = lse - E[x]
         if (a.argmax != nullptr) a.argmax[row] = t.idx;
     }
 }
