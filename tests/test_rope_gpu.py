@@ -113,3 +113,34 @@ def test_qkv_rotate_matches_transformers(cuda_lib, lengths, seq, padded):
     for mine, theirs in zip(out, o):
         torch.testing.assert_close(mine.detach().cpu().float(), theirs.float(), rtol=1e-3, atol=1e-3)
     cuda_lib.device_status()
+
+
+@pytest.mark.parametrize("heads,kv_heads", [(12, 2), (28, 4), (4, 2), (6, 2)])   # 6, 7, 2 and 3 copies
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_backward_heads_of_128_vs_oracle(cuda_lib, heads, kv_heads, dtype):
+    """Packed layout, heads of 128 (the model's head size), several copy counts, both projection
+    types: the backward against the oracle on the same gradients."""
+    from hackaton_b200.rope import qkv_rotate
+
+    g = torch.Generator().manual_seed(heads * 10 + kv_heads)
+    lengths, seq, dim = [9, 4, 7], 9, 128
+    b_idx = torch.tensor([b for b, n in enumerate(lengths) for _ in range(n)], dtype=torch.int32)
+    t_idx = torch.tensor([t for n in lengths for t in range(n)], dtype=torch.int32)
+    n = b_idx.numel()
+    q = torch.randn(n, heads * dim, generator=g).to(dtype)
+    k = torch.randn(n, kv_heads * dim, generator=g).to(dtype)
+    v = torch.randn(n, kv_heads * dim, generator=g).to(dtype)
+    ang = torch.arange(seq).float()[:, None] * (1.0 / (1e6 ** (torch.arange(0, dim, 2).float() / dim)))[None]
+    cos = torch.cat((ang, ang), -1).cos()[None].contiguous()
+    sin = torch.cat((ang, ang), -1).sin()[None].contiguous()
+    grads = [torch.randn(n, heads, dim, generator=g).half() for _ in range(3)]
+    qg, kg, vg = (t.cuda().requires_grad_() for t in (q, k, v))
+    outs = qkv_rotate(qg, kg, vg, cos.cuda(), sin.cuda(), b_idx.cuda(), t_idx.cuda(), len(lengths), seq,
+                      heads, kv_heads)
+    torch.autograd.backward(outs, [x.cuda() for x in grads])
+    want = nf4_oracle.qkv_rotate_bwd(*grads, cos, sin, b_idx, t_idx, heads, kv_heads, False, dtype)
+    tol = dict(rtol=2e-3, atol=2e-3) if dtype == torch.float16 else dict(rtol=1e-5, atol=1e-5)
+    for got, ref in zip((qg.grad, kg.grad, vg.grad), want):
+        assert got.dtype == dtype
+        torch.testing.assert_close(got.cpu().float(), ref.float(), **tol)
+    cuda_lib.device_status()
