@@ -16,4 +16,9 @@ Parity status
   peft==0.20.0; neither is vendored nor installed. The oracle restates their published
   arithmetic: `code2[u8] * absmax2[i // 256]`, then `+ offset`, two separately rounded fp32 ops;
   `y = base(x) + (x Aᵀ Bᵀ) * (alpha / r)`.
+* SwiGLU (solution/kernels.py:39-57), RMSNorm in its four modes (solution/rmsnorm.py:17-49), the
+  q/k/v rotation with grouped-query expansion (solution/attention.py:36-146) and the
+  cross-entropy statistics / gradient (solution/kernels.py:106-165): pinned against the
+  reference's own kernels run on CPU under the Triton interpreter (tests/golden/make_golden_*.py,
+  vectors committed beside the scripts).
 """

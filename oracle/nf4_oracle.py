@@ -2,7 +2,10 @@
 
 Every function names the reference lines it follows. Parity status is stated in the package
 docstring (oracle/__init__.py): the flat decode and the linear are pinned by golden vectors made
-with the reference's own code; the nested-absmax decode and LoRA are "parity unpinned".
+with the reference's own code; the nested-absmax decode and LoRA are "parity unpinned". The
+steps either side of the projections (SwiGLU, RMSNorm, q/k/v rotation + grouped-query expansion,
+cross-entropy) are restated at the end of this file and pinned the same way, by golden vectors of
+the reference's own kernels (tests/golden/make_golden_*.py).
 
 Byte and nibble layout (solution/nf4.py:7-14, 33-44): flat element i of the row-major weight sits
 in byte i // 2; the even element is the HIGH nibble, the odd one the LOW nibble; `blocksize`
