@@ -983,12 +983,21 @@ def main():
                          "per step); gathered = every weight sharded along output features "
                          "(all-gather of outputs, all-reduce of dX)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--multi-gpu-workload", action="store_true",
+                    help="with --gpus 1: run the N > 1 workload (7B shapes, 8192 tokens) on one GPU, "
+                         "the base of the strong-scaling numbers")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world > 1:
+    if world == 1 and args.gpus == 1 and args.multi_gpu_workload:
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29577")
+        run_multi(args)
+    elif world > 1:
         run_multi(args)
     else:
         if args.gpus != 1:
