@@ -49,7 +49,7 @@ __device__ __forceinline__ void store4_any(void* base, long long idx4, int half,
 }
 
 template <int NV>
-__global__ void __launch_bounds__(RN_WARPS * 32)
+__global__ void __launch_bounds__(RN_WARPS * 32, NV <= 16 ? 2 : 1)
 rmsnorm_rows_kernel(const RmsNormArgs a) {
     grid_dep_wait();
     grid_dep_launch();
@@ -85,10 +85,39 @@ rmsnorm_rows_kernel(const RmsNormArgs a) {
         }
         if (lane == 0) a.rstd[row] = rstd;
     } else {
-        // the row of dy is read twice (the second time out of L1 / L2): keeping g = dy * w next to
-        // xhat would need 2 * NV float4 registers per thread
         const float rstd = a.rstd[row];
         float dot = 0.f;
+        if (a.y_half && NV <= 16) {
+            // fp16 dy of a narrow row stays in registers (2 per 4 elements) next to xhat
+            uint2 dyr[NV];
+#pragma unroll
+            for (int i = 0; i < NV; ++i) dyr[i] = __ldg(reinterpret_cast<const uint2*>(a.dy) + base4 + i * 32 + lane);
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const float4 w = __ldg(reinterpret_cast<const float4*>(a.w) + i * 32 + lane);
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&dyr[i].x));
+                const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&dyr[i].y));
+                x[i].x *= rstd; x[i].y *= rstd; x[i].z *= rstd; x[i].w *= rstd;  // xhat
+                dot += lo.x * w.x * x[i].x + lo.y * w.y * x[i].y + hi.x * w.z * x[i].z + hi.y * w.w * x[i].w;
+            }
+            const float mean_gx = warp_sum(dot) * inv_h;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const float4 w = __ldg(reinterpret_cast<const float4*>(a.w) + i * 32 + lane);
+                const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&dyr[i].x));
+                const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&dyr[i].y));
+                float4 dx = make_float4(rstd * (lo.x * w.x - x[i].x * mean_gx), rstd * (lo.y * w.y - x[i].y * mean_gx),
+                                        rstd * (hi.x * w.z - x[i].z * mean_gx), rstd * (hi.y * w.w - x[i].w * mean_gx));
+                if (a.mode == 3) {
+                    const float4 t = __ldg(reinterpret_cast<const float4*>(a.d_total) + base4 + i * 32 + lane);
+                    dx.x += t.x; dx.y += t.y; dx.z += t.z; dx.w += t.w;
+                }
+                reinterpret_cast<float4*>(a.dx)[base4 + i * 32 + lane] = dx;
+            }
+            return;
+        }
+        // otherwise the row of dy is read twice (the second time out of L1 / L2): keeping it next
+        // to xhat would need up to 2 * NV float4 registers per thread
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const float4 w = __ldg(reinterpret_cast<const float4*>(a.w) + i * 32 + lane);
