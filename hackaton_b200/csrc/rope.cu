@@ -71,7 +71,7 @@ __device__ __forceinline__ F8 fma8(const F8& a, const F8& b, const F8& c, const 
 constexpr int ROPE_MAX_REP = 4;  // copies whose loads are issued together in the backward
 
 template <bool F32, bool BACKWARD>
-__global__ void __launch_bounds__(256, BACKWARD ? 3 : 4)
+__global__ void __launch_bounds__(256, 4)
 qkv_rotate_kernel(const RopeArgs a) {
     grid_dep_wait();
     grid_dep_launch();
