@@ -17,7 +17,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libnf4b200.so"
-SOURCES = ["capi.cu", "cross_entropy.cu", "dequant.cu", "gemm.cu", "gemv.cu", "lora.cu", "rmsnorm.cu", "rope.cu", "static_scratch.cu", "swiglu.cu"]
+SOURCES = ["capi.cu", "cross_entropy.cu", "dequant.cu", "gemm.cu", "gemv.cu", "lora.cu", "rmsnorm.cu", "rope.cu", "selftest.cu", "static_scratch.cu", "swiglu.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

@@ -220,8 +220,27 @@ int nf4b200_device_status(int* status_out) {
     if (rc != NF4B200_OK) return rc;
     cudaError_t e = nf4::read_and_clear_device_status(status_out);
     if (e != cudaSuccess) return fail(NF4B200_ECUDA, "device status: %s", cudaGetErrorString(e));
-    if (*status_out != 0)
-        return fail(NF4B200_EDEVICE, "a kernel gave up a bounded wait (status %d)", *status_out);
+    if (*status_out != 0) {
+        const int st = *status_out;
+        const char* what = st == nf4::STATUS_CE_TARGET_RANGE
+                               ? "cross-entropy saw a target index beyond the vocabulary; the row was treated as ignored"
+                           : st == nf4::STATUS_SCALE_RANGE
+                               ? "a block scale is outside fp16's normal range; the fused GEMM cannot represent it"
+                           : st == nf4::STATUS_SELFTEST_WAIT ? "the self-test kernel's bounded wait ran out"
+                                                             : "a kernel gave up a bounded wait";
+        return fail(NF4B200_EDEVICE, "%s (status %d)", what, st);
+    }
+    return NF4B200_OK;
+}
+
+int nf4b200_selftest_wait(int64_t limit_ns, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (limit_ns <= 0 || limit_ns > 1000000000ll)
+        return fail(NF4B200_EINVAL, "selftest_wait: limit of %lld ns (allowed: 1 ns .. 1 s)", (long long)limit_ns);
+    cudaError_t e = nf4::launch_selftest_wait((unsigned long long)limit_ns, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(NF4B200_ECUDA, "selftest_wait launch: %s", cudaGetErrorString(e));
     return NF4B200_OK;
 }
 
@@ -687,6 +706,7 @@ int nf4b200_ce_stats(const void* logits, int logits_dtype, const void* targets, 
     a.lse = static_cast<float*>(lse); a.loss = static_cast<float*>(loss);
     a.entropy = static_cast<float*>(entropy); a.argmax = static_cast<long long*>(argmax);
     a.rows = rows; a.vocab = vocab; a.f32 = logits_dtype == NF4B200_F32 ? 1 : 0;
+    a.status = nf4::device_status_word();
     cudaError_t e = nf4::launch_ce(a, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(NF4B200_ECUDA, "ce_stats: %s", cudaGetErrorString(e));
     return NF4B200_OK;
@@ -708,6 +728,7 @@ int nf4b200_ce_grad(const void* logits, int logits_dtype, const void* targets, c
     a.lse = const_cast<float*>(static_cast<const float*>(lse));
     a.scale = static_cast<const float*>(scale); a.grad = grad;
     a.rows = rows; a.vocab = vocab; a.f32 = logits_dtype == NF4B200_F32 ? 1 : 0;
+    a.status = nf4::device_status_word();
     cudaError_t e = nf4::launch_ce(a, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(NF4B200_ECUDA, "ce_grad: %s", cudaGetErrorString(e));
     return NF4B200_OK;

@@ -143,11 +143,14 @@ ce_stats_kernel(const CeArgs a) {
     if (threadIdx.x == 0) {
         CeState t = part[0];
         for (int w = 1; w < CE_THREADS / 32; ++w) t = ce_merge(t, part[w]);
+        // A target beyond the vocabulary (a tokenizer / padding mismatch) is treated like an
+        // ignored row, its logit is never read, and the device status word records it.
         const long long target = a.targets[row];
-        const bool valid = target >= 0;
+        const bool valid = target >= 0 && target < a.vocab;
+        if (target >= a.vocab && a.status != nullptr) atomicCAS(a.status, 0, STATUS_CE_TARGET_RANGE);
         const float ln_s = logf(t.s);
         const float lse = t.m + ln_s;
-        const float picked = ce_load1<F32>(base, target > 0 ? target : 0);
+        const float picked = ce_load1<F32>(base, valid ? target : 0);
         a.lse[row] = valid ? lse : 0.f;
         a.loss[row] = valid ? lse - picked : 0.f;
         if (a.entropy != nullptr) a.entropy[row] = ln_s - t.d / (t.s * CE_LOG2E);  // = lse - E[x]
@@ -163,7 +166,9 @@ ce_grad_kernel(const CeArgs a) {
     const long long row = blockIdx.x;
     const long long target = a.targets[row];
     const float lse = a.lse[row];
-    const bool valid = target >= 0;  // other rows get exact zeros (their lse is 0: exp may overflow)
+    // ignored rows and rows whose target lies beyond the vocabulary get exact zeros (their lse
+    // is 0: exp may overflow)
+    const bool valid = target >= 0 && target < a.vocab;
     const float scale = *a.scale;
     const void* base = F32 ? static_cast<const void*>(static_cast<const float*>(a.logits) + row * a.vocab)
                            : static_cast<const void*>(static_cast<const __half*>(a.logits) + row * a.vocab);

@@ -147,9 +147,10 @@ __global__ void __launch_bounds__(256)
 prepare_scales_kernel(const void* __restrict__ absmax, const float* __restrict__ code2,
                       const float* __restrict__ absmax2, const float* __restrict__ offset,
                       long long n_rows, long long bpr, int nested, int nested_blocksize,
-                      __half* __restrict__ out) {
+                      __half* __restrict__ out, int* status) {
     grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
     grid_dep_launch();
+    bool out_of_range = false;
     const long long total = n_rows * bpr;
     const float off = nested ? __ldg(offset) : 0.f;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -162,8 +163,14 @@ prepare_scales_kernel(const void* __restrict__ absmax, const float* __restrict__
                               __ldg(absmax2 + blk / nested_blocksize), off);
         else
             sc = __ldg(static_cast<const float*>(absmax) + blk);
-        out[i] = __float2half_rn(sc);
+        const __half h = __float2half_rn(sc);
+        out[i] = h;
+        // The fused GEMM multiplies in fp16: a scale that rounds to inf, to zero or into the
+        // subnormals loses the block there (the standalone decode multiplies in fp32 and is fine).
+        const float back = fabsf(__half2float(h));
+        if (sc != 0.f && (back > 65504.f || back < 6.103515625e-5f)) out_of_range = true;
     }
+    if (out_of_range && status != nullptr) atomicCAS(status, 0, STATUS_SCALE_RANGE);
 }
 
 cudaError_t launch_prepare_scales(const void* absmax, const float* code2, const float* absmax2,
@@ -176,7 +183,8 @@ cudaError_t launch_prepare_scales(const void* absmax, const float* code2, const 
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return launch_pdl(prepare_scales_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, absmax,
-                      code2, absmax2, offset, n_rows, bpr, nested, nested_blocksize, out);
+                      code2, absmax2, offset, n_rows, bpr, nested, nested_blocksize, out,
+                      device_status_word());
 }
 
 }  // namespace nf4

@@ -122,6 +122,9 @@ struct GemmParams {
     __half* sw_dup;
     long long ld_sw;
     int debug;               // NF4B200_DEBUG; the kernel looks at it only in -DNF4B200_TRACE builds
+#ifdef NF4B200_DUMP
+    uint32_t* dump;          // tuning aid: what each decoding thread read from the code ring
+#endif
 };
 
 struct GemmMaps {
@@ -816,12 +819,29 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                             cw[0] = q.x; cw[1] = q.y;
                         }
                     }
+#ifdef NF4B200_DUMP
+                    if (p.dump != nullptr && CG == 1 && it < 16) {
+                        uint32_t* d = p.dump + ((size_t)(blockIdx.x * 16 + it) * DECODE_THREADS + pt) * 8;
+                        d[0] = cw[0]; d[1] = cw[1]; d[2] = cw[WORDS - 2]; d[3] = cw[WORDS - 1];
+                        d[4] = *reinterpret_cast<const uint32_t*>(&scale2);
+                        d[5] = 0x80000000u | (uint32_t)(w.kb_begin + it);
+                    }
+#endif
+#ifdef NF4B200_EARLY_HANDBACK
+#if NF4B200_EARLY_HANDBACK == 2
+                    fence_proxy_async_smem();
+#endif
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_empty_c(c));
+                    if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
+#else
                     if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
                     // The code-ring slot goes back only now, with the operand slot in hand. Handing
                     // it back before that wait gave intermittently wrong weight rows in the
                     // single-CTA kernel (first calls on a new weight, M <= 128).
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_empty_c(c));
+#endif
                     if (pt == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(7, it); }
                     if (!NF4_TUNE(1)) {
 #pragma unroll
@@ -1241,14 +1261,36 @@ bool pdl_enabled() {
     return on != 0;
 }
 
+// Tuning switches (NF4B200_DEBUG bits, NF4B200_PLAN = "nacc,splits") exist only in
+// -DNF4B200_TRACE builds and are read from the environment once; a normal build has neither.
+#ifdef NF4B200_TRACE
 static int debug_flags() {
-    static int flags = -1;
-    if (flags < 0) {
+    static const int flags = [] {
         const char* e = std::getenv("NF4B200_DEBUG");
-        flags = e ? std::atoi(e) : 0;
-    }
+        return e ? std::atoi(e) : 0;
+    }();
     return flags;
 }
+
+struct ForcedPlan { int nacc, splits; };
+static ForcedPlan forced_plan() {
+    static const ForcedPlan fp = [] {
+        ForcedPlan r = {0, 0};
+        if (const char* e = std::getenv("NF4B200_PLAN")) {
+            int a = 0, b = 0;
+            if (std::sscanf(e, "%d,%d", &a, &b) == 2) { r.nacc = a; r.splits = b; }
+        }
+        return r;
+    }();
+    return fp;
+}
+#else
+static constexpr int debug_flags() { return 0; }
+#endif
+
+#ifdef NF4B200_DUMP
+static uint32_t* g_dump = nullptr;
+#endif
 
 // Tiling and split-K plan shared by the launcher and the workspace-size query.
 GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long k_w, bool trans_w,
@@ -1257,16 +1299,17 @@ GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long
     if (m <= 128)      { pl.cg = 1; pl.nacc = 1; }
     else if (m <= 256) { pl.cg = 2; pl.nacc = 1; }
     else               { pl.cg = 2; pl.nacc = 2; }
-    if ((debug_flags() & 16) && m > 128 && count == 1) { pl.cg = 1; pl.nacc = 2; }  // tuning
     int force_splits = 0;
-    if (const char* e = std::getenv("NF4B200_PLAN")) {  // tuning: "nacc,splits" for pair tiles
-        int a = 0, b = 0;
-        if (std::sscanf(e, "%d,%d", &a, &b) == 2 && m > 128) {
-            if (a == 1 || a == 2) { pl.cg = 2; pl.nacc = a; }
-            force_splits = b;
-        }
+    bool forced = false;
+#ifdef NF4B200_TRACE
+    if ((debug_flags() & 16) && m > 128 && count == 1) { pl.cg = 1; pl.nacc = 2; forced = true; }
+    const ForcedPlan fp = forced_plan();
+    if ((fp.nacc != 0 || fp.splits != 0) && m > 128) {
+        if (fp.nacc == 1 || fp.nacc == 2) { pl.cg = 2; pl.nacc = fp.nacc; }
+        force_splits = fp.splits;
+        forced = true;
     }
-    bool forced = (debug_flags() & 16) != 0 || std::getenv("NF4B200_PLAN") != nullptr;
+#endif
     int n_tiles = 0, nkb = 0;
     size_t ws_floats = 0;
     for (int i = 0; i < count; ++i) {
@@ -1411,6 +1454,9 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
     p.splits = pl.splits;
     p.kb_per_split = pl.kb_per_split;
     p.debug = debug_flags();
+#ifdef NF4B200_DUMP
+    p.dump = g_dump;
+#endif
     if (p.splits > 1) {
         if (a0.workspace == nullptr || a0.workspace_bytes < pl.ws_bytes) {
             p.splits = 1;  // no scratch given: one unit per tile walks the whole K range
@@ -1594,6 +1640,10 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why
 }
 
 }  // namespace nf4
+
+#ifdef NF4B200_DUMP
+extern "C" void nf4dbg_set_dump(void* ptr) { nf4::g_dump = static_cast<uint32_t*>(ptr); }
+#endif
 
 #ifdef NF4B200_TRACE
 // Tuning aid, not part of the public ABI: copies the phase timestamps to the host.

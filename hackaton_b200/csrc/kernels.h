@@ -194,6 +194,7 @@ struct CeArgs {
     long long rows, vocab;
     int f32;
     int vec;                     // set by the launcher
+    int* status;                 // device status word (a target beyond the vocabulary is recorded there)
 };
 cudaError_t launch_ce(const CeArgs& a, cudaStream_t stream);
 
@@ -239,8 +240,16 @@ cudaError_t launch_lora_grad_batch(const LoraGradBatch& b, cudaStream_t stream);
 // Records a message for nf4b200_last_error() on this thread and returns `code`.
 int set_error(int code, const char* fmt, ...);
 
-// Device-side status word: 0, or a code written by a kernel whose bounded wait ran out.
+// Device-side status word: 0, or the first code a kernel recorded since it was last read:
+//   100 + role   a bounded wait of the fused GEMM ran out (role = which wait)
+//   200          cross-entropy: a target index beyond the vocabulary (row treated as ignored)
+//   300          scale table: a block scale outside fp16's normal range (inf, subnormal or zero)
+//   400          the self-test kernel's bounded wait ran out (what nf4b200_selftest_wait asks for)
+constexpr int STATUS_CE_TARGET_RANGE = 200;
+constexpr int STATUS_SCALE_RANGE = 300;
+constexpr int STATUS_SELFTEST_WAIT = 400;
 int* device_status_word();   // device address of the word for the current device
+cudaError_t launch_selftest_wait(unsigned long long limit_ns, cudaStream_t stream);  // selftest.cu
 cudaError_t read_and_clear_device_status(int* out);
 
 }  // namespace nf4

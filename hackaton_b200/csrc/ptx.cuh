@@ -63,7 +63,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 
 // Bounded wait. `abort_flag` lives in shared memory; any role that times out sets it, and every
 // other waiting role sees it within a few polls and gives up too.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns = WAIT_TIMEOUT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long t0 = 0;
     uint32_t polls = 0;
@@ -73,7 +74,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             unsigned long long now = globaltimer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > WAIT_TIMEOUT_NS) {
+            } else if (now - t0 > limit_ns) {
                 *abort_flag = 1;
                 return false;
             }

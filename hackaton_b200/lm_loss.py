@@ -1,9 +1,8 @@
-"""Cross-entropy straight from the lm_head's logits, and lm_head + loss in chunks of rows.
+"""Cross-entropy straight from the lm_head's logits, and lm_head + loss over row chunks.
 
-Mirrors the reference's `ce_stats` / `ce_grad` / `fused_cross_entropy` (solution/kernels.py:173-238)
-and `linear_cross_entropy` (solution/lm_loss.py:27-62): the statistics pass and the gradient pass
-are this library's kernels; the two matmuls of a chunk are plain fp16 GEMMs on an unquantised
-weight (the tied embedding table), i.e. library calls, as in the reference.
+Same surface as the reference's `ce_stats` / `ce_grad` / `fused_cross_entropy`
+(solution/kernels.py:173-238) and `linear_cross_entropy` (solution/lm_loss.py:27-67). The
+statistics pass and the gradient pass are this library's kernels (csrc/cross_entropy.cu).
 """
 
 from __future__ import annotations
@@ -11,10 +10,11 @@ from __future__ import annotations
 import torch
 
 from . import _lib
+from ._autograd import call
 from .nf4 import _stream_ptr
 
-CHUNK_ROWS = 256      # solution/lm_loss.py:27
-GRAD_SCALE = 1024.0   # solution/lm_loss.py:28
+CHUNK_ROWS = 256      # rows of logits alive at a time (solution/lm_loss.py:27)
+GRAD_SCALE = 1024.0   # the chunk gradients are kept in fp16 at this scale (solution/lm_loss.py:28)
 
 
 def _dtype_code(logits):
@@ -27,100 +27,103 @@ def _dtype_code(logits):
     raise TypeError(f"hackaton_b200: logits must be fp16 or fp32, got {logits.dtype}")
 
 
-def ce_grad(logits, targets, lse, scale, grad):
-    """grad = scale * (softmax(logits) - onehot(targets)) per row, 0 for rows with target < 0;
-    `grad` may be `logits` itself (solution/kernels.py:173-179)."""
-    rows, vocab = logits.shape
-    with torch.cuda.device(logits.device):
-        _lib.check(_lib.lib().nf4b200_ce_grad(
-            logits.data_ptr(), _dtype_code(logits), targets.data_ptr(), lse.data_ptr(), scale.data_ptr(),
-            grad.data_ptr(), rows, vocab, _stream_ptr(logits.device)))
+def _opt_ptr(t):
+    return None if t is None else t.data_ptr()
 
 
 def ce_stats(logits, targets, want_entropy, out=None):
     """Per-row logsumexp, loss (0 for rows with target < 0) and, if asked, entropy of (rows,
-    vocab) logits. `out` = (lse, loss, entropy, argmax) buffers to fill, argmax included
-    (solution/kernels.py:182-204)."""
+    vocab) logits. `out` = (lse, loss, entropy, argmax) buffers to fill instead of new ones;
+    the argmax is only written there (solution/kernels.py:182-204)."""
     rows, vocab = logits.shape
     if targets.dtype != torch.int64:
         raise TypeError("hackaton_b200: targets must be int64")
-    if out is not None:
-        lse, loss, entropy, argmax = out
-    else:
-        lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
-        loss = torch.empty_like(lse)
-        entropy = torch.empty_like(lse) if want_entropy else None
-        argmax = None
+    if out is None:
+        fresh = lambda: torch.empty(rows, dtype=torch.float32, device=logits.device)  # noqa: E731
+        out = (fresh(), fresh(), fresh() if want_entropy else None, None)
+    lse, loss, entropy, argmax = out
     with torch.cuda.device(logits.device):
         _lib.check(_lib.lib().nf4b200_ce_stats(
-            logits.data_ptr(), _dtype_code(logits), targets.data_ptr(), lse.data_ptr(), loss.data_ptr(),
-            None if entropy is None else entropy.data_ptr(),
-            None if argmax is None else argmax.data_ptr(), rows, vocab, _stream_ptr(logits.device)))
+            logits.data_ptr(), _dtype_code(logits), targets.data_ptr(), lse.data_ptr(),
+            loss.data_ptr(), _opt_ptr(entropy), _opt_ptr(argmax), rows, vocab,
+            _stream_ptr(logits.device)))
     return lse, loss, entropy
 
 
-class FusedCrossEntropy(torch.autograd.Function):
-    """sum over rows of (logsumexp - logit[target]) / denom, rows with target < 0 ignored
-    (solution/kernels.py:207-231)."""
+def ce_grad(logits, targets, lse, scale, grad):
+    """grad = scale * (softmax(logits) - onehot(targets)) per row, 0 for rows with target < 0;
+    `scale` is one fp32 number on the device; `grad` may be `logits` itself
+    (solution/kernels.py:173-179)."""
+    rows, vocab = logits.shape
+    with torch.cuda.device(logits.device):
+        _lib.check(_lib.lib().nf4b200_ce_grad(
+            logits.data_ptr(), _dtype_code(logits), targets.data_ptr(), lse.data_ptr(),
+            scale.data_ptr(), grad.data_ptr(), rows, vocab, _stream_ptr(logits.device)))
 
-    @staticmethod
-    def forward(ctx, logits, targets, denom, inplace_grad):
-        lse, losses, _ = ce_stats(logits, targets, False)
-        ctx.save_for_backward(logits, targets, lse, denom)
-        ctx.inplace_grad = inplace_grad
-        return losses.sum() / denom
 
-    @staticmethod
-    def backward(ctx, grad_output):
-        logits, targets, lse, denom = ctx.saved_tensors
-        scale = (grad_output / denom).to(torch.float32).reshape(1)
-        grad = logits if ctx.inplace_grad else torch.empty_like(logits)
-        ce_grad(logits, targets, lse, scale, grad)
-        return grad, None, None, None
+class _LossFromLogits:
+    """sum over rows of (logsumexp - logit[target]) / denom; the gradient may overwrite the
+    logits."""
+
+    def __init__(self, overwrite_logits):
+        self.overwrite_logits = overwrite_logits
+
+    def run(self, keep, logits, targets, denom):
+        lse, per_row, _ = ce_stats(logits, targets, False)
+        keep(logits, targets, lse, denom)
+        return per_row.sum() / denom
+
+    def grad(self, kept, upstream):
+        logits, targets, lse, denom = kept.tensors
+        d_logits = logits if self.overwrite_logits else torch.empty_like(logits)
+        ce_grad(logits, targets, lse, (upstream / denom).float().reshape(1), d_logits)
+        return d_logits, None, None
 
 
 def fused_cross_entropy(logits, targets, denom, inplace_grad=False):
-    """solution/kernels.py:234-238."""
-    return FusedCrossEntropy.apply(logits.contiguous(), targets, denom, inplace_grad)
+    """Mean-style loss of (rows, vocab) logits, rows with target < 0 ignored
+    (solution/kernels.py:207-238)."""
+    return call(_LossFromLogits(bool(inplace_grad)), logits.contiguous(), targets, denom)
 
 
-def _chunks(hidden, weight, targets, lse, losses, entropy, argmax, unit, grad_hidden):
-    rows = hidden.shape[0]
-    for start in range(0, rows, CHUNK_ROWS):
-        part = slice(start, min(start + CHUNK_ROWS, rows))
-        logits = torch.nn.functional.linear(hidden[part], weight)
-        ce_stats(logits, targets[part], True, out=(lse[part], losses[part], entropy[part], argmax[part]))
-        ce_grad(logits, targets[part], lse[part], unit, logits)   # 1024 (p - onehot), in place
-        torch.mm(logits, weight, out=grad_hidden[part])
+def _head_chunk(hidden_rows, weight):
+    """Logits of one chunk of rows: hidden_rows . weightᵀ, fp16 in and out."""
+    return torch.nn.functional.linear(hidden_rows, weight)
 
 
-class LinearCrossEntropy(torch.autograd.Function):
-    """lm_head and the loss without the (tokens, vocab) logits (solution/lm_loss.py:45-62): the
-    gradient with respect to `hidden` is formed in the forward, chunk by chunk, and scaled in the
-    backward; the weight is frozen."""
+class _HeadAndLoss:
+    """lm_head + loss without ever holding the (tokens, vocab) logits: walks the rows in chunks;
+    per chunk the logits are made, reduced to their statistics, turned in place into
+    GRAD_SCALE * (softmax - onehot) and multiplied back through the (frozen) head weight, so the
+    gradient with respect to `hidden` exists when the forward ends and the backward only rescales
+    it (solution/lm_loss.py:31-62)."""
 
-    @staticmethod
-    def forward(ctx, hidden, weight, targets, denom):
+    def run(self, keep, hidden, weight, targets, denom):
         rows, device = hidden.shape[0], hidden.device
-        lse = torch.empty(rows, dtype=torch.float32, device=device)
-        losses, entropy = torch.empty_like(lse), torch.empty_like(lse)
+        stats = {name: torch.empty(rows, dtype=torch.float32, device=device)
+                 for name in ("lse", "loss", "entropy")}
         argmax = torch.empty(rows, dtype=torch.int64, device=device)
+        d_hidden = torch.empty_like(hidden)
         unit = torch.full((1,), GRAD_SCALE, dtype=torch.float32, device=device)
-        grad_hidden = torch.empty_like(hidden)
         with torch.autocast("cuda", enabled=False):
-            _chunks(hidden, weight, targets, lse, losses, entropy, argmax, unit, grad_hidden)
-        ctx.save_for_backward(grad_hidden, denom)
-        ctx.mark_non_differentiable(losses, entropy, argmax)
-        return losses.sum() / denom, losses, entropy, argmax
+            for lo in range(0, rows, CHUNK_ROWS):
+                rs = slice(lo, min(lo + CHUNK_ROWS, rows))
+                logits = _head_chunk(hidden[rs], weight)
+                ce_stats(logits, targets[rs], True,
+                         out=(stats["lse"][rs], stats["loss"][rs], stats["entropy"][rs], argmax[rs]))
+                ce_grad(logits, targets[rs], stats["lse"][rs], unit, logits)
+                torch.mm(logits, weight, out=d_hidden[rs])
+        keep(d_hidden, denom)
+        keep.constant(stats["loss"], stats["entropy"], argmax)
+        return stats["loss"].sum() / denom, stats["loss"], stats["entropy"], argmax
 
-    @staticmethod
-    def backward(ctx, grad_output, _losses, _entropy, _argmax):
-        grad_hidden, denom = ctx.saved_tensors
-        scale = (grad_output.float() / (denom * GRAD_SCALE)).reshape(1, 1)
-        return (grad_hidden.float() * scale).to(grad_hidden.dtype), None, None, None
+    def grad(self, kept, upstream, *_unused):
+        d_hidden, denom = kept.tensors
+        factor = (upstream.float() / (denom * GRAD_SCALE)).reshape(1, 1)
+        return (d_hidden.float() * factor).to(d_hidden.dtype), None, None, None
 
 
 def linear_cross_entropy(hidden, weight, targets, denom):
-    """(loss, per-row losses, entropy, argmax) of hidden @ weight^T against `targets`
+    """(loss, per-row losses, entropy, argmax) of hidden @ weightᵀ against `targets`
     (solution/lm_loss.py:65-67)."""
-    return LinearCrossEntropy.apply(hidden.contiguous(), weight, targets, denom)
+    return call(_HeadAndLoss(), hidden.contiguous(), weight, targets, denom)

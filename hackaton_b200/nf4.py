@@ -102,15 +102,20 @@ class WeightRef:
             w.nested_blocksize = 1
         self.struct = w
         self.keep = keep
-        self.key = (packed.data_ptr(), state.absmax.data_ptr(), nested, rows, cols)
+        self.key = _content_key(packed, state)
         self.rows, self.cols = rows, cols
         self.scales16 = None
+        self._ready = None   # (event, stream) of the table's construction while it may be pending
 
     def prepare(self):
         """Builds, once, the fp16 block-scale table the fused GEMM can fetch by TMA (see
         nf4b200_prepare_scales in include/nf4b200.h) and hooks it into the descriptor. Weights
-        are frozen in QLoRA, so the table stays valid for the life of the quantisation state."""
+        are frozen in QLoRA, so the table stays valid while the state's tensors are not written
+        (`weight_ref` drops the descriptor when they are). No host synchronisation: a call on
+        another stream than the one that built the table waits for the build on the device."""
         if self.scales16 is not None or not PREPARED_SCALES:
+            if self._ready is not None:
+                self._order_after_build()
             return self
         need = int(_lib.lib().nf4b200_scales16_bytes(self.rows, self.cols))
         if need == 0 or self.struct.blocksize != 64:
@@ -121,17 +126,50 @@ class WeightRef:
             _lib.check(_lib.lib().nf4b200_prepare_scales(ctypes.byref(self.struct), table.data_ptr(),
                                                          _stream_ptr(device)))
             if not torch.cuda.is_current_stream_capturing():
-                torch.cuda.current_stream(device).synchronize()  # later calls may use other streams
+                event = torch.cuda.Event()
+                event.record()
+                self._ready = (event, torch.cuda.current_stream(device).cuda_stream)
         self.scales16 = table
         self.struct.scales16 = table.data_ptr()
         return self
 
+    def _order_after_build(self):
+        event, stream = self._ready
+        current = torch.cuda.current_stream(self.keep[0].device)
+        if not torch.cuda.is_current_stream_capturing() and event.query():
+            self._ready = None
+            return
+        if current.cuda_stream != stream:
+            current.wait_event(event)
+
+
+def _content_key(packed, state):
+    """Identity of a weight's contents: where its tensors live and how often they have been
+    written in place. Loading other weights into the same storage (`copy_`, a second checkpoint)
+    bumps the version counters, so a cached descriptor (and its scale table) is not reused."""
+    nested = bool(getattr(state, "nested", False))
+    parts = [packed.data_ptr(), packed._version, state.absmax.data_ptr(), state.absmax._version,
+             nested]
+    if nested:
+        state2 = state.state2
+        offset = state.offset
+        parts += [state2.absmax.data_ptr(), state2.absmax._version,
+                  offset._version if isinstance(offset, torch.Tensor) else float(offset)]
+    return tuple(parts)
+
+
+def prepare_weights(weights):
+    """Builds the scale tables of many weights back to back (a whole model's at load time):
+    `weights` is an iterable of (packed, state). Nothing waits on the host; returns the
+    descriptors."""
+    return [weight_ref(packed.reshape(-1), state).prepare() for packed, state in weights]
+
 
 def weight_ref(packed, state) -> WeightRef:
-    """Descriptor for (packed, state), cached on the state object while its tensors stay put."""
-    nested = bool(getattr(state, "nested", False))
+    """Descriptor for (packed, state), cached on the state object while its tensors stay put and
+    unwritten."""
     cached = getattr(state, "_nf4b200_ref", None)
-    if cached is not None and cached.key[:3] == (packed.data_ptr(), state.absmax.data_ptr(), nested):
+    if cached is not None and cached.key == _content_key(packed, state):
         return cached
     ref = WeightRef(packed, state)
     try:

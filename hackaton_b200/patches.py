@@ -36,6 +36,30 @@ def _eligible(A, state, packed, bias):
             and (bias is None or bias.dtype == A.dtype))
 
 
+def _plain_lora_adapter(module, name, state):
+    """True when adapter `name` of a peft LoRA wrapper is the plain update the fused kernel
+    computes, base(x) + scaling * B(A(dropout(x))): rank 16, no bias on either factor, A reading
+    the base layer's input features, and none of peft's variants that change the formula
+    (DoRA's magnitude vector, entries of `lora_variant`). Anything else must take peft's own
+    forward: computing plain LoRA for such an adapter would be silently wrong."""
+    if name not in getattr(module, "lora_A", {}) or name not in getattr(module, "lora_B", {}):
+        return False
+    use_dora = getattr(module, "use_dora", None)
+    if isinstance(use_dora, dict) and use_dora.get(name):
+        return False
+    for attr in ("lora_variant", "lora_magnitude_vector"):
+        table = getattr(module, attr, None)
+        if table is not None and name in table:
+            return False
+    a_mod, b_mod = module.lora_A[name], module.lora_B[name]
+    lora_a, lora_b = getattr(a_mod, "weight", None), getattr(b_mod, "weight", None)
+    if lora_a is None or lora_b is None or lora_a.dim() != 2 or lora_b.dim() != 2:
+        return False
+    return (lora_a.shape[0] == RANK and lora_b.shape[1] == RANK
+            and lora_a.shape[1] == state.shape[1] and lora_b.shape[0] == state.shape[0]
+            and getattr(a_mod, "bias", None) is None and getattr(b_mod, "bias", None) is None)
+
+
 def patch_nf4_matmul():
     """Replaces `bitsandbytes.matmul_4bit(A, B, quant_state, out=None, bias=None)` (the call every
     `Linear4bit.forward` makes) by the fused NF4 linear; see solution/patches.py:251-277."""
@@ -72,10 +96,9 @@ def lora_forward_for(original):
                 or not _eligible(x, state, weight, getattr(base, "bias", None))):
             return original(self, x, *args, **kwargs)
         name = adapters[0]
-        lora_a, lora_b = self.lora_A[name].weight, self.lora_B[name].weight
-        if lora_a.shape[0] != RANK or getattr(self.lora_A[name], "bias", None) is not None \
-                or getattr(self.lora_B[name], "bias", None) is not None:
+        if not _plain_lora_adapter(self, name, state):
             return original(self, x, *args, **kwargs)
+        lora_a, lora_b = self.lora_A[name].weight, self.lora_B[name].weight
         dropout = self.lora_dropout[name]
         x_lora = dropout(x) if (dropout.training and getattr(dropout, "p", 0.0) > 0.0) else x
         return nf4_lora_linear(x, weight, base.bias, state, lora_a, lora_b,
@@ -151,11 +174,11 @@ class SiblingGroup:
                 or len(adapters) != 1 or adapters[0] not in module.lora_A):
             return None
         name = adapters[0]
+        if not _plain_lora_adapter(module, name, state):
+            return None
         lora_a, lora_b = module.lora_A[name].weight, module.lora_B[name].weight
         dropout = module.lora_dropout[name]
-        if (lora_a.shape[0] != RANK or getattr(module.lora_A[name], "bias", None) is not None
-                or getattr(module.lora_B[name], "bias", None) is not None
-                or (getattr(dropout, "training", False) and getattr(dropout, "p", 0.0) > 0.0)):
+        if getattr(dropout, "training", False) and getattr(dropout, "p", 0.0) > 0.0:
             return None
         return Projection(weight, state, bias, lora_a, lora_b, float(module.scaling[name]))
 

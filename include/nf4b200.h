@@ -24,7 +24,7 @@ extern "C" {
 #define NF4B200_EINVAL (-1)  /* bad argument: shape, alignment, dtype, null pointer */
 #define NF4B200_EARCH (-2)   /* device is not sm_100 */
 #define NF4B200_ECUDA (-3)   /* a CUDA runtime / driver call failed */
-#define NF4B200_EDEVICE (-4) /* a kernel reported a bounded-wait timeout */
+#define NF4B200_EDEVICE (-4) /* a kernel recorded a problem in the device status word */
 
 enum { NF4B200_F16 = 0, NF4B200_BF16 = 1, NF4B200_F32 = 2 };
 
@@ -86,9 +86,23 @@ int nf4b200_prepare_scales(const nf4b200_weight* w, void* scales16, void* stream
 
 /*
  * Reads and clears the device-side status word of the current device (synchronises the device).
- * 0 = no kernel reported a timeout since the last call.
+ * 0 = no kernel reported anything since the last call. Otherwise the call returns NF4B200_EDEVICE
+ * and *status_out holds the first code recorded: 100..199 a bounded wait of the fused GEMM ran
+ * out; 200 cross-entropy met a target index beyond the vocabulary (that row was treated as
+ * ignored, nothing was read out of bounds); 300 nf4b200_prepare_scales met a block scale outside
+ * fp16's normal range (the fused GEMM multiplies table and scale in fp16 and cannot represent
+ * that block; the standalone decode can); 400 the self-test below.
  */
 int nf4b200_device_status(int* status_out);
+
+/*
+ * Self-test of the failure-reporting path: launches one small kernel that waits, with the same
+ * bounded wait the fused GEMM uses, on a barrier nothing ever signals; after limit_ns
+ * (1 ns .. 1 s) the kernel gives up, records a status and ends by itself. The next
+ * nf4b200_device_status then returns NF4B200_EDEVICE (status 400) and the context stays usable.
+ * The reference has no counterpart (its Triton kernels contain no waits).
+ */
+int nf4b200_selftest_wait(int64_t limit_ns, void* stream);
 
 /*
  * Standalone decode: out[n_rows, n_cols] = table[code] * scale, one rounding to out_dtype.
@@ -122,9 +136,13 @@ int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_
  * fixed array of NF4B200_STATIC_SCRATCH_BYTES inside the library image (each GPU that loads the
  * library holds it until the process exits); this entry point allocates nothing. Shapes that need
  * more scratch than that are refused with NF4B200_EINVAL and a message naming both sizes.
- * The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
- * that first call outside any stream capture. All calls on a device share the array: calls that
- * can overlap on the GPU would race on it. It has no counterpart in the reference.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress); with
+ * CUDA's lazy module loading that look-up is also the moment the driver places the library's
+ * device image, the array included, on that GPU, so it is the one call that can still fail for
+ * lack of memory. Make it once per device at start-up (any small shape that needs scratch will
+ * do), outside any stream capture; later calls allocate nothing. All calls on a device share the
+ * array: calls that can overlap on the GPU would race on it. It has no counterpart in the
+ * reference.
  */
 #define NF4B200_STATIC_SCRATCH_BYTES (32u << 20)
 int nf4b200_linear_fwd_static(const nf4b200_weight* w, const void* x, int64_t m, int64_t ldx,

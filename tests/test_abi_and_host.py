@@ -106,6 +106,58 @@ def test_lora_patch_falls_through_to_original():
     assert forward(module, torch.zeros(2, 64)) == "orig" and seen == [1]
 
 
+def _fake_lora_module(k=128, n=64, rank=16, **extra):
+    """A stand-in for peft's LoRA wrapper around a 4-bit linear, with the attributes the patch reads."""
+    state = types.SimpleNamespace(shape=(n, k))
+    base = types.SimpleNamespace(weight=types.SimpleNamespace(quant_state=state), bias=None)
+    mod = types.SimpleNamespace(
+        active_adapters=["default"], disable_adapters=False, merged=False, base_layer=base,
+        lora_A={"default": types.SimpleNamespace(weight=torch.zeros(rank, k), bias=None)},
+        lora_B={"default": types.SimpleNamespace(weight=torch.zeros(n, rank), bias=None)},
+        lora_dropout={"default": torch.nn.Identity()}, scaling={"default": 2.0},
+        forward=lambda x: "own")
+    for key, value in extra.items():
+        setattr(mod, key, value)
+    return mod
+
+
+@pytest.mark.parametrize("extra,fused", [
+    ({}, True),
+    ({"use_dora": {"default": True}}, False),                 # DoRA: another formula
+    ({"use_dora": {"default": False}}, True),
+    ({"lora_variant": {"default": object()}}, False),          # newer peft: any registered variant
+    ({"lora_magnitude_vector": {"default": object()}}, False),
+    ({"lora_variant": {}, "lora_magnitude_vector": {}}, True),
+])
+def test_lora_patch_leaves_adapter_variants_to_peft(monkeypatch, extra, fused):
+    """Adapters whose forward is not the plain low-rank update (DoRA, entries of `lora_variant`)
+    take peft's own forward, in the module patch and in the sibling groups alike."""
+    from hackaton_b200 import patches
+
+    monkeypatch.setattr(patches, "_eligible", lambda x, state, weight, bias: True)
+    monkeypatch.setattr(patches, "nf4_lora_linear", lambda *a, **k: "fused")
+    forward = patches.lora_forward_for(lambda self, x, *a, **k: "orig")
+    module = _fake_lora_module(**extra)
+    assert forward(module, torch.zeros(2, 128)) == ("fused" if fused else "orig")
+    proj = patches.SiblingGroup([module])._projection(module, torch.zeros(2, 128))
+    assert (proj is not None) == fused
+
+
+def test_lora_patch_checks_rank_and_feature_counts(monkeypatch):
+    from hackaton_b200 import patches
+
+    monkeypatch.setattr(patches, "_eligible", lambda x, state, weight, bias: True)
+    monkeypatch.setattr(patches, "nf4_lora_linear", lambda *a, **k: "fused")
+    forward = patches.lora_forward_for(lambda self, x, *a, **k: "orig")
+    assert forward(_fake_lora_module(rank=8), torch.zeros(2, 128)) == "orig"
+    wrong_in = _fake_lora_module()
+    wrong_in.lora_A["default"].weight = torch.zeros(16, 64)     # A does not read the base input
+    assert forward(wrong_in, torch.zeros(2, 128)) == "orig"
+    biased = _fake_lora_module()
+    biased.lora_B["default"].bias = torch.zeros(64)
+    assert forward(biased, torch.zeros(2, 128)) == "orig"
+
+
 def test_sibling_group_routes_one_launch(monkeypatch):
     """q/k/v called one after the other with the same tensor: one grouped computation, every
     module gets its own share; another tensor, or an ineligible input, starts over or falls

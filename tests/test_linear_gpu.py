@@ -52,7 +52,7 @@ def test_linear_forward_backward_vs_oracle(cuda_lib, m, n, k, nested):
 
 
 def test_config0_q_proj(cuda_lib):
-    """BASELINE config 0: W[1536,1536], X[2048,1536]."""
+    """One q_proj of the 1.5B model: W[1536,1536], X[2048,1536] (batch 4 x 512 tokens)."""
     ef, eb = run_case(2048, 1536, 1536, True, bias=False, seed=0)
     assert ef <= TOL and eb <= TOL, (ef, eb)
 
@@ -91,21 +91,44 @@ def test_leading_dims_and_strided_rows(cuda_lib):
     assert rel(y.reshape(-1, 256), nf4_oracle.linear_fwd(x[..., :128].reshape(-1, 128), w)) <= TOL
 
 
-def test_linearity_at_full_size(cuda_lib):
-    """Size-independent property at the full 8960x1536 shape with M = 2048: f(a + b) = f(a) + f(b)
-    up to fp16 rounding, and the bias gradient equals the column sums of dy."""
+def _within_reference_tolerance(got, want, contraction):
+    """The reference's own bound between its fused linear and bitsandbytes' (rtol = atol = 2e-3,
+    solution/test_nf4.py:63-64). Its two sides multiply identical fp16 weights; here the weights
+    inside the GEMM are rounded as fp16(table) * fp16(scale) and differ from the one-rounding
+    decode by up to one fp16 step, an error that grows with the square root of the contraction
+    length. Up to 1536 terms every element meets the bound; at 8960 terms 99.9 % do and none is
+    further out than twice the bound."""
+    err = (got.float() - want.float()).abs()
+    allow = 2e-3 + 2e-3 * want.float().abs()
+    if contraction <= 1536:
+        assert bool((err <= allow).all()), float((err / allow).max())
+    else:
+        assert float((err <= allow).float().mean()) >= 0.999
+        assert bool((err <= 2 * allow).all()), float((err / allow).max())
+
+
+@pytest.mark.parametrize("n,k", [(8960, 1536), (1536, 8960), (1536, 1536)])
+def test_training_shapes_at_2048_tokens_vs_oracle(cuda_lib, n, k):
+    """gate/up, down and q/o of the 1.5B layer at the full 2048 tokens, forward and backward,
+    every output element against the oracle: at the task's bound (max rel err <= 1e-2) and at the
+    reference's elementwise 2e-3; the bias gradient equals the column sums of dy."""
     from hackaton_b200 import nf4_linear
 
-    packed, state = synthetic_weight(8960, 1536, True, seed=3, device="cuda")
-    g = torch.Generator(device="cuda").manual_seed(1)
-    a = torch.randn(2048, 1536, generator=g, device="cuda").half()
-    b = torch.randn(2048, 1536, generator=g, device="cuda").half()
-    ya, yb, yab = (nf4_linear(t, packed, None, state).float() for t in (a, b, (a + b)))
-    assert float((yab - ya - yb).abs().max() / yab.abs().max()) <= TOL
-    bias = torch.zeros(8960, device="cuda", dtype=torch.float16, requires_grad=True)
-    dy = torch.randn(2048, 8960, generator=g, device="cuda").half()
-    nf4_linear(a, packed, bias, state).backward(dy)
-    torch.testing.assert_close(bias.grad.float(), dy.float().sum(0), rtol=2e-2, atol=2e-1)
+    packed, state = synthetic_weight(n, k, True, seed=3 + n, device="cuda")
+    w = oracle_weight(packed, state)
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(2048, k, generator=g).half()
+    dy = torch.randn(2048, n, generator=g).half()
+    bias = torch.zeros(n, device="cuda", dtype=torch.float16, requires_grad=True)
+    xg = x.cuda().requires_grad_()
+    y = nf4_linear(xg, packed, bias, state)
+    y.backward(dy.cuda())
+    y_ref, dx_ref = nf4_oracle.linear_fwd(x, w), nf4_oracle.linear_bwd(dy, w)
+    assert rel(y, y_ref) <= TOL and rel(xg.grad, dx_ref) <= TOL
+    _within_reference_tolerance(y.detach().cpu(), y_ref, k)
+    _within_reference_tolerance(xg.grad.cpu(), dx_ref, n)
+    torch.testing.assert_close(bias.grad.float().cpu(), dy.float().sum(0), rtol=2e-2, atol=2e-1)
+    assert cuda_lib.device_status() == 0
 
 
 def test_bad_arguments_raise(cuda_lib):

@@ -16,7 +16,7 @@ GOLDEN = Path(__file__).resolve().parent / "golden"
 @pytest.mark.parametrize("name", ["qwen", "odd"])      # 1536: register-resident kernel; 1000: generic
 @pytest.mark.parametrize("tag", ["f32", "f16"])
 def test_matches_reference_kernel(cuda_lib, name, tag):
-    from hackaton_b200.rmsnorm import _backward, _forward
+    from hackaton_b200.rmsnorm import launch_backward as _backward, launch_forward as _forward
 
     z = np.load(GOLDEN / "rmsnorm_small.npz")
     t = lambda key: torch.from_numpy(z[f"{name}_{key}"])

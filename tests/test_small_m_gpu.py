@@ -1,5 +1,5 @@
-"""GPU: the weight-streaming forward kernel that serves M <= 64 (the decode shapes of
-BASELINE.json's config 3: M in {1, 4, 16, 64}) against the oracle, with bias and the LoRA term, and
+"""GPU: the weight-streaming forward kernel that serves M <= 64 (decode-like token counts,
+M in {1, 4, 16, 64}) against the oracle, with bias and the LoRA term, and
 against the tensor-core kernel it replaces at these sizes."""
 
 import pytest
@@ -62,12 +62,12 @@ def test_small_m_matches_tensor_core_kernel(cuda_lib):
     assert (outs[0] - outs[1]).abs().max() <= 2e-3 * outs[1].abs().max()
 
 
-def test_fresh_weights_repeatable(cuda_lib):
+def test_fresh_weights_first_calls_vs_reference(cuda_lib):
     """First calls on freshly created weights (cold caches, scale table just built), M <= 128 with
-    split-K: two calls in a row must give the same bits, for several weights in a row. Guards the
-    hand-back order of the code ring (a slot released before the operand slot was obtained gave
-    intermittently wrong weight rows in the single-CTA kernel)."""
-    from hackaton_b200.nf4 import linear_forward
+    split-K, several weights in a row: each of two calls in a row is compared with the fp32
+    product of the bit-exact standalone decode (itself pinned to the oracle), the first weight of
+    every token count also with the CPU oracle, and the two calls must give the same bits."""
+    from hackaton_b200.nf4 import dequantize_nf4, linear_forward
 
     n, k = 1536, 8960
     for rep in range(6):
@@ -76,5 +76,15 @@ def test_fresh_weights_repeatable(cuda_lib):
             x = torch.randn(m, k, device="cuda").half()
             y1 = linear_forward(x, packed, None, state)
             y2 = linear_forward(x, packed, None, state)
+            w_dev = dequantize_nf4(packed, state)
+            want = x.float() @ w_dev.float().t()
+            scale = float(want.abs().max())
+            for call, y in enumerate((y1, y2)):
+                err = float((y.float() - want).abs().max()) / scale
+                assert err <= 2e-3, (rep, m, call, err)
             assert torch.equal(y1, y2), (rep, m)
-    cuda_lib.device_status()
+            if rep == 0:
+                w = oracle_weight(packed, state)
+                assert torch.equal(w_dev.cpu(), w)
+                assert nf4_oracle.max_rel_err(y1.cpu(), nf4_oracle.linear_fwd(x.cpu(), w)) <= TOL
+    assert cuda_lib.device_status() == 0

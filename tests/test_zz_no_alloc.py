@@ -1,5 +1,6 @@
 """GPU: the allocation-free forward entry point (`nf4b200_linear_fwd_static`) against the regular
-one (`nf4b200_linear_fwd` with a caller-owned workspace), through the C ABI.
+one (`nf4b200_linear_fwd` with a caller-owned workspace) and against the CPU oracle, through the
+C ABI.
 
 Who needs it: callers that cannot give the library device memory, for example a server whose
 memory pool is fully assigned at start-up or a plug-in that may not allocate inside its host's
@@ -13,23 +14,29 @@ import ctypes
 import pytest
 import torch
 
-from tests.util import synthetic_weight
+from oracle import nf4_oracle
+from tests.util import oracle_weight, synthetic_weight
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-2
 
 
-def _call(lib_mod, fn_name, ref, x, y, workspace=None):
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _call(lib_mod, fn_name, ref, x, y, workspace=None, bias=None, xa=None, lora_b=None):
     lib = lib_mod.lib()
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     if fn_name == "static":
         rc = lib.nf4b200_linear_fwd_static(ctypes.byref(ref.struct), x.data_ptr(), x.shape[0],
-                                           x.stride(0), None, None, None, y.data_ptr(),
-                                           y.stride(0), stream)
+                                           x.stride(0), _ptr(bias), _ptr(xa), _ptr(lora_b),
+                                           y.data_ptr(), y.stride(0), stream)
     else:
         rc = lib.nf4b200_linear_fwd(ctypes.byref(ref.struct), x.data_ptr(), x.shape[0],
-                                    x.stride(0), None, None, None, y.data_ptr(), y.stride(0),
-                                    workspace.data_ptr(), workspace.numel(), stream)
+                                    x.stride(0), _ptr(bias), _ptr(xa), _ptr(lora_b), y.data_ptr(),
+                                    y.stride(0), _ptr(workspace),
+                                    0 if workspace is None else workspace.numel(), stream)
     lib_mod.check(rc)
 
 
@@ -42,6 +49,7 @@ def test_static_scratch_forward_matches_regular_entry_point(cuda_lib):
     need = cuda_lib.lib().nf4b200_workspace_bytes(n, k, m, 0)
     assert 0 < need <= cuda_lib.STATIC_SCRATCH_BYTES
     workspace = torch.empty(need, dtype=torch.uint8, device="cuda")
+    w = oracle_weight(packed, state)
     g = torch.Generator(device="cuda").manual_seed(5)
     for call in range(2):                # two calls in a row share the built-in array
         x = torch.randn(m, k, generator=g, device="cuda").half()
@@ -50,9 +58,42 @@ def test_static_scratch_forward_matches_regular_entry_point(cuda_lib):
         _call(cuda_lib, "regular", ref, x, want, workspace)
         _call(cuda_lib, "static", ref, x, got)
         torch.cuda.synchronize()
-        err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
-        assert err <= TOL, f"call {call}: max rel err {err}"
+        err = nf4_oracle.max_rel_err(got.cpu(), nf4_oracle.linear_fwd(x.cpu(), w))
+        assert err <= TOL, f"call {call}: max rel err against the oracle {err}"
         assert torch.equal(got, want), f"call {call}: same kernels, same slice order"
+    assert cuda_lib.device_status() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 1536, 1536),     # a few token rows: the weight-streaming kernel
+                                   (300, 512, 1536),     # split-K scratch in use, bias and LoRA on
+                                   (2048, 8960, 1536)])  # enough tiles: no scratch at all
+def test_static_scratch_allocates_nothing_and_matches_the_oracle(cuda_lib, m, n, k):
+    """Bias and the rank-16 term through the allocation-free entry point, for a shape of each
+    route, against the oracle; after one warm-up call (which loads the library's device image
+    with its built-in array) a call changes neither the free device memory nor torch's own
+    allocation count."""
+    from hackaton_b200.nf4 import weight_ref
+
+    packed, state = synthetic_weight(n, k, True, seed=23 + m, device="cuda")
+    ref = weight_ref(packed.reshape(-1), state).prepare()
+    w = oracle_weight(packed, state)
+    g = torch.Generator().manual_seed(6)
+    x = torch.randn(m, k, generator=g).half()
+    bias = torch.randn(n, generator=g).half()
+    a = ((torch.rand(16, k, generator=g) * 2 - 1) / k ** 0.5).half()
+    b = (torch.randn(n, 16, generator=g) * 0.1).half()
+    xa = (2.0 * (x.float() @ a.float().t())).half()          # scaling * x . A^T, as the kernel takes it
+    x_d, bias_d, xa_d, b_d = (t.cuda() for t in (x, bias, xa, b))
+    y = torch.empty(m, n, dtype=torch.float16, device="cuda")
+    _call(cuda_lib, "static", ref, x_d, y, bias=bias_d, xa=xa_d, lora_b=b_d)   # warm-up
+    torch.cuda.synchronize()
+    free0, used0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+    y.fill_(float("nan"))
+    _call(cuda_lib, "static", ref, x_d, y, bias=bias_d, xa=xa_d, lora_b=b_d)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0 and torch.cuda.memory_allocated() == used0
+    want = (x.float() @ w.float().t() + bias.float() + xa.float() @ b.float().t()).half()
+    assert nf4_oracle.max_rel_err(y.cpu(), want) <= TOL
     assert cuda_lib.device_status() == 0
 
 
