@@ -77,6 +77,19 @@ def peaks():
             "source": "fallback"}
 
 
+def measured_traffic(kernel_key):
+    """DRAM bytes per launch of a kernel as an ncu capture counted them (dram__bytes_read.sum +
+    dram__bytes_write.sum), from the tracked summary profiles/dram_traffic.json; None when the
+    file has no entry for the kernel."""
+    path = ROOT / "profiles" / "dram_traffic.json"
+    if path.exists():
+        entry = json.loads(path.read_text()).get(kernel_key)
+        if entry:
+            return {"bytes_per_launch": entry["read_bytes"] + entry["write_bytes"],
+                    "source": entry["capture"]}
+    return {"bytes_per_launch": None, "source": "no capture on record"}
+
+
 # ------------------------------------------------------------------------------------------------
 # clocks
 # ------------------------------------------------------------------------------------------------
@@ -157,8 +170,10 @@ def make_layer(shapes, seed, device, world=1, rank=0, paired=False):
         w = (torch.randn(n_local, k, generator=g, device=device) * 0.02).half()
         packed, state = quantize_nf4(w, blocksize=64, compress_statistics=True)
         entry = {"packed": packed.reshape(-1), "state": state, "n": n_local, "k": k}
-        if name in LORA_ON and world == 1:
-            entry["A"] = ((torch.rand(RANK_LORA, k, generator=g, device=device) * 2 - 1)
+        if name in LORA_ON:
+            # A is replicated (same seed on every rank), B follows the rank's rows of W
+            ga = torch.Generator(device=device).manual_seed(seed * 100 + i * 10 + 7)
+            entry["A"] = ((torch.rand(RANK_LORA, k, generator=ga, device=device) * 2 - 1)
                           / k ** 0.5).half()
             entry["B"] = (torch.randn(n_local, RANK_LORA, generator=g, device=device) * 0.01).half()
         layer[name] = entry
@@ -243,6 +258,26 @@ def step_functional(layer, acts):
     return outs
 
 
+def layer_forward(layer, acts):
+    """Forward of the seven projections (no LoRA), grouped as in step_functional."""
+    from hackaton_b200.group import linear_forward_group
+
+    outs = []
+    for group in GROUPS:
+        outs += linear_forward_group(acts[INPUT_OF[group[0]]],
+                                     [(layer[n]["packed"], layer[n]["state"]) for n in group])
+    return outs
+
+
+def layer_backward(layer, acts):
+    """dX of the seven projections (no LoRA), grouped as in step_functional."""
+    from hackaton_b200.group import linear_backward_dx_group
+
+    return [linear_backward_dx_group([acts["dy_" + n] for n in group],
+                                     [(layer[n]["packed"], layer[n]["state"]) for n in group])
+            for group in reversed(GROUPS)]
+
+
 def kernels_per_step(shapes, m):
     """Kernels of this library that one step launches: a fused GEMM per group and direction, one
     split-K reduction per output wherever the library's plan slices the contraction (it does when
@@ -289,15 +324,37 @@ def step_autograd(layer, acts_dev):
 
 
 def step_sharded(layer_mods, acts):
-    """N > 1: every projection's local GEMM followed by its collective, issued asynchronously so
-    the transfer of one projection overlaps the GEMM of the next."""
-    works, outs = [], []
+    """N > 1, gathered layout: every projection's local GEMM followed by its collective (all-gather
+    of the output shards, all-reduce of the partial dX), issued asynchronously so the transfer of
+    one projection overlaps the GEMM of the next. LoRA on q and v as in step_paired."""
+    from hackaton_b200.sharded import backward_dx_group, forward_local_group, lora_weight_grads
+
+    works, outs, xas = [], [], {}
     for name in ORDER:
-        out, work = layer_mods[name].forward(acts[INPUT_OF[name]], async_op=True)
+        mod = layer_mods[name]
+        if mod.lora_a is not None:
+            (y,), (xa,) = forward_local_group([mod], acts[INPUT_OF[name]], return_lora_inputs=True)
+            xas[name] = xa
+            flat = torch.empty((mod.world * y.shape[0], y.shape[1]), dtype=y.dtype, device=y.device)
+            work = None
+            if mod.world > 1:
+                work = torch.distributed.all_gather_into_tensor(flat, y, group=mod.group, async_op=True)
+            out = flat
+        else:
+            out, work = mod.forward(acts[INPUT_OF[name]], async_op=True)
         outs.append(out)
         works.append(work)
     for name in reversed(ORDER):
-        dx, work = layer_mods[name].backward_dx(acts["dy_" + name], async_op=True)
+        mod = layer_mods[name]
+        if mod.lora_a is not None:
+            dx, work, (u,) = backward_dx_group([mod], [acts["dy_" + name]], async_op=True,
+                                               return_lora_inputs=True)
+            wg, ww = lora_weight_grads([mod], acts[INPUT_OF[name]], [acts["dy_" + name]],
+                                       [xas[name]], [u], async_op=True)
+            outs += list(wg[0])
+            works += ww
+        else:
+            dx, work = mod.backward_dx(acts["dy_" + name], async_op=True)
         outs.append(dx)
         works.append(work)
     for w in works:
@@ -306,35 +363,45 @@ def step_sharded(layer_mods, acts):
     return outs
 
 
-def step_paired(mods, acts):
+def step_paired(mods, acts, results=None):
     """N > 1, paired layout: q/k/v and gate/up hold rows of W and keep their output shards (what
     follows them works per head / per column), o and down hold columns of W and take those shards
-    as input. Four all-reduces of [M, hidden] per step, each issued asynchronously so that it
-    runs under the next GEMM; nothing is gathered."""
-    from hackaton_b200.sharded import backward_dx_group, forward_local_group
+    as input. Four all-reduces of [M, hidden] per step (plus the [16, K] gradients of the replicated
+    LoRA factors), each issued asynchronously so that it runs under the next GEMM; nothing is
+    gathered. LoRA r=16 on q and v: A replicated, B split with W. `results`, if a dict, receives
+    the named outputs (for verification)."""
+    from hackaton_b200.sharded import backward_dx_group, forward_local_group, lora_weight_grads
 
     works, outs = [], []
-    outs += forward_local_group([mods[n] for n in ("q", "k", "v")], acts["x_attn"])
-    y, work = mods["o"].forward(acts["x_o"], async_op=True)
-    outs.append(y)
+    res = {} if results is None else results
+    qkv = [mods[n] for n in ("q", "k", "v")]
+    ys, xas = forward_local_group(qkv, acts["x_attn"], return_lora_inputs=True)
+    res.update(zip(("y_q", "y_k", "y_v"), ys))
+    outs += ys
+    res["y_o"], work = mods["o"].forward(acts["x_o"], async_op=True)
     works.append(work)
-    outs += forward_local_group([mods[n] for n in ("gate", "up")], acts["x_mlp"])
-    y, work = mods["down"].forward(acts["x_down"], async_op=True)
-    outs.append(y)
+    gu = forward_local_group([mods[n] for n in ("gate", "up")], acts["x_mlp"])
+    res.update(zip(("y_gate", "y_up"), gu))
+    outs += gu
+    res["y_down"], work = mods["down"].forward(acts["x_down"], async_op=True)
     works.append(work)
-    outs.append(mods["down"].backward_dx(acts["dy_down"])[0])
-    dx, work = backward_dx_group([mods[n] for n in ("gate", "up")],
-                                 [acts["dy_gate"], acts["dy_up"]], async_op=True)
-    outs.append(dx)
+    res["dx_down"] = mods["down"].backward_dx(acts["dy_down"])[0]
+    res["dx_mlp"], work = backward_dx_group([mods[n] for n in ("gate", "up")],
+                                            [acts["dy_gate"], acts["dy_up"]], async_op=True)
     works.append(work)
-    outs.append(mods["o"].backward_dx(acts["dy_o"])[0])
-    dx, work = backward_dx_group([mods[n] for n in ("q", "k", "v")],
-                                 [acts["dy_q"], acts["dy_k"], acts["dy_v"]], async_op=True)
-    outs.append(dx)
+    res["dx_o"] = mods["o"].backward_dx(acts["dy_o"])[0]
+    grads = [acts["dy_q"], acts["dy_k"], acts["dy_v"]]
+    res["dx_attn"], work, us = backward_dx_group(qkv, grads, async_op=True, return_lora_inputs=True)
     works.append(work)
+    wg, ww = lora_weight_grads(qkv, acts["x_attn"], grads, xas, us, async_op=True)
+    works += ww
+    for i, name in ((0, "q"), (2, "v")):
+        if i in wg:
+            res["dA_" + name], res["dB_" + name] = wg[i]
     for w in works:
         if w is not None:
             w.wait()
+    outs += [v for k, v in res.items() if k not in ("y_q", "y_k", "y_v", "y_gate", "y_up")]
     return outs
 
 
@@ -346,14 +413,29 @@ def step_paired_local(mods, acts):
     def ws(names):
         return [(mods[n].packed, mods[n].state) for n in names]
 
-    linear_forward_group(acts["x_attn"], ws(("q", "k", "v")))
+    from hackaton_b200.lora import lora_down_batch, lora_grad_batch
+    lora_on = [n for n in ("q", "k", "v") if mods[n].lora_a is not None]
+    xas = dict(zip(lora_on, lora_down_batch([acts["x_attn"]] * len(lora_on), [mods[n].lora_a for n in lora_on],
+                                            True, [mods[n].scaling for n in lora_on]))) if lora_on else {}
+    linear_forward_group(acts["x_attn"], ws(("q", "k", "v")), None, [xas.get(n) for n in ("q", "k", "v")],
+                         [mods[n].lora_b for n in ("q", "k", "v")])
     mods["o"].forward_local(acts["x_o"])
     linear_forward_group(acts["x_mlp"], ws(("gate", "up")))
     mods["down"].forward_local(acts["x_down"])
     linear_backward_dx(acts["dy_down"], mods["down"].packed, mods["down"].state)
     linear_backward_dx_group([acts["dy_gate"], acts["dy_up"]], ws(("gate", "up")))
     linear_backward_dx(acts["dy_o"], mods["o"].packed, mods["o"].state)
-    linear_backward_dx_group([acts["dy_q"], acts["dy_k"], acts["dy_v"]], ws(("q", "k", "v")))
+    us = dict(zip(lora_on, lora_down_batch([acts["dy_" + n] for n in lora_on], [mods[n].lora_b for n in lora_on],
+                                           False, [mods[n].scaling for n in lora_on]))) if lora_on else {}
+    linear_backward_dx_group([acts["dy_q"], acts["dy_k"], acts["dy_v"]], ws(("q", "k", "v")),
+                             [us.get(n) for n in ("q", "k", "v")], [mods[n].lora_a for n in ("q", "k", "v")])
+    if lora_on:
+        zs, ss, rms = [], [], []
+        for n in lora_on:
+            zs += [acts["x_attn"], acts["dy_" + n]]
+            ss += [us[n], xas[n]]
+            rms += [True, False]
+        lora_grad_batch(zs, ss, rms)
 
 
 def step_cpu(layer_cpu, acts_cpu):
@@ -461,15 +543,16 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus, m_override=None, layout="paired"):
-    if n_gpus == 1:
+def workload_config(n_gpus, m_override=None, layout="paired", multi_gpu_workload=False):
+    if n_gpus == 1 and not multi_gpu_workload:
         return {"workload": "Qwen2.5-1.5B decoder layer: 7 NF4 (double-quant) projections, "
                             "forward + backward, LoRA r=16 on q and v",
                 "tokens": m_override or 2048, "layers_rotated": N_LAYERS,
                 "l2": "each step touches ~290 MB of activations and the next of 28 layers' "
                       "weights (676 MB in rotation): larger than the 126 MB L2, no flush needed"}
     if layout == "paired":
-        return {"workload": "Qwen2.5-7B-shaped decoder layer: 7 NF4 projections, forward + backward; "
+        return {"workload": "Qwen2.5-7B-shaped decoder layer: 7 NF4 projections, forward + backward, "
+                            "LoRA r=16 on q and v (A replicated, B sharded with W); "
                             "q/k/v/gate/up sharded along output features, o/down along input "
                             "features (they consume the others' shards), four NCCL all-reduces of "
                             "[tokens, hidden] per step, nothing gathered",
@@ -477,6 +560,7 @@ def workload_config(n_gpus, m_override=None, layout="paired"):
                 "layers_rotated": 4,
                 "l2": "each step touches > 1 GB of activations per GPU: larger than L2"}
     return {"workload": "Qwen2.5-7B-shaped decoder layer: 7 NF4 projections, forward + backward, "
+                        "LoRA r=16 on q and v, "
                         "weights sharded along output features, NCCL all-gather of outputs and "
                         "all-reduce of input gradients",
             "tokens": m_override or 8192, "parallelism": f"tp{n_gpus} (column shards)",
@@ -736,6 +820,62 @@ def run_single(args):
         ce[key] = {"us": us, "gbs": gbs, "frac_of_hbm": gbs / pk["hbm_gbs"], "bytes_per_element": bytes_per_elem}
     del ce_logits, ce_grad_out
 
+    # ---- standalone decode (codes + two-level scales -> fp16 weights), HBM bound:
+    # 0.515869 B read + 2 B written per weight, rotating over the 28 layers' weights
+    from hackaton_b200.nf4 import dequantize_nf4
+    dq = {"bytes_per_weight": BYTES_PER_WEIGHT + 2.0, "hbm_peak_gbs": pk["hbm_gbs"]}
+    for key, name in (("gate_8960x1536", "gate"), ("q_1536x1536", "q")):
+        us = time_kernel(lambda i: dequantize_nf4(layers[i % N_LAYERS][name]["packed"],
+                                                  layers[i % N_LAYERS][name]["state"])) * 1e3
+        n_w = shapes[name][0] * shapes[name][1]
+        gbs = n_w * dq["bytes_per_weight"] / (us * 1e-6) / 1e9
+        dq[key] = {"us": us, "gbs": gbs, "frac_of_hbm": gbs / pk["hbm_gbs"],
+                   "traffic": measured_traffic("nf4_dequant_kernel " + key)["bytes_per_launch"]}
+
+    # ---- weight-bound regime: a few token rows against every projection of the 28-layer stack
+    # (676 MB of packed weights per pass, so the weights come from HBM, not from L2)
+    layer_weights = sum(n * k for n, k in shapes.values())
+    small = {"hbm_peak_gbs": pk["hbm_gbs"], "layers": N_LAYERS,
+             "weight_bytes_per_layer": BYTES_PER_WEIGHT * layer_weights}
+    for m_small in (1, 4, 16, 64):
+        a_small = make_activations(shapes, m_small, device)
+        act_bytes = 2.0 * m_small * sum(n + k for n, k in shapes.values())
+        entry = {}
+        for direction, fn in (("fwd", layer_forward), ("bwd", layer_backward)):
+            us = time_kernel(lambda i: fn(layers[i % N_LAYERS], a_small)) * 1e3
+            entry[direction] = {
+                "us_per_layer": us,
+                "weight_gbs": small["weight_bytes_per_layer"] / (us * 1e-6) / 1e9,
+                "frac_of_hbm": (small["weight_bytes_per_layer"] + act_bytes) / (us * 1e-6) / 1e9 / pk["hbm_gbs"]}
+        small[f"m{m_small}"] = entry
+
+    # ---- packed variable-length batch: four sequences with lengths ~U[32, 512], M = sum of them
+    gl = torch.Generator().manual_seed(4321)
+    lengths = [int(v) for v in torch.randint(32, 513, (4,), generator=gl)]
+    m_var = sum(lengths)
+    a_var = make_activations(shapes, m_var, device)
+    var_ms = time_kernel(lambda i: step_functional(layers[i % N_LAYERS], a_var))
+    varlen = {"lengths": lengths, "tokens": m_var, "ms_per_step": var_ms,
+              "tflops": step_flops(shapes, m_var) / (var_ms * 1e-3) / 1e12}
+    varlen["frac_of_tensor_peak"] = varlen["tflops"] / pk["tflops_burst"]
+
+    # ---- the whole step under the board's power limit: the step graphs replayed back to back for
+    # about three seconds, the last third timed with the clocks sampled
+    step_sustained = None
+    if use_graphs:
+        per = total_ms / args.steps
+        n_rep = max(N_LAYERS, int(1000.0 / per))
+        smp = ClockSampler(0)
+        smp.start()
+        for i in range(2 * n_rep):
+            graphs[i % N_LAYERS][0].replay()
+        tot, _, _ = timed_steps(lambda i: graphs[i % N_LAYERS][0].replay(), n_rep)
+        sv = flops * n_rep / (tot * 1e-3) / 1e12
+        step_sustained = {"value": sv, "unit": "TFLOP/s", "ms_per_step": tot / n_rep,
+                          "frac_of_sustained_tensor_peak": sv / pk["tflops_sustained"],
+                          "clocks": smp.stop(), "timing": "~3 s of back-to-back steps, last third timed"}
+
+    traffic = measured_traffic("nf4_gemm_kernel gate_proj forward M=2048")
     gemm_flops = 2.0 * m * 8960 * 1536
     achieved = gemm_flops / (kern["gate_fwd"] * 1e-3) / 1e12
     # The kernel is timed alone in bursts of a few milliseconds, at full clocks: the denominator is
@@ -744,10 +884,10 @@ def run_single(args):
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": pk["tflops_burst"], "unit": "TFLOP/s",
         "frac": achieved / pk["tflops_burst"],
-        # dram__bytes_read.sum + dram__bytes_write.sum of one gate_proj forward launch in an ncu
-        # capture of this benchmark (13.67 MB + 0.13 MB; the algorithmic input is 13.82 MB: codes,
-        # fp16 scale table and X)
-        "traffic": 13.80e6, "traffic_unit": "bytes per launch, from an ncu capture of this command",
+        # dram__bytes_read.sum + dram__bytes_write.sum of one gate_proj forward launch, read from
+        # the tracked summary of the ncu capture (profiles/dram_traffic.json names the capture)
+        "traffic": traffic["bytes_per_launch"], "traffic_unit": "bytes per launch",
+        "traffic_source": traffic["source"],
         "kernel": "nf4_gemm_kernel<CG=2,NACC=2,fwd> (CTA pairs, 512x256 tiles) on gate_proj (M=2048, N=8960, K=1536)",
         "peak_source": pk["source"] + " (burst cuBLAS bf16; the kernel is timed alone)",
         "timing": f"CUDA events around a graph of {reps} launches over the rotating layers"
@@ -833,7 +973,8 @@ def run_single(args):
         "frac_of_tensor_peak": value / pk["tflops_burst"],
         "frac_of_sustained_tensor_peak": value / pk["tflops_sustained"],
         "ms_per_28_layer_step": total_ms / args.steps * N_LAYERS,
-        "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs, "swiglu": sw, "rmsnorm": rn, "rope": rp, "cross_entropy": ce,
+        "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs, "dequant": dq, "small_m": small,
+        "packed_varlen": varlen, "sustained": step_sustained, "swiglu": sw, "rmsnorm": rn, "rope": rp, "cross_entropy": ce,
         "step_ms_min_med_max": [min(per_step), statistics.median(per_step), max(per_step)],
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
@@ -844,11 +985,90 @@ def run_single(args):
     print(json.dumps(line), flush=True)
 
 
+def build_sharded_layers(shapes, n_rot, device, world, rank, paired):
+    from hackaton_b200.sharded import InputShardedNF4Linear, ShardedNF4Linear
+
+    layers = []
+    for i in range(n_rot):
+        raw = make_layer(shapes, seed=i, device=device, world=world, rank=rank, paired=paired)
+        mods = {}
+        for name, e in raw.items():
+            if paired and name in INPUT_SHARDED:
+                mods[name] = InputShardedNF4Linear(e["packed"], e["state"], shapes[name][1])
+            else:
+                mods[name] = ShardedNF4Linear(e["packed"], e["state"], shapes[name][0],
+                                              lora_a=e.get("A"), lora_b=e.get("B"), scaling=SCALING)
+        layers.append(mods)
+    return layers
+
+
+def verify_paired_step(mods, acts, world, device, n_rows=24):
+    """One paired step checked against the CPU oracle on a sample of token rows, before anything is
+    timed: every rank decodes its own shards with the oracle and forms its share of each result on
+    the host; shares of all-reduced results are summed over the ranks (one small all-reduce of the
+    expected values), local results are compared on the rank. Returns the largest max-rel-err."""
+    import torch.distributed as dist
+
+    from oracle import nf4_oracle
+    from tests.util import oracle_weight
+
+    m = acts["x_attn"].shape[0]
+    rows = torch.linspace(0, m - 1, n_rows).long()
+    rows_dev = rows.to(device)
+    res = {}
+    step_paired(mods, acts, results=res)
+    torch.cuda.synchronize()
+    w = {n: oracle_weight(mods[n].packed, mods[n].state).float() for n in ORDER}
+    a = {k: v[rows_dev].float().cpu() for k, v in acts.items()}
+    lora = {n: (mods[n].lora_a.float().cpu(), mods[n].lora_b.float().cpu()) for n in ORDER
+            if getattr(mods[n], "lora_a", None) is not None}
+    worst = 0.0
+
+    def local(name, want):
+        nonlocal worst
+        worst = max(worst, nf4_oracle.max_rel_err(res[name][rows_dev].float().cpu(), want))
+
+    def summed(name, share, rows_sampled=True):
+        nonlocal worst
+        total = share.to(device)
+        if world > 1:
+            dist.all_reduce(total)
+        got = res[name][rows_dev] if rows_sampled else res[name]
+        worst = max(worst, nf4_oracle.max_rel_err(got.float().cpu(), total.cpu()))
+
+    for n in ("q", "k", "v", "gate", "up"):
+        y = a[INPUT_OF[n]] @ w[n].t()
+        if n in lora:
+            y = y + SCALING * ((a[INPUT_OF[n]] @ lora[n][0].t()).half().float() @ lora[n][1].t())
+        local("y_" + n, y)
+    summed("y_o", a["x_o"] @ w["o"].t())
+    summed("y_down", a["x_down"] @ w["down"].t())
+    local("dx_down", a["dy_down"] @ w["down"])
+    local("dx_o", a["dy_o"] @ w["o"])
+    summed("dx_mlp", a["dy_gate"] @ w["gate"] + a["dy_up"] @ w["up"])
+    dx_attn = sum(a["dy_" + n] @ w[n] for n in ("q", "k", "v"))
+    for n in lora:
+        dx_attn = dx_attn + SCALING * ((a["dy_" + n] @ lora[n][1]).half().float() @ lora[n][0])
+    summed("dx_attn", dx_attn)
+    # LoRA weight gradients are sums over all token rows: compare them in full on the device side
+    x_full = acts["x_attn"].float()
+    for n in lora:
+        dy_full = acts["dy_" + n].float()
+        a_dev, b_dev = mods[n].lora_a.float(), mods[n].lora_b.float()
+        u = (SCALING * (dy_full @ b_dev)).half().float()
+        xa = (SCALING * (x_full @ a_dev.t())).half().float()
+        summed("dA_" + n, (u.t() @ x_full).cpu(), rows_sampled=False)
+        worst = max(worst, nf4_oracle.max_rel_err(res["dB_" + n].float().cpu(), (dy_full.t() @ xa).cpu()))
+    t = torch.tensor([worst], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
 def run_multi(args):
     import torch.distributed as dist
 
     from hackaton_b200 import _lib
-    from hackaton_b200.sharded import InputShardedNF4Linear, ShardedNF4Linear
 
     rank = int(os.environ["RANK"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -868,16 +1088,23 @@ def run_multi(args):
     pk = peaks()
     n_rot = 4
     paired = args.layout == "paired"
-    layers = []
-    for i in range(n_rot):
-        raw = make_layer(shapes, seed=i, device=device, world=world, rank=rank, paired=paired)
-        layers.append({name: (InputShardedNF4Linear(e["packed"], e["state"], shapes[name][1])
-                              if paired and name in INPUT_SHARDED
-                              else ShardedNF4Linear(e["packed"], e["state"], shapes[name][0]))
-                       for name, e in raw.items()})
+    layers = build_sharded_layers(shapes, n_rot, device, world, rank, paired)
     acts = make_activations(shapes, m, device, world=world, paired=paired)
-    flops = step_flops(shapes, m, lora=False)
+    flops = step_flops(shapes, m, lora=True)
     step_fn = step_paired if paired else step_sharded
+
+    # ---- parity first: one step against the CPU oracle, outside every timed region
+    verified, verify_err = None, None
+    if paired and not args.no_verify:
+        verify_err = verify_paired_step(layers[0], acts, world, device)
+        verified = verify_err <= 1e-2
+        if not verified:
+            if rank == 0:
+                print(json.dumps({"error": "multi-GPU step differs from the oracle",
+                                  "max_rel_err": verify_err, "n_gpus": world}), flush=True)
+            dist.barrier()
+            dist.destroy_process_group()
+            raise SystemExit(1)
 
     def run(i):
         step_fn(layers[i % n_rot], acts)
@@ -891,9 +1118,13 @@ def run_multi(args):
                                         barrier=dist.barrier)
     clocks = sampler.stop() if rank == 0 else None
     _lib.device_status()
-    t = torch.tensor([total_ms], device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
+
+    def max_over_ranks(value):
+        t = torch.tensor([value], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    total_ms = max_over_ranks(total_ms)
 
     # local GEMMs alone (no collectives), to separate kernel time from transfer time
     def run_local(i):
@@ -909,55 +1140,113 @@ def run_multi(args):
 
     for i in range(3):
         run_local(i)
-    local_ms, _, _ = timed_steps(run_local, max(3, args.steps // 2), barrier=dist.barrier)
-    local_ms /= max(3, args.steps // 2)
-    t = torch.tensor([local_ms], device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    local_ms = float(t.item())
+    n_local = max(3, args.steps // 2)
+    local_ms, _, _ = timed_steps(run_local, n_local, barrier=dist.barrier)
+    local_ms = max_over_ranks(local_ms / n_local)
 
-    # end to end: every step's inputs come from pinned host memory, a scalar goes back
+    # ---- the other layout, for the record (a few steps outside the main timed region): the
+    # all-gather-of-outputs layout when the main run is paired, and the other way round
+    other_ms = None
+    if world > 1 and not args.no_other_layout:
+        other_paired = not paired
+        o_layers = build_sharded_layers(shapes, 2, device, world, rank, other_paired)
+        o_acts = make_activations(shapes, m, device, world=world, paired=other_paired)
+        o_step = step_paired if other_paired else step_sharded
+        for i in range(3):
+            o_step(o_layers[i % 2], o_acts)
+        o_ms, _, _ = timed_steps(lambda i: o_step(o_layers[i % 2], o_acts), 5, barrier=dist.barrier)
+        other_ms = max_over_ranks(o_ms / 5)
+        del o_layers, o_acts
+        torch.cuda.empty_cache()
+
+    # ---- end to end: every step's inputs come from pinned host memory (two sets of device buffers:
+    # the copy of step i+1 runs on a copy stream under step i's kernels), a scalar goes back
     host = make_activations(shapes, m, device, pinned=True, world=world, paired=paired)
-    dev_in = {k: torch.empty_like(v, device=device) for k, v in host.items()}
+    dev_in = [{k: torch.empty_like(v, device=device) for k, v in host.items()} for _ in range(2)]
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     metric_host = torch.empty((), dtype=torch.float32).pin_memory()
+    copy_stream = torch.cuda.Stream()
+    landed = [torch.cuda.Event() for _ in range(2)]
+    released = [torch.cuda.Event() for _ in range(2)]
+    for ev in released:
+        ev.record()
 
-    def run_e2e(i):
-        for key, src in host.items():
-            dev_in[key].copy_(src, non_blocking=True)
-        outs = step_fn(layers[i % n_rot], dev_in)
-        metric_host.copy_(outs[-1].float().mean(), non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+    def enqueue_copy(i):
+        b = i % 2
+        copy_stream.wait_event(released[b])
+        with torch.cuda.stream(copy_stream):
+            for key, src in host.items():
+                dev_in[b][key].copy_(src, non_blocking=True)
+            landed[b].record(copy_stream)
 
-    for i in range(2):
-        run_e2e(i)
-    e2e_steps = 3
-    _, _, e2e_wall = timed_steps(run_e2e, e2e_steps, barrier=dist.barrier)
-    t = torch.tensor([e2e_wall], device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_wall = float(t.item())
+    def e2e_phase(n_steps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        wall0 = time.perf_counter()
+        enqueue_copy(0)
+        for i in range(n_steps):
+            if i + 1 < n_steps:
+                enqueue_copy(i + 1)
+            b = i % 2
+            torch.cuda.current_stream().wait_event(landed[b])
+            outs = step_fn(layers[i % n_rot], dev_in[b])
+            released[b].record()
+            metric_host.copy_(outs[-1].float().mean(), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        return time.perf_counter() - wall0
+
+    e2e_phase(2)
+    e2e_steps = 4
+    e2e_wall = max_over_ranks(e2e_phase(e2e_steps))
+
+    # ---- the same workload on one GPU (rank 0 alone, outside every timed region): the base of the
+    # strong-scaling efficiency
+    one_gpu_ms = None
+    if world > 1 and not args.no_one_gpu_base:
+        del dev_in, host
+        torch.cuda.empty_cache()
+        if rank == 0:
+            full_layers = [{n: e for n, e in make_layer(shapes, seed=i, device=device).items()} for i in range(2)]
+            full_acts = make_activations(shapes, m, device)
+            for i in range(3):
+                step_functional(full_layers[i % 2], full_acts)
+            base_ms, _, _ = timed_steps(lambda i: step_functional(full_layers[i % 2], full_acts), 5)
+            one_gpu_ms = base_ms / 5
+            del full_layers, full_acts
+        t = torch.tensor([one_gpu_ms or 0.0], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        one_gpu_ms = float(t.item())
 
     if rank == 0:
-        value = flops * args.steps / (total_ms * 1e-3) / 1e12
+        ms_per_step = total_ms / args.steps
+        value = flops / (ms_per_step * 1e-3) / 1e12
         if paired:   # four all-reduces of [m, hidden]: o and down outputs, the two summed dX
             gathered = 0.0
             reduced = 2.0 * m * (shapes["o"][0] + shapes["down"][0] + shapes["gate"][1] + shapes["q"][1])
         else:
             gathered = 2.0 * m * sum(n for n, _ in shapes.values())
             reduced = 2.0 * m * sum(k for _, k in shapes.values())
+        local_tflops = flops / (local_ms * 1e-3) / 1e12
         line = {
             "metric": "fused NF4 dequant-GEMM TFLOP/s (fwd+bwd)", "value": value,
             "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": workload_config(world, layout=args.layout),
+            "config": workload_config(world, layout=args.layout, multi_gpu_workload=True),
+            "verified": verified, "verify_max_rel_err": verify_err,
             "frac_of_tensor_peak": value / (pk["tflops_burst"] * world),
             "frac_of_sustained_tensor_peak": value / (pk["tflops_sustained"] * world),
             "gemm_only_ms_per_step": local_ms,
-            "gemm_only_tflops": flops / (local_ms * 1e-3) / 1e12,
+            "gemm_only_tflops": local_tflops,
+            "one_gpu_same_workload_ms": one_gpu_ms,
+            "strong_scaling_efficiency": None if not one_gpu_ms else one_gpu_ms / (world * ms_per_step),
+            "other_layout": None if other_ms is None else {
+                "layout": "gathered" if paired else "paired", "ms_per_step": other_ms,
+                "value": flops / (other_ms * 1e-3) / 1e12},
             "collective_bytes_per_step": {"all_gather_out": gathered, "all_reduce_dx": reduced},
-            "roofline": {"bound": "tensor", "achieved": flops / (local_ms * 1e-3) / 1e12 / world,
+            "roofline": {"bound": "tensor", "achieved": local_tflops / world,
                          "peak": pk["tflops_burst"], "unit": "TFLOP/s",
-                         "frac": flops / (local_ms * 1e-3) / 1e12 / world / pk["tflops_burst"],
+                         "frac": local_tflops / world / pk["tflops_burst"],
                          "peak_source": pk["source"] + " (burst cuBLAS bf16; timed regions of "
                                         "tens of milliseconds)",
                          "traffic": None,
@@ -966,7 +1255,7 @@ def run_multi(args):
             "e2e": {"value": flops * e2e_steps / e2e_wall / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": h2d * world, "d2h_bytes_per_step": 4 * world,
                     "steps": e2e_steps, "ms_per_step": e2e_wall / e2e_steps * 1e3},
-            "gpu_launches": (8 if paired else 14) * args.steps, "clocks": clocks,
+            "gpu_launches": (14 if paired else 26) * args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     dist.barrier()
@@ -987,6 +1276,12 @@ def main():
                          "per step); gathered = every weight sharded along output features "
                          "(all-gather of outputs, all-reduce of dX)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-verify", action="store_true",
+                    help="multi-GPU: skip the oracle check of one step (it runs before any timing)")
+    ap.add_argument("--no-other-layout", action="store_true",
+                    help="multi-GPU: skip the few extra steps of the layout that is not being timed")
+    ap.add_argument("--no-one-gpu-base", action="store_true",
+                    help="multi-GPU: skip rank 0's one-GPU run of the same workload")
     ap.add_argument("--multi-gpu-workload", action="store_true",
                     help="with --gpus 1: run the N > 1 workload (7B shapes, 8192 tokens) on one GPU, "
                          "the base of the strong-scaling numbers")

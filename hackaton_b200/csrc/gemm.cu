@@ -122,9 +122,6 @@ struct GemmParams {
     __half* sw_dup;
     long long ld_sw;
     int debug;               // NF4B200_DEBUG; the kernel looks at it only in -DNF4B200_TRACE builds
-#ifdef NF4B200_DUMP
-    uint32_t* dump;          // tuning aid: what each decoding thread read from the code ring
-#endif
 };
 
 struct GemmMaps {
@@ -819,26 +816,23 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                             cw[0] = q.x; cw[1] = q.y;
                         }
                     }
-#ifdef NF4B200_DUMP
-                    if (p.dump != nullptr && CG == 1 && it < 16) {
-                        uint32_t* d = p.dump + ((size_t)(blockIdx.x * 16 + it) * DECODE_THREADS + pt) * 8;
-                        d[0] = cw[0]; d[1] = cw[1]; d[2] = cw[WORDS - 2]; d[3] = cw[WORDS - 1];
-                        d[4] = *reinterpret_cast<const uint32_t*>(&scale2);
-                        d[5] = 0x80000000u | (uint32_t)(w.kb_begin + it);
-                    }
-#endif
-#ifdef NF4B200_EARLY_HANDBACK
-#if NF4B200_EARLY_HANDBACK == 2
+                    // Hand the code-ring slot back. The slot was read through the generic proxy
+                    // (ld.shared) and will be re-filled by TMA, i.e. through the async proxy. An
+                    // mbarrier arrive alone does not order the two: it can be performed while this
+                    // warp's loads are still queued in the (saturated) shared-memory pipe, the
+                    // feeding warp then sees a free slot, and the TMA write can land before some
+                    // of the loads' wavefronts are served, which then return the next k-block's
+                    // codes for part of the warp's lanes. fence.proxy.async makes the loads
+                    // complete before anything the async proxy does after the arrive; it is the
+                    // ordering the PTX memory model asks for between the two proxies.
+#ifdef NF4B200_HANDBACK_EARLY  // test builds: hand back before the operand slot is awaited
                     fence_proxy_async_smem();
-#endif
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_empty_c(c));
                     if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
 #else
                     if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
-                    // The code-ring slot goes back only now, with the operand slot in hand. Handing
-                    // it back before that wait gave intermittently wrong weight rows in the
-                    // single-CTA kernel (first calls on a new weight, M <= 128).
+                    fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_empty_c(c));
 #endif
@@ -1288,10 +1282,6 @@ static ForcedPlan forced_plan() {
 static constexpr int debug_flags() { return 0; }
 #endif
 
-#ifdef NF4B200_DUMP
-static uint32_t* g_dump = nullptr;
-#endif
-
 // Tiling and split-K plan shared by the launcher and the workspace-size query.
 GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long k_w, bool trans_w,
                          int sm_count) {
@@ -1454,9 +1444,6 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
     p.splits = pl.splits;
     p.kb_per_split = pl.kb_per_split;
     p.debug = debug_flags();
-#ifdef NF4B200_DUMP
-    p.dump = g_dump;
-#endif
     if (p.splits > 1) {
         if (a0.workspace == nullptr || a0.workspace_bytes < pl.ws_bytes) {
             p.splits = 1;  // no scratch given: one unit per tile walks the whole K range
@@ -1640,10 +1627,6 @@ cudaError_t launch_gemm(const GemmArgs& a, cudaStream_t stream, const char** why
 }
 
 }  // namespace nf4
-
-#ifdef NF4B200_DUMP
-extern "C" void nf4dbg_set_dump(void* ptr) { nf4::g_dump = static_cast<uint32_t*>(ptr); }
-#endif
 
 #ifdef NF4B200_TRACE
 // Tuning aid, not part of the public ABI: copies the phase timestamps to the host.

@@ -112,7 +112,9 @@ class WeightRef:
         nf4b200_prepare_scales in include/nf4b200.h) and hooks it into the descriptor. Weights
         are frozen in QLoRA, so the table stays valid while the state's tensors are not written
         (`weight_ref` drops the descriptor when they are). No host synchronisation: a call on
-        another stream than the one that built the table waits for the build on the device."""
+        another stream than the one that built the table waits for the build on the device.
+        Under CUDA-graph capture nothing can wait on work outside the capture, so build the
+        tables (`prepare_weights`) and let them finish before capturing."""
         if self.scales16 is not None or not PREPARED_SCALES:
             if self._ready is not None:
                 self._order_after_build()
@@ -134,9 +136,11 @@ class WeightRef:
         return self
 
     def _order_after_build(self):
+        if torch.cuda.is_current_stream_capturing():
+            return   # a capture cannot wait on outside work: build the tables before capturing
         event, stream = self._ready
         current = torch.cuda.current_stream(self.keep[0].device)
-        if not torch.cuda.is_current_stream_capturing() and event.query():
+        if event.query():
             self._ready = None
             return
         if current.cuda_stream != stream:

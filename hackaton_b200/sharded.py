@@ -1,9 +1,8 @@
 """Output-feature (column) sharding of the NF4 linear across the GPUs of one node.
 
-Rank g of G holds rows [g*N/G, (g+1)*N/G) of W, quantised as an NF4 weight of its own (its own
-codes, first- and second-level scales: a second-level block covers 16,384 consecutive weights
-and does not end on a row boundary, so a row-sliced shard of one big quant state would not be a
-clean slice of its nested array). The input X is replicated.
+Rank g of G holds rows [g*N/G, (g+1)*N/G) of W as an NF4 weight of its own: either quantised
+from the rank's slice of an fp16 weight (`from_full_weight`) or cut out of an already quantised
+weight (`from_quantized`, see below). The input X is replicated.
 
   forward : Y_g = X . W_gᵀ on each rank (fused kernel), then an NCCL all-gather of the shards.
             The gathered tensor is shard-major, [G, M, N/G]; `row_major()` rearranges it to
@@ -23,6 +22,24 @@ and the output-sharded members need no all-gather either (`forward_local`), only
 of their summed dX (`backward_dx_group`). Per decoder layer that is four all-reduces of
 [M, hidden] instead of seven all-gathers and seven all-reduces (6x fewer bytes at the 7B shapes).
 Shard boundaries along K fall on multiples of 64, so every shard is a whole number of NF4 blocks.
+
+LoRA on an output-sharded projection (q, v): A [16, K] is replicated, B [N, 16] is split by rows
+with W. The forward's rank-16 term and the rank's share of dX ride in the same fused launches
+(u_g = s . dY_g . B_g, and sum_g u_g . A is part of the one all-reduce of dX); dB_g is local, and
+dA = sum_g u_gᵀ . X is a [16, K] fp32 all-reduce (`lora_weight_grads`).
+
+Sharding an existing quantised weight (`slice_rows` / `slice_cols`): shard boundaries fall on
+whole 64-weight blocks, so the codes and the first-level scales of a shard are exact slices of
+the full weight's; the second-level blocks (256 first-level scales) do not end on shard
+boundaries, so the shard carries its first-level scales flattened to fp32 (the reference's own
+layout, solution/packed.py:57-79) and decodes to exactly the matching slice of the full weight.
+`from_full_weight` instead quantises the rank's slice of an fp16 weight on its own (other
+second-level blocks and another offset: close to, but not bit-equal to, the single-GPU weight).
+
+Precision of the input-sharded forward: every rank rounds its partial sum to fp16 before the
+all-reduce (the single-GPU kernel rounds the full fp32 sum once), so the result carries up to G
+extra half-ulp roundings: relative error <= G * 2^-11 of the largest partial, about 4e-3 at G = 8,
+inside the 1e-2 bound the fused linear is held to.
 
 The reference is single-GPU (harness/common.py:39); this is the one parallel strategy the
 B200 build adds. Collectives run through torch.distributed (NCCL over NVLink/NVSwitch); with
@@ -51,6 +68,47 @@ def reserve_comm_sms(n_sms: int) -> int:
     return use
 
 
+def _flat_scales(state):
+    """fp32 first-level scales of a quant state (two-level states decoded as the reference's
+    `_flatten_quant_states` does: code2[u8] * absmax2[i // 256], then + offset; two roundings)."""
+    if not getattr(state, "nested", False):
+        return state.absmax.float()
+    s2 = state.state2
+    idx = torch.arange(state.absmax.numel(), device=state.absmax.device) // int(s2.blocksize)
+    flat = s2.code.float()[state.absmax.long()] * s2.absmax.float()[idx]
+    return flat + state.offset.float()
+
+
+def slice_rows(packed, state, lo: int, hi: int):
+    """(packed, state) of rows [lo, hi) of an existing NF4 weight, decoding to exactly those rows
+    of the full weight. K must be a multiple of the block size."""
+    from .quantize import QuantState
+
+    n, k = int(state.shape[0]), int(state.shape[1])
+    bs = int(state.blocksize)
+    if k % bs != 0 or k % 2 != 0:
+        raise ValueError(f"{k} input features are not whole NF4 blocks of {bs}")
+    codes = packed.reshape(n, k // 2)[lo:hi].contiguous().reshape(-1, 1)
+    scales = _flat_scales(state).reshape(n, k // bs)[lo:hi].contiguous().reshape(-1)
+    return codes, QuantState(absmax=scales, code=state.code, shape=(hi - lo, k), dtype=state.dtype,
+                             blocksize=bs)
+
+
+def slice_cols(packed, state, lo: int, hi: int):
+    """(packed, state) of input features [lo, hi) of an existing NF4 weight; lo and hi must be
+    multiples of the block size."""
+    from .quantize import QuantState
+
+    n, k = int(state.shape[0]), int(state.shape[1])
+    bs = int(state.blocksize)
+    if lo % bs != 0 or hi % bs != 0 or k % bs != 0:
+        raise ValueError(f"columns [{lo}, {hi}) of {k} do not fall on NF4 blocks of {bs}")
+    codes = packed.reshape(n, k // 2)[:, lo // 2:hi // 2].contiguous().reshape(-1, 1)
+    scales = _flat_scales(state).reshape(n, k // bs)[:, lo // bs:hi // bs].contiguous().reshape(-1)
+    return codes, QuantState(absmax=scales, code=state.code, shape=(n, hi - lo), dtype=state.dtype,
+                             blocksize=bs)
+
+
 def shard_rows(n_rows: int, world: int, rank: int):
     """Row range of `rank`; N must split evenly so every shard has the same shape."""
     if n_rows % world != 0:
@@ -60,7 +118,8 @@ def shard_rows(n_rows: int, world: int, rank: int):
 
 
 class ShardedNF4Linear:
-    def __init__(self, packed, state, n_total: int, group=None):
+    def __init__(self, packed, state, n_total: int, group=None, lora_a=None, lora_b=None,
+                 scaling: float = 1.0):
         self.packed, self.state = packed, state
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -68,6 +127,23 @@ class ShardedNF4Linear:
         self.n_total = n_total
         self.n_local = int(state.shape[0])
         assert self.n_local * self.world == n_total
+        if (lora_a is None) != (lora_b is None):
+            raise ValueError("a sharded projection needs both LoRA factors or none")
+        if lora_b is not None and lora_b.shape[0] != self.n_local:
+            raise ValueError("lora_b must hold this rank's rows of B")
+        self.lora_a, self.lora_b, self.scaling = lora_a, lora_b, float(scaling)
+
+    @classmethod
+    def from_quantized(cls, packed, state, group=None, lora_a=None, lora_b=None, scaling=1.0):
+        """This rank's row shard of an already quantised full weight (e.g. one read from a 4-bit
+        checkpoint): decodes to exactly the matching rows of the full weight. `lora_b`, if given,
+        is the full [N, 16] factor; the rank keeps its rows."""
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        lo, hi = shard_rows(int(state.shape[0]), world, rank)
+        p, st = slice_rows(packed, state, lo, hi)
+        b = None if lora_b is None else lora_b[lo:hi].contiguous()
+        return cls(p, st, int(state.shape[0]), group, lora_a, b, scaling)
 
     @classmethod
     def from_full_weight(cls, weight, group=None, **quant_kwargs):
@@ -79,6 +155,8 @@ class ShardedNF4Linear:
         return cls(packed, state, weight.shape[0], group)
 
     def forward_local(self, x):
+        if self.lora_a is not None:
+            return forward_local_group([self], x)[0]
         return linear_forward(x, self.packed, None, self.state)
 
     def forward(self, x, async_op=False):
@@ -93,6 +171,8 @@ class ShardedNF4Linear:
 
     def backward_dx(self, grad_shard, async_op=False):
         """grad_shard: this rank's [M, N/G] slice of dY. Returns (dX summed over ranks, work)."""
+        if self.lora_a is not None:
+            return backward_dx_group([self], [grad_shard], async_op=async_op)
         dx = linear_backward_dx(grad_shard, self.packed, self.state)
         if self.world == 1:
             return dx, None
@@ -123,6 +203,15 @@ class InputShardedNF4Linear:
                              "columns are not whole NF4 blocks of 64")
 
     @classmethod
+    def from_quantized(cls, packed, state, group=None):
+        """This rank's column shard of an already quantised full weight."""
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        lo, hi = shard_rows(int(state.shape[1]), world, rank)
+        p, st = slice_cols(packed, state, lo, hi)
+        return cls(p, st, int(state.shape[1]), group)
+
+    @classmethod
     def from_full_weight(cls, weight, group=None, **quant_kwargs):
         """Quantise this rank's column shard of a full [N, K] weight."""
         world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -146,19 +235,70 @@ class InputShardedNF4Linear:
         return linear_backward_dx(grad, self.packed, self.state), None
 
 
-def forward_local_group(mods, x):
+def _lora_members(mods):
+    return [i for i, m in enumerate(mods) if getattr(m, "lora_a", None) is not None]
+
+
+def forward_local_group(mods, x, return_lora_inputs=False):
     """Output shards of several output-sharded projections that read the same x: one grouped launch,
-    no exchange (their consumer is input-sharded)."""
+    no exchange (their consumer is input-sharded). Members with LoRA get their rank-16 term in the
+    same launch; with `return_lora_inputs` the per-member s . x . Aᵀ (needed for dB) come back too."""
     from .group import linear_forward_group
-    return linear_forward_group(x, [(m.packed, m.state) for m in mods])
+    from .lora import lora_down_batch
+
+    xas = [None] * len(mods)
+    with_lora = _lora_members(mods)
+    if with_lora:
+        downs = lora_down_batch([x] * len(with_lora), [mods[i].lora_a for i in with_lora], True,
+                                [mods[i].scaling for i in with_lora])
+        for i, xa in zip(with_lora, downs):
+            xas[i] = xa
+    outs = linear_forward_group(x, [(m.packed, m.state) for m in mods], None, xas,
+                                [getattr(m, "lora_b", None) for m in mods])
+    return (outs, xas) if return_lora_inputs else outs
 
 
-def backward_dx_group(mods, grad_shards, async_op=False):
+def backward_dx_group(mods, grad_shards, async_op=False, return_lora_inputs=False):
     """dX of several output-sharded projections that read the same x: one grouped launch sums their
-    local shares, one all-reduce sums over ranks. Returns (dX, work-or-None)."""
+    local shares (LoRA shares included), one all-reduce sums over ranks. Returns (dX, work-or-None)
+    and, with `return_lora_inputs`, the per-member s . dY_g . B_g (needed for dA)."""
     from .group import linear_backward_dx_group
-    dx = linear_backward_dx_group(list(grad_shards), [(m.packed, m.state) for m in mods])
+    from .lora import lora_down_batch
+
+    grad_shards = list(grad_shards)
+    us = [None] * len(mods)
+    with_lora = _lora_members(mods)
+    if with_lora:
+        downs = lora_down_batch([grad_shards[i] for i in with_lora], [mods[i].lora_b for i in with_lora],
+                                False, [mods[i].scaling for i in with_lora])
+        for i, u in zip(with_lora, downs):
+            us[i] = u
+    dx = linear_backward_dx_group(grad_shards, [(m.packed, m.state) for m in mods], us,
+                                  [getattr(m, "lora_a", None) for m in mods])
     world = mods[0].world
-    if world == 1:
-        return dx, None
-    return dx, dist.all_reduce(dx, group=mods[0].group, async_op=async_op)
+    work = None if world == 1 else dist.all_reduce(dx, group=mods[0].group, async_op=async_op)
+    return (dx, work, us) if return_lora_inputs else (dx, work)
+
+
+def lora_weight_grads(mods, x, grad_shards, xas, us, async_op=False):
+    """fp32 gradients of the LoRA factors of the members that have them, in one launch:
+    dA = sum over ranks of u_gᵀ . x ([16, K], all-reduced: A is replicated), dB_g = dY_gᵀ . xa
+    ([N/G, 16], local: B is sharded with W). Returns ({member index: (dA, dB)}, [works])."""
+    from .lora import lora_grad_batch
+
+    with_lora = _lora_members(mods)
+    if not with_lora:
+        return {}, []
+    zs, ss, rank_major = [], [], []
+    for i in with_lora:
+        zs += [x, grad_shards[i]]
+        ss += [us[i], xas[i]]
+        rank_major += [True, False]
+    res = lora_grad_batch(zs, ss, rank_major)
+    out, works = {}, []
+    for j, i in enumerate(with_lora):
+        d_a, d_b = res[2 * j], res[2 * j + 1]
+        if mods[i].world > 1:
+            works.append(dist.all_reduce(d_a, group=mods[i].group, async_op=async_op))
+        out[i] = (d_a, d_b)
+    return out, [w for w in works if w is not None]

@@ -88,3 +88,41 @@ def test_fresh_weights_first_calls_vs_reference(cuda_lib):
                 assert torch.equal(w_dev.cpu(), w)
                 assert nf4_oracle.max_rel_err(y1.cpu(), nf4_oracle.linear_fwd(x.cpu(), w)) <= TOL
     assert cuda_lib.device_status() == 0
+
+
+@pytest.mark.parametrize("nested", [True, False])
+def test_code_ring_hand_back_under_load(cuda_lib, nested):
+    """The code ring of the fused kernel is read with ordinary shared-memory loads and re-filled by
+    TMA; the hand-back between the two has to order them (a proxy fence). When it did not, a warp
+    could decode part of its rows from the next k-block's codes: a few wrong output columns in
+    about half of the calls at these shapes. Fresh weights, both scale paths, token counts of
+    every kernel variant, forward and backward, each call against the fp32 product of the
+    standalone decode (bit-equal to the oracle, which the first weight re-checks)."""
+    import copy
+
+    from hackaton_b200 import nf4
+
+    for i in range(10):
+        n, k = ((1536, 8960), (1536, 8960), (8960, 1536), (1536, 1536))[i % 4]
+        packed, state = synthetic_weight(n, k, nested, seed=900 + i, device="cuda")
+        bare = copy.copy(state)            # same tensors, no cached descriptor, no scale table
+        w = nf4.dequantize_nf4(packed, state)
+        if i == 0:
+            assert torch.equal(w.cpu(), oracle_weight(packed, state))
+        wf = w.float()
+        for m in (1, 20, 33, 64, 128, 300, 2048):
+            x = torch.randn(m, k, device="cuda").half()
+            dy = torch.randn(m, n, device="cuda").half()
+            want_y, want_dx = x.float() @ wf.t(), dy.float() @ wf
+            try:
+                for prepared, st in ((True, state), (False, bare)):
+                    nf4.PREPARED_SCALES = prepared
+                    for call in range(2):
+                        y = nf4.linear_forward(x, packed, None, st)
+                        dx = nf4.linear_backward_dx(dy, packed, st)
+                        ey = float((y.float() - want_y).abs().max() / want_y.abs().max())
+                        edx = float((dx.float() - want_dx).abs().max() / want_dx.abs().max())
+                        assert ey <= 2e-3 and edx <= 2e-3, (i, n, k, m, prepared, call, ey, edx)
+            finally:
+                nf4.PREPARED_SCALES = True
+    assert cuda_lib.device_status() == 0
