@@ -592,6 +592,56 @@ def timed_steps(run, n_steps, barrier=None):
     return sum(per_step), per_step, wall
 
 
+def run_leg(args):
+    """`--only LEG`: a few eager launches of one family of kernels over eight layers' weights
+    (193 MB of packed weights, more than the L2 holds) and nothing else: the small, bounded
+    command the profiler captures are taken from. Prints one short JSON line."""
+    from hackaton_b200 import _lib
+    from hackaton_b200.lora import lora_down_batch, lora_grad_batch
+    from hackaton_b200.nf4 import dequantize_nf4, linear_forward, prepare_weights
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    shapes = SHAPES_15B
+    n_layers = 8
+    layers = [make_layer(shapes, seed=i, device=device) for i in range(n_layers)]
+    for layer in layers:
+        prepare_weights([(e["packed"], e["state"]) for e in layer.values()])
+    torch.cuda.synchronize()
+    reps = max(1, args.steps)
+    launches = 0
+    if args.only == "dequant":
+        for i in range(reps * n_layers):
+            e = layers[i % n_layers]["gate"]
+            dequantize_nf4(e["packed"], e["state"])
+            launches += 1
+    elif args.only in ("small_m", "small_m_bwd"):
+        acts = make_activations(shapes, args.tokens or 1, device)
+        fn = layer_forward if args.only == "small_m" else layer_backward
+        for i in range(reps * n_layers):
+            launches += len(fn(layers[i % n_layers], acts))
+    elif args.only == "down_fwd":      # a split-K shape: GEMM + reduction kernel
+        acts = make_activations(shapes, args.tokens or 2048, device)
+        for i in range(reps * n_layers):
+            e = layers[i % n_layers]["down"]
+            linear_forward(acts["x_down"], e["packed"], None, e["state"])
+            launches += 2
+    elif args.only == "lora":
+        acts = make_activations(shapes, args.tokens or 2048, device)
+        for i in range(reps * n_layers):
+            lay = layers[i % n_layers]
+            xa = lora_down_batch([acts["x_attn"]] * 2, [lay["q"]["A"], lay["v"]["A"]], True, [SCALING] * 2)
+            u = lora_down_batch([acts["dy_q"], acts["dy_v"]], [lay["q"]["B"], lay["v"]["B"]], False,
+                                [SCALING] * 2)
+            lora_grad_batch([acts["x_attn"], acts["dy_q"], acts["x_attn"], acts["dy_v"]],
+                            [u[0], xa[0], u[1], xa[1]], [True, False, True, False])
+            launches += 3
+    torch.cuda.synchronize()
+    _lib.device_status()
+    print(json.dumps({"only": args.only, "launch_groups": launches, "layers": n_layers,
+                      "tokens": args.tokens}), flush=True)
+
+
 def run_single(args):
     from hackaton_b200 import _lib
 
@@ -600,6 +650,9 @@ def run_single(args):
     props = _lib.query(0)
     if not props.supported:
         raise SystemExit(f"bench.py needs a B200 (sm_100); found sm_{props.cc_major}{props.cc_minor}")
+    if args.only:
+        run_leg(args)
+        return
     shapes, m = SHAPES_15B, 2048
     pk = peaks()
     layers = [make_layer(shapes, seed=i, device=device) for i in range(N_LAYERS)]
@@ -1276,6 +1329,11 @@ def main():
                          "per step); gathered = every weight sharded along output features "
                          "(all-gather of outputs, all-reduce of dX)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--only", default=None,
+                    choices=["dequant", "small_m", "small_m_bwd", "down_fwd", "lora"],
+                    help="run a few eager launches of one kernel family and nothing else (the "
+                         "command profiler captures are taken from)")
+    ap.add_argument("--tokens", type=int, default=0, help="with --only: token rows")
     ap.add_argument("--no-verify", action="store_true",
                     help="multi-GPU: skip the oracle check of one step (it runs before any timing)")
     ap.add_argument("--no-other-layout", action="store_true",

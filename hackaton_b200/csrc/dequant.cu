@@ -7,7 +7,8 @@
 // value = table[code] * scale (fp32), rounded once to the output type.
 //
 // HBM bound: 0.5159 B read + 2 B written per weight (fp16 out, nested scales). One lane per
-// 32-bit word of codes (8 weights): 128-byte coalesced loads, 512-byte coalesced stores.
+// 32-bit word of codes (8 weights), eight words in flight per thread: 128-byte coalesced loads,
+// 512-byte coalesced stores, one wave of resident CTAs in a grid-stride loop.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -52,61 +53,93 @@ struct Pack8<float> {
 };
 
 constexpr int DEQ_THREADS = 256;
-constexpr int DEQ_WORDS_PER_THREAD = 4;
+constexpr int DEQ_WORDS_PER_THREAD = 8;   // 32-bit code words (8 weights each) in flight per thread
 
-template <typename T, bool NESTED>
+// The 16-entry table is kept once per lane (entry e of lane l at [e * 32 + l]): every look-up of a
+// warp then goes to 32 different banks whatever the codes are.
+// SHIFTS: block sizes are powers of two (the bitsandbytes layout: 64 and 256), so the block of a
+// word and the second-level block of a block are shifts; other sizes take the dividing variant.
+template <typename T, bool NESTED, bool SHIFTS>
 __global__ void __launch_bounds__(DEQ_THREADS)
 nf4_dequant_kernel(const uint32_t* __restrict__ codes, const void* __restrict__ absmax,
                    const float* __restrict__ code2, const float* __restrict__ absmax2,
                    const float* __restrict__ offset_ptr, const float* __restrict__ code16,
                    T* __restrict__ out, long long n_words, int words_per_block,
-                   int nested_blocksize) {
+                   int nested_blocksize, int block_shift, int nested_shift, int prefetch_ok) {
+    const long long tile = (long long)DEQ_THREADS * DEQ_WORDS_PER_THREAD;
+    // The CTA's first tile of codes on its way to L2 while the previous kernel of the stream is
+    // still running (a prefetch reads no values, so it may precede the dependency wait).
+    if (threadIdx.x == 0 && prefetch_ok) {
+        const long long first = (long long)blockIdx.x * tile;
+        if (first < n_words) {
+            const long long n = n_words - first < tile ? n_words - first : tile;
+            const uint32_t bytes = (uint32_t)(n * 4) & ~15u;
+            if (bytes != 0) bulk_prefetch_l2(codes + first, bytes);
+        }
+    }
     grid_dep_wait();    // (programmatic dependent launch: the predecessor's results)
     grid_dep_launch();
-    __shared__ float table[16];
+    __shared__ float table[16 * 32];
     __shared__ float table2[256];
-    if (threadIdx.x < 16) table[threadIdx.x] = code16[threadIdx.x];
-    if (NESTED) table2[threadIdx.x] = code2[threadIdx.x];
-    __syncthreads();
-    const float offset = NESTED ? *offset_ptr : 0.f;
+    const float* my_table = table + (threadIdx.x & 31);
 
-    const long long tile = (long long)DEQ_THREADS * DEQ_WORDS_PER_THREAD;
-    for (long long base = (long long)blockIdx.x * tile; base < n_words;
-         base += (long long)gridDim.x * tile) {
-        uint32_t word[DEQ_WORDS_PER_THREAD];
-        float scale[DEQ_WORDS_PER_THREAD];
+    uint32_t word[DEQ_WORDS_PER_THREAD];
+    float raw[DEQ_WORDS_PER_THREAD];      // flat: the scale; nested: the second-level scale
+    uint32_t q8[DEQ_WORDS_PER_THREAD];    // nested: the 8-bit first-level code
+    auto issue = [&](long long base) {
 #pragma unroll
         for (int j = 0; j < DEQ_WORDS_PER_THREAD; ++j) {
             const long long w = base + j * DEQ_THREADS + threadIdx.x;
             word[j] = 0;
-            scale[j] = 0.f;
+            raw[j] = 0.f;
+            q8[j] = 0;
             if (w < n_words) {
                 word[j] = __ldcs(codes + w);
-                const long long blk = w / words_per_block;
+                const long long blk = SHIFTS ? (w >> block_shift) : (w / words_per_block);
                 if (NESTED) {
-                    const uint8_t q = __ldg(static_cast<const uint8_t*>(absmax) + blk);
-                    scale[j] = nested_scale(table2[q], __ldg(absmax2 + blk / nested_blocksize),
-                                            offset);
+                    q8[j] = __ldg(static_cast<const uint8_t*>(absmax) + blk);
+                    const long long blk2 = SHIFTS ? (blk >> nested_shift) : (blk / nested_blocksize);
+                    raw[j] = __ldg(absmax2 + blk2);
                 } else {
-                    scale[j] = __ldg(static_cast<const float*>(absmax) + blk);
+                    raw[j] = __ldg(static_cast<const float*>(absmax) + blk);
                 }
             }
         }
+    };
+    // the first tile's loads go out before the tables are built: their round trips overlap
+    long long base = (long long)blockIdx.x * tile;
+    if (base < n_words) issue(base);
+    for (int i = threadIdx.x; i < 16 * 32; i += DEQ_THREADS) table[i] = code16[i >> 5];
+    if (NESTED) table2[threadIdx.x] = code2[threadIdx.x];
+    const float offset = NESTED ? *offset_ptr : 0.f;
+    __syncthreads();
+
+    while (base < n_words) {
 #pragma unroll
         for (int j = 0; j < DEQ_WORDS_PER_THREAD; ++j) {
             const long long w = base + j * DEQ_THREADS + threadIdx.x;
             if (w < n_words) {
+                const float scale = NESTED ? nested_scale(table2[q8[j]], raw[j], offset) : raw[j];
                 float v[8];
 #pragma unroll
                 for (int k = 0; k < 4; ++k) {
                     const uint32_t byte = (word[j] >> (8 * k)) & 0xFFu;
-                    v[2 * k] = __fmul_rn(table[byte >> 4], scale[j]);
-                    v[2 * k + 1] = __fmul_rn(table[byte & 15u], scale[j]);
+                    v[2 * k] = __fmul_rn(my_table[(byte >> 4) << 5], scale);
+                    v[2 * k + 1] = __fmul_rn(my_table[(byte & 15u) << 5], scale);
                 }
                 Pack8<T>::store(out + w * 8, v);
             }
         }
+        base += (long long)gridDim.x * tile;
+        if (base < n_words) issue(base);
     }
+}
+
+static int exact_log2(long long v) {
+    if (v <= 0 || (v & (v - 1)) != 0) return -1;
+    int s = 0;
+    while ((1ll << s) < v) ++s;
+    return s;
 }
 
 template <typename T>
@@ -114,21 +147,34 @@ static cudaError_t launch_t(const DequantArgs& a, cudaStream_t stream) {
     const long long n_words = a.n / 8;
     const long long tile = (long long)DEQ_THREADS * DEQ_WORDS_PER_THREAD;
     long long blocks = (n_words + tile - 1) / tile;
-    const long long cap = (long long)a.sm_count * 16;
+    // One wave: as many CTAs as are resident at once (8 per SM at 256 threads), each walking
+    // the words in grid-stride order; a second, partly filled wave would cost as much as the first.
+    const long long cap = (long long)a.sm_count * 8;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     const int wpb = a.blocksize / 8;
+    const int bshift = exact_log2(wpb);
+    const int nshift = a.nested ? exact_log2(a.nested_blocksize) : 0;
+    const bool shifts = bshift >= 0 && nshift >= 0;
+    const dim3 grid((unsigned)blocks), block(DEQ_THREADS);
+    const int pf = (reinterpret_cast<uintptr_t>(a.codes) & 15) == 0 ? 1 : 0;  // bulk prefetch needs 16 B
+    const uint32_t* codes = static_cast<const uint32_t*>(a.codes);
+    T* out = static_cast<T*>(a.out);
     if (a.nested) {
-        return launch_pdl(nf4_dequant_kernel<T, true>, dim3((unsigned)blocks), dim3(DEQ_THREADS), 0,
-                          stream, static_cast<const uint32_t*>(a.codes), a.absmax, a.code2, a.absmax2,
-                          a.offset, a.code16, static_cast<T*>(a.out), n_words, wpb,
-                          a.nested_blocksize);
+        if (shifts)
+            return launch_pdl(nf4_dequant_kernel<T, true, true>, grid, block, 0, stream, codes, a.absmax,
+                              a.code2, a.absmax2, a.offset, a.code16, out, n_words, wpb,
+                              a.nested_blocksize, bshift, nshift, pf);
+        return launch_pdl(nf4_dequant_kernel<T, true, false>, grid, block, 0, stream, codes, a.absmax,
+                          a.code2, a.absmax2, a.offset, a.code16, out, n_words, wpb,
+                          a.nested_blocksize, 0, 0, pf);
     }
-    return launch_pdl(nf4_dequant_kernel<T, false>, dim3((unsigned)blocks), dim3(DEQ_THREADS), 0,
-                      stream, static_cast<const uint32_t*>(a.codes), a.absmax,
-                      static_cast<const float*>(nullptr), static_cast<const float*>(nullptr),
-                      static_cast<const float*>(nullptr), a.code16, static_cast<T*>(a.out), n_words,
-                      wpb, 1);
+    const float* none = nullptr;
+    if (shifts)
+        return launch_pdl(nf4_dequant_kernel<T, false, true>, grid, block, 0, stream, codes, a.absmax,
+                          none, none, none, a.code16, out, n_words, wpb, 1, bshift, 0, pf);
+    return launch_pdl(nf4_dequant_kernel<T, false, false>, grid, block, 0, stream, codes, a.absmax,
+                      none, none, none, a.code16, out, n_words, wpb, 1, 0, 0, pf);
 }
 
 cudaError_t launch_dequant(const DequantArgs& a, cudaStream_t stream) {

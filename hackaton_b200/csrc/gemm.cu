@@ -1211,6 +1211,19 @@ splitk_reduce_kernel(const float* __restrict__ ws, long long m, long long n_out,
     }
 }
 
+cudaError_t launch_splitk_reduce(const float* planes, long long m, long long n_out, long long ldp,
+                                 int splits, const __half* bias, __half* out, long long ld_out,
+                                 int sm_count, cudaStream_t stream) {
+    const long long total = m * ((n_out + 7) / 8);
+    long long blocks = (total + 255) / 256;
+    const long long cap = (long long)sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    const int vec_ok = (ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+    return launch_pdl(splitk_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, planes, m,
+                      n_out, ldp, splits, bias, out, ld_out, vec_ok);
+}
+
 // ------------------------------------------------------------------------------------ host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -1347,6 +1360,12 @@ GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long
         if (pl.splits > 1) ws_floats += (size_t)pl.splits * (size_t)m * (size_t)pl.ldp[i];
     }
     pl.ws_bytes = ws_floats * sizeof(float);
+    // a few token rows, backward: the weight-streaming kernel may serve the call instead (it needs
+    // the scale tables, which a size query cannot see): the scratch has to do for either
+    if (trans_w && m <= 16) {
+        const StreamBwdPlan sp = plan_stream_bwd(m, n_w, count, k_w, sm_count);
+        if (sp.ws_bytes > pl.ws_bytes) pl.ws_bytes = sp.ws_bytes;
+    }
     return pl;
 }
 
@@ -1492,16 +1511,9 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
     if (p.splits > 1) {
         for (int i = 0; i < (TRANS_W ? 1 : ga.count); ++i) {
             const GemmArgs& a = ga.item[i];
-            const long long n_out = TRANS_W ? k_w : a.n_w;
-            const long long total = m * ((n_out + 7) / 8);
-            long long blocks = (total + 255) / 256;
-            const long long cap = (long long)a0.sm_count * 8;
-            if (blocks > cap) blocks = cap;
-            const int vec_ok = (a.ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(a.out) & 15) == 0);
-            e = launch_pdl(splitk_reduce_kernel, dim3((unsigned)blocks), dim3(256), 0, stream,
-                           p.prob[i].ws, (long long)m, (long long)n_out, (long long)p.prob[i].ldp,
-                           p.splits, TRANS_W ? static_cast<const __half*>(nullptr) : a.bias, a.out,
-                           (long long)a.ld_out, vec_ok);
+            e = launch_splitk_reduce(p.prob[i].ws, m, TRANS_W ? k_w : a.n_w, p.prob[i].ldp, p.splits,
+                                     TRANS_W ? static_cast<const __half*>(nullptr) : a.bias, a.out,
+                                     a.ld_out, a0.sm_count, stream);
             if (e != cudaSuccess) { *why = "split-K reduce launch"; return e; }
         }
     }
@@ -1569,23 +1581,26 @@ cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, cons
     long long n_w[GEMM_MAX_GROUP];
     for (int i = 0; i < ga.count; ++i) n_w[i] = ga.item[i].n_w;
     const GemmArgs& a = ga.item[0];
-    // A handful of token rows: stream the weights through the small-M kernel, one launch per
-    // weight (NF4B200_DEBUG bit 7 keeps them on the tensor-core kernel, for comparison).
-    if (!a.trans_w && a.m <= 64 && !(debug_flags() & 128)) {
+    // A handful of token rows: stream the weights through the small-M kernels, the whole group in
+    // one launch (NF4B200_DEBUG bit 7 keeps them on the tensor-core kernel, for comparison).
+    if (a.m <= 64 && !(debug_flags() & 128)) {
         bool all = true;
         for (int i = 0; i < ga.count; ++i) {
             GemmArgs it = ga.item[i];
-            it.act = a.act; it.m = a.m; it.ld_act = a.ld_act; it.trans_w = false;
-            if (!gemv_eligible(it)) all = false;
+            it.m = a.m; it.trans_w = a.trans_w;
+            if (!a.trans_w) { it.act = a.act; it.ld_act = a.ld_act; }
+            if (!(a.trans_w ? gemv_bwd_eligible(it) : gemv_eligible(it))) all = false;
         }
-        if (all) {
-            for (int i = 0; i < ga.count; ++i) {
-                GemmArgs it = ga.item[i];
-                it.act = a.act; it.m = a.m; it.ld_act = a.ld_act; it.trans_w = false;
-                cudaError_t e = launch_gemv(it, stream);
-                if (e != cudaSuccess) { *why = "small-M kernel launch"; return e; }
-            }
-            return cudaSuccess;
+        if (all && a.trans_w) {
+            long long rows[GEMM_MAX_GROUP];
+            for (int i = 0; i < ga.count; ++i) rows[i] = ga.item[i].n_w;
+            const StreamBwdPlan sp = plan_stream_bwd(a.m, rows, ga.count, a.k_w, a.sm_count);
+            if (a.workspace != nullptr && a.workspace_bytes >= sp.ws_bytes)
+                return launch_gemv_bwd_group(ga, stream, why);
+        } else if (all) {
+            cudaError_t e = launch_gemv_group(ga, stream);
+            if (e != cudaSuccess) *why = "small-M kernel launch";
+            return e;
         }
     }
     const GemmPlan pl = plan_gemm_group(a.m, n_w, ga.count, a.k_w, a.trans_w, a.sm_count);

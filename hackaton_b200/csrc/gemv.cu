@@ -1,17 +1,38 @@
-// Forward NF4 linear for a handful of token rows (M <= 64, the decode shapes of serving):
-//   out[M, N] = act[M, K] . W^T (+ bias) (+ ext_a . ext_b^T)
+// NF4 linear for a handful of token rows (the decode shapes of serving), both directions:
+//   forward  (M <= 64): out_i[M, N_i] = act[M, K] . W_i^T (+ bias_i) (+ ext_a_i . ext_b_i^T)
+//   backward (M <= 16): out[M, K]     = sum_i act_i[M, N_i] . W_i  (+ ext_a_i . ext_b_i)
+// for a group of up to four weights that share K (forward: they also share the activations).
 // At these sizes the work is reading the packed weights once (0.52 B per weight); a 128-row
 // tensor-core tile would be 50-99 % padding and the persistent tcgen05 kernel's set-up and
-// epilogue would dominate. So: no shared-memory ring, no TMEM. A CTA owns 16 weight rows, its
-// 4, 8 or 16 warps (more for long rows, fewer when there are many CTAs) split the 64-deep k-blocks; every warp streams its rows' codes straight from global
-// memory (one 32-byte sector per row and k-block), expands them in registers with the same
-// byte-permute table look-up as the big kernel (same rounding: fp16(table) * fp16(scale)), and
-// multiplies with warp-level mma.sync (m16n8k16: 16 weight rows x 8 tokens x 16 k, fp32
-// accumulate). The contraction index is visited in a permuted order that A and B share, so a
-// thread's 16 consecutive weights and 16 consecutive activations feed four k16 steps without any
-// shuffle. The warps' partial tiles are added through shared memory; bias and the rank-16 LoRA
-// term are applied there. Needs the ready-made fp16 block-scale table (kernels.h,
-// launch_prepare_scales) and N % 16 == 0; other calls take the tcgen05 kernel.
+// epilogue would dominate. So: no shared-memory ring, no TMEM. Warps stream the codes straight
+// from global memory, expand them in registers with the same byte-permute table look-up as the
+// big kernel (same rounding: fp16(table) * fp16(scale)) and multiply with warp-level mma.sync
+// (m16n8k16, fp32 accumulate).
+//
+// Forward: a CTA owns 16 weight rows of one member of the group, its warps split the 64-deep
+// k-blocks. The contraction index is visited in a permuted order that A (weights) and B (tokens)
+// share, so a thread's 16 consecutive weights and 16 consecutive activations feed four k16 steps
+// without any shuffle. The warps' partial tiles are added through shared memory; bias and the
+// rank-16 LoRA term are applied there.
+//
+// Backward: the contraction runs over weight rows, along which the codes are NOT contiguous. A
+// warp owns one k-block (64 output columns) and a slab of weight rows; per step of 16 rows lane
+// (g, t) decodes one 32-bit word (8 columns: word g of the k-block) of rows 2t, 2t+1, 2t+8, 2t+9
+// and issues eight MMAs, one per column position c of its word: in MMA c the B operand's column
+// g is "column c of word g", so the fragment a thread needs (two consecutive contraction rows of
+// one column) is a byte-permute of two of its own decoded words. A (the upstream gradient,
+// row-major over the contraction) is loaded as plain fragments. A thread ends up with 16
+// consecutive output columns of tokens g and g + 8. Row slabs are summed in two steps: the
+// warps of a CTA through shared memory, the CTAs of a k-block as fp32 planes that the split-K
+// reduction kernel adds in slab order (deterministic).
+//
+// Both kernels ask for their slab of codes to be brought into L2 before they wait for the
+// previous kernel of the stream (programmatic dependent launch): a prefetch reads no values, so
+// it needs no ordering, and in a chain of small launches the weights of launch i + 1 travel
+// from HBM while launch i runs.
+//
+// Both need the ready-made fp16 block-scale table (kernels.h, launch_prepare_scales) and
+// N % 16 == 0; other calls take the tcgen05 kernel.
 #include <cuda_fp16.h>
 
 #include "decode.cuh"
@@ -22,18 +43,31 @@ namespace nf4 {
 
 constexpr int GV_ROWS = 16;
 constexpr int GV_BATCH = 4;
+constexpr int GV_MAXP = GEMM_MAX_GROUP;
 
-struct GemvParams {
+struct GemvProblem {
     const uint8_t* codes;
     const __half* scales16;  // [K / 64][N]
     const float* code16;
-    const __half* act;
     const __half* bias;
-    const __half* ext_a;     // [M, 16] or null
-    const __half* ext_b;     // [N, 16]
-    __half* out;
-    long long ld_act, ld_out;
-    int m, n_w, k_w;
+    const __half* ext_a;     // forward: [M, 16] or null; backward: u [M, 16] or null
+    const __half* ext_b;     // forward: lora_b [N, 16]; backward: lora_a [16, K]
+    const __half* act;       // backward: this member's dY [M, N]
+    __half* out;             // forward: this member's output
+    long long ld_out, ld_act;
+    int n_w;
+    int first;               // forward: first CTA of this member; backward: first row slab
+};
+
+struct GemvParams {
+    GemvProblem prob[GV_MAXP];
+    const __half* act;       // forward: shared activations
+    long long ld_act;
+    float* planes;           // backward: [slabs][M][ldp] fp32
+    long long ldp;
+    int n_prob, m, k_w;
+    int rows_per_slab;       // backward: weight rows per CTA (multiple of 16 * warps)
+    int prefetch;            // codes are 16-byte aligned: bulk L2 prefetch is legal
 };
 
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -45,26 +79,49 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ RegLut load_reg_lut(const float* code16) {
+    uint16_t bits[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) bits[i] = __half_as_ushort(__float2half_rn(__ldg(code16 + i)));
+    return make_reg_lut(bits);
+}
+
+__device__ __forceinline__ int gemv_find(const GemvParams& p, int idx) {
+    int r = 0;
+#pragma unroll
+    for (int i = 1; i < GV_MAXP; ++i)
+        if (i < p.n_prob && idx >= p.prob[i].first) r = i;
+    return r;
+}
+
+// Asks for `bytes` starting at `ptr` (16-byte aligned, multiple of 16) to be brought into L2, in
+// pieces the bulk-prefetch instruction takes.
+__device__ __forceinline__ void prefetch_span(const uint8_t* ptr, long long bytes) {
+    constexpr long long PIECE = 32768;
+    for (long long off = 0; off < bytes; off += PIECE) {
+        const long long n = bytes - off < PIECE ? bytes - off : PIECE;
+        bulk_prefetch_l2(ptr + off, (uint32_t)n);
+    }
+}
+
 template <int NT, int GV_WARPS>  // token blocks of 8 (M <= 8 * NT); warps that split K
 __global__ void __launch_bounds__(GV_WARPS * 32)
-nf4_gemv_kernel(const GemvParams p) {
+nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
     constexpr int GV_THREADS = GV_WARPS * 32;
+    const int pi = gemv_find(p, (int)blockIdx.x);
+    const GemvProblem& pr = p.prob[pi];
+    const int r0 = ((int)blockIdx.x - pr.first) * GV_ROWS;
+    const size_t row_bytes = (size_t)p.k_w >> 1;
+    // The CTA's 16 rows of codes are one contiguous span: on its way to L2 while the previous
+    // kernel of the stream is still running.
+    if (threadIdx.x == 0 && p.prefetch)
+        prefetch_span(pr.codes + (size_t)r0 * row_bytes, (long long)(GV_ROWS * row_bytes));
     grid_dep_wait();
     grid_dep_launch();
     __shared__ float red[GV_WARPS][NT * 8][GV_ROWS + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int r0 = blockIdx.x * GV_ROWS;
     const int r_lo = r0 + g, r_hi = r0 + g + 8;  // n_w % 16 == 0: both inside the weight
-
-    RegLut lut;
-    {
-        uint16_t bits[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-            bits[i] = __half_as_ushort(__float2half_rn(__ldg(p.code16 + i)));
-        lut = make_reg_lut(bits);
-    }
 
     float acc[NT][4];
 #pragma unroll
@@ -72,25 +129,32 @@ nf4_gemv_kernel(const GemvParams p) {
 
     const int nkb = p.k_w >> 6;
     const int kb_begin = nkb * warp / GV_WARPS, kb_end = nkb * (warp + 1) / GV_WARPS;
-    const size_t row_bytes = (size_t)p.k_w >> 1;
-    const uint8_t* c_lo = p.codes + (size_t)r_lo * row_bytes + t * 8;
-    const uint8_t* c_hi = p.codes + (size_t)r_hi * row_bytes + t * 8;
+    const uint8_t* c_lo = pr.codes + (size_t)r_lo * row_bytes + t * 8;
+    const uint8_t* c_hi = pr.codes + (size_t)r_hi * row_bytes + t * 8;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
     // k-blocks in batches of GV_BATCH: all of a batch's code and scale loads are issued before the
-    // first one is used, so a warp pays the HBM latency once per batch, not once per k-block
-    for (int kb0 = kb_begin; kb0 < kb_end; kb0 += GV_BATCH) {
-        uint2 q_lo[GV_BATCH], q_hi[GV_BATCH];
-        __half s_lo[GV_BATCH], s_hi[GV_BATCH];
+    // first one is used, so a warp pays the memory latency once per batch, not once per k-block.
+    // The first batch goes out before the table look-up is built, so that the table's own loads
+    // share its round trip instead of preceding it.
+    uint2 q_lo[GV_BATCH], q_hi[GV_BATCH];
+    __half s_lo[GV_BATCH], s_hi[GV_BATCH];
+    auto issue = [&](int kb0) {
 #pragma unroll
         for (int b = 0; b < GV_BATCH; ++b) {
             const int kb = min(kb0 + b, kb_end - 1);  // (tail: re-reads the last block, unused)
             // this thread's 16 weights of rows r_lo and r_hi: k = kb*64 + 16t .. + 15
             q_lo[b] = __ldg(reinterpret_cast<const uint2*>(c_lo + (size_t)kb * 32));
             q_hi[b] = __ldg(reinterpret_cast<const uint2*>(c_hi + (size_t)kb * 32));
-            s_lo[b] = __ldg(p.scales16 + (size_t)kb * p.n_w + r_lo);
-            s_hi[b] = __ldg(p.scales16 + (size_t)kb * p.n_w + r_hi);
+            s_lo[b] = __ldg(pr.scales16 + (size_t)kb * pr.n_w + r_lo);
+            s_hi[b] = __ldg(pr.scales16 + (size_t)kb * pr.n_w + r_hi);
         }
+    };
+    if (kb_begin < kb_end) issue(kb_begin);
+    const RegLut lut = load_reg_lut(pr.code16);
+
+    for (int kb0 = kb_begin; kb0 < kb_end; kb0 += GV_BATCH) {
+        if (kb0 != kb_begin) issue(kb0);
 #pragma unroll
         for (int b = 0; b < GV_BATCH; ++b) {
             const int kb = kb0 + b;
@@ -141,9 +205,9 @@ nf4_gemv_kernel(const GemvParams p) {
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < GV_WARPS; ++w) v += red[w][token][r];
-        if (p.ext_a != nullptr) {
-            const __half2* xa = reinterpret_cast<const __half2*>(p.ext_a + (long long)token * 16);
-            const __half2* lb = reinterpret_cast<const __half2*>(p.ext_b + (long long)(r0 + r) * 16);
+        if (pr.ext_a != nullptr) {
+            const __half2* xa = reinterpret_cast<const __half2*>(pr.ext_a + (long long)token * 16);
+            const __half2* lb = reinterpret_cast<const __half2*>(pr.ext_b + (long long)(r0 + r) * 16);
             float s = 0.f;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -153,50 +217,246 @@ nf4_gemv_kernel(const GemvParams p) {
             }
             v += s;
         }
-        if (p.bias != nullptr) v += __half2float(__ldg(p.bias + r0 + r));
-        p.out[(long long)token * p.ld_out + r0 + r] = __float2half_rn(v);
+        if (pr.bias != nullptr) v += __half2float(__ldg(pr.bias + r0 + r));
+        pr.out[(long long)token * pr.ld_out + r0 + r] = __float2half_rn(v);
     }
+}
+
+// ------------------------------------------------------------------------------------ backward
+
+constexpr int GB_BATCH = 4;   // 16-row steps whose loads are in flight together
+
+// grid = (k-blocks, row slabs over the whole group); a CTA's warps take the 16-row steps of its
+// slab in turn. The slab's sums go to an fp32 plane; the split-K reduction kernel adds the planes.
+template <int GB_WARPS>
+__global__ void __launch_bounds__(GB_WARPS * 32)
+nf4_gemv_bwd_kernel(const __grid_constant__ GemvParams p) {
+    const int kb = (int)blockIdx.x;
+    const int slab = (int)blockIdx.y;
+    const int pi = gemv_find(p, slab);
+    const GemvProblem& pr = p.prob[pi];
+    const int row0 = (slab - pr.first) * p.rows_per_slab;          // first row of the slab
+    const int row_end = min(row0 + p.rows_per_slab, pr.n_w);
+    const size_t row_bytes = (size_t)p.k_w >> 1;
+    grid_dep_wait();
+    grid_dep_launch();
+    __shared__ float red[GB_WARPS][16][64 + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    const RegLut lut = load_reg_lut(pr.code16);
+    float acc[8][4];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) acc[c][0] = acc[c][1] = acc[c][2] = acc[c][3] = 0.f;
+
+    // this lane's word of the k-block: columns kb*64 + 8g .. + 7
+    const uint8_t* cbase = pr.codes + (size_t)kb * 32 + (size_t)g * 4;
+    const __half* sbase = pr.scales16 + (size_t)kb * pr.n_w;
+    const __half* a_lo = pr.act + (long long)g * pr.ld_act;        // token g
+    const __half* a_hi = pr.act + (long long)(g + 8) * pr.ld_act;  // token g + 8
+    const bool lo_ok = g < p.m, hi_ok = g + 8 < p.m;
+
+    const int n_steps = (row_end - row0 + 15) / 16;   // n_w % 16 == 0: whole steps
+    for (int s0 = warp * GB_BATCH; s0 < n_steps; s0 += GB_WARPS * GB_BATCH) {
+        uint32_t code[GB_BATCH][4];
+        uint32_t sc[GB_BATCH][2], av[GB_BATCH][4];
+#pragma unroll
+        for (int b = 0; b < GB_BATCH; ++b) {
+            const int st = min(s0 + b, n_steps - 1);              // (tail: re-read, unused)
+            const int n = row0 + st * 16 + 2 * t;                 // rows n, n+1, n+8, n+9
+            const uint8_t* c0 = cbase + (size_t)n * row_bytes;
+            code[b][0] = __ldg(reinterpret_cast<const uint32_t*>(c0));
+            code[b][1] = __ldg(reinterpret_cast<const uint32_t*>(c0 + row_bytes));
+            code[b][2] = __ldg(reinterpret_cast<const uint32_t*>(c0 + 8 * row_bytes));
+            code[b][3] = __ldg(reinterpret_cast<const uint32_t*>(c0 + 9 * row_bytes));
+            sc[b][0] = __ldg(reinterpret_cast<const uint32_t*>(sbase + n));      // scales of n, n+1
+            sc[b][1] = __ldg(reinterpret_cast<const uint32_t*>(sbase + n + 8));  // of n+8, n+9
+            av[b][0] = lo_ok ? __ldg(reinterpret_cast<const uint32_t*>(a_lo + n)) : 0u;
+            av[b][1] = hi_ok ? __ldg(reinterpret_cast<const uint32_t*>(a_hi + n)) : 0u;
+            av[b][2] = lo_ok ? __ldg(reinterpret_cast<const uint32_t*>(a_lo + n + 8)) : 0u;
+            av[b][3] = hi_ok ? __ldg(reinterpret_cast<const uint32_t*>(a_hi + n + 8)) : 0u;
+        }
+#pragma unroll
+        for (int b = 0; b < GB_BATCH; ++b) {
+            if (s0 + b >= n_steps) break;
+            uint32_t w[4][4];   // w[row][pair]: columns (2j, 2j+1) of the word, scaled
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const uint32_t s32 = sc[b][r >> 1];
+                const uint32_t dup = (r & 1) ? __byte_perm(s32, 0u, 0x3232u) : __byte_perm(s32, 0u, 0x1010u);
+                const uint4 d = decode_word_reg(code[b][r], lut, *reinterpret_cast<const __half2*>(&dup));
+                w[r][0] = d.x; w[r][1] = d.y; w[r][2] = d.z; w[r][3] = d.w;
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const uint32_t sel = (c & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = __byte_perm(w[0][c >> 1], w[1][c >> 1], sel);  // rows n, n+1
+                const uint32_t b1 = __byte_perm(w[2][c >> 1], w[3][c >> 1], sel);  // rows n+8, n+9
+                mma_16816(acc[c], av[b][0], av[b][1], av[b][2], av[b][3], b0, b1);
+            }
+        }
+    }
+
+    // acc[c]: d0,d1 -> (token g, words 2t, 2t+1); d2,d3 -> (token g+8, same); column of (word j,
+    // position c) = 8j + c
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        red[warp][g][16 * t + c] = acc[c][0];
+        red[warp][g][16 * t + 8 + c] = acc[c][1];
+        red[warp][g + 8][16 * t + c] = acc[c][2];
+        red[warp][g + 8][16 * t + 8 + c] = acc[c][3];
+    }
+    __syncthreads();
+    float* plane = p.planes + (size_t)slab * ((size_t)p.m * (size_t)p.ldp);
+    for (int e = threadIdx.x; e < 16 * 64; e += GB_WARPS * 32) {
+        const int token = e >> 6, col = e & 63;
+        if (token >= p.m) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < GB_WARPS; ++w) v += red[w][token][col];
+        const int kcol = kb * 64 + col;
+        if (pr.ext_a != nullptr && slab == pr.first) {   // u . lora_a, once per member
+            float s = 0.f;
+#pragma unroll
+            for (int r = 0; r < 16; ++r)
+                s = fmaf(__half2float(__ldg(pr.ext_a + (long long)token * 16 + r)),
+                         __half2float(__ldg(pr.ext_b + (long long)r * p.k_w + kcol)), s);
+            v += s;
+        }
+        plane[(size_t)token * p.ldp + kcol] = v;
+    }
+}
+
+// ------------------------------------------------------------------------------------ host side
+
+static bool gemv_common_ok(const GemmArgs& a) {
+    return a.scales16 != nullptr && a.n_w % GV_ROWS == 0 && a.k_w % 64 == 0 &&
+           (reinterpret_cast<uintptr_t>(a.codes) & 7) == 0;
 }
 
 bool gemv_eligible(const GemmArgs& a) {
     // measured against the tensor-core kernel: always ahead up to 16 rows; up to 64 rows only for
     // the small projections (the activations are re-read through L1/L2 once per 16 weight rows)
     const bool small_enough = a.m <= 16 || (a.m <= 64 && a.n_w * a.k_w <= (1ll << 22));
-    return !a.trans_w && a.m >= 1 && small_enough && a.scales16 != nullptr && a.n_w % GV_ROWS == 0 &&
-           a.k_w % 64 == 0 && a.ld_act % 8 == 0 && (reinterpret_cast<uintptr_t>(a.act) & 15) == 0 &&
-           (reinterpret_cast<uintptr_t>(a.codes) & 7) == 0;
+    return !a.trans_w && a.m >= 1 && small_enough && gemv_common_ok(a) && a.ld_act % 8 == 0 &&
+           (reinterpret_cast<uintptr_t>(a.act) & 15) == 0;
+}
+
+bool gemv_bwd_eligible(const GemmArgs& a) {
+    return a.trans_w && a.m >= 1 && a.m <= 16 && gemv_common_ok(a) && a.ld_act % 2 == 0 &&
+           (reinterpret_cast<uintptr_t>(a.act) & 3) == 0 &&
+           (reinterpret_cast<uintptr_t>(a.scales16) & 3) == 0;
+}
+
+static void fill_problem(GemvProblem& q, const GemmArgs& a) {
+    q.codes = a.codes; q.scales16 = a.scales16; q.code16 = a.code16; q.bias = a.bias;
+    q.ext_a = a.ext_a; q.ext_b = a.ext_b; q.act = a.act; q.out = a.out;
+    q.ld_out = a.ld_out; q.ld_act = a.ld_act; q.n_w = (int)a.n_w; q.first = 0;
 }
 
 template <int NT, int WARPS>
-static cudaError_t launch_gemv_t(const GemvParams& p, cudaStream_t stream) {
-    return launch_pdl(nf4_gemv_kernel<NT, WARPS>, dim3((unsigned)(p.n_w / GV_ROWS)), dim3(WARPS * 32), 0,
-                      stream, p);
+static cudaError_t launch_gemv_t(const GemvParams& p, unsigned ctas, cudaStream_t stream) {
+    return launch_pdl(nf4_gemv_kernel<NT, WARPS>, dim3(ctas), dim3(WARPS * 32), 0, stream, p);
 }
 
-cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t stream) {
-    GemvParams p;
-    p.codes = a.codes; p.scales16 = a.scales16; p.code16 = a.code16; p.act = a.act;
-    p.bias = a.bias; p.ext_a = a.ext_a; p.ext_b = a.ext_b; p.out = a.out;
-    p.ld_act = a.ld_act; p.ld_out = a.ld_out;
-    p.m = (int)a.m; p.n_w = (int)a.n_w; p.k_w = (int)a.k_w;
+cudaError_t launch_gemv_group(const GemmGroupArgs& ga, cudaStream_t stream) {
+    const GemmArgs& a = ga.item[0];
+    GemvParams p = {};
+    p.n_prob = ga.count;
+    p.act = a.act; p.ld_act = a.ld_act;
+    p.m = (int)a.m; p.k_w = (int)a.k_w;
+    p.prefetch = 1;
+    long long ctas = 0;
+    for (int i = 0; i < ga.count; ++i) {
+        fill_problem(p.prob[i], ga.item[i]);
+        p.prob[i].first = (int)ctas;
+        ctas += ga.item[i].n_w / GV_ROWS;
+        if ((reinterpret_cast<uintptr_t>(ga.item[i].codes) & 15) != 0 || ((a.k_w / 2) * GV_ROWS) % 16 != 0)
+            p.prefetch = 0;
+    }
+    for (int i = ga.count; i < GV_MAXP; ++i) p.prob[i] = p.prob[0];
     // Warps per CTA: with many row groups, small CTAs so that all of them are resident at once
     // (a second round of CTAs costs as much as the first); with few row groups and long rows,
     // 16 warps to spread K.
-    const long long ctas = a.n_w / GV_ROWS;
     const int sms = a.sm_count > 0 ? a.sm_count : 148;
     const int warps = ctas >= 3ll * sms ? 4 : (a.k_w >= 4096 && ctas < 2ll * sms ? 16 : 8);
+    const unsigned grid = (unsigned)ctas;
     if (a.m <= 8) {
-        if (warps == 4) return launch_gemv_t<1, 4>(p, stream);
-        if (warps == 16) return launch_gemv_t<1, 16>(p, stream);
-        return launch_gemv_t<1, 8>(p, stream);
+        if (warps == 4) return launch_gemv_t<1, 4>(p, grid, stream);
+        if (warps == 16) return launch_gemv_t<1, 16>(p, grid, stream);
+        return launch_gemv_t<1, 8>(p, grid, stream);
     }
     if (a.m <= 16) {
-        if (warps == 4) return launch_gemv_t<2, 4>(p, stream);
-        if (warps == 16) return launch_gemv_t<2, 16>(p, stream);
-        return launch_gemv_t<2, 8>(p, stream);
+        if (warps == 4) return launch_gemv_t<2, 4>(p, grid, stream);
+        if (warps == 16) return launch_gemv_t<2, 16>(p, grid, stream);
+        return launch_gemv_t<2, 8>(p, grid, stream);
     }
-    if (a.m <= 32) return launch_gemv_t<4, 8>(p, stream);
-    return launch_gemv_t<8, 8>(p, stream);
+    if (a.m <= 32) return launch_gemv_t<4, 8>(p, grid, stream);
+    return launch_gemv_t<8, 8>(p, grid, stream);
+}
+
+cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t stream) {
+    GemmGroupArgs ga;
+    ga.count = 1;
+    ga.item[0] = a;
+    return launch_gemv_group(ga, stream);
+}
+
+// Row slabs of the streaming backward: enough CTAs (k-blocks x slabs) for about three per SM, slabs
+// of whole 16-row steps for every warp.
+constexpr int GB_WARPS_PER_CTA = 8;
+
+StreamBwdPlan plan_stream_bwd(long long m, const long long* n_w, int count, long long k_w, int sm_count) {
+    StreamBwdPlan pl = {};
+    const long long nkb = k_w / 64;
+    long long total_rows = 0;
+    for (int i = 0; i < count; ++i) total_rows += n_w[i];
+    const int sms = sm_count > 0 ? sm_count : 148;
+    long long want = (3ll * sms + nkb - 1) / nkb;              // slabs wanted over the group
+    if (want < 1) want = 1;
+    const long long unit = 16ll * GB_WARPS_PER_CTA;             // one step per warp at least
+    long long rows = (total_rows + want - 1) / want;
+    rows = (rows + unit - 1) / unit * unit;
+    pl.rows_per_slab = (int)rows;
+    int slabs = 0;
+    for (int i = 0; i < count; ++i) {
+        pl.first[i] = slabs;
+        slabs += (int)((n_w[i] + rows - 1) / rows);
+    }
+    pl.slabs = slabs;
+    pl.ldp = (k_w + 3) / 4 * 4;
+    pl.ws_bytes = (size_t)slabs * (size_t)m * (size_t)pl.ldp * sizeof(float);
+    return pl;
+}
+
+cudaError_t launch_gemv_bwd_group(const GemmGroupArgs& ga, cudaStream_t stream, const char** why) {
+    const GemmArgs& a = ga.item[0];
+    long long n_w[GEMM_MAX_GROUP];
+    for (int i = 0; i < ga.count; ++i) n_w[i] = ga.item[i].n_w;
+    const StreamBwdPlan pl = plan_stream_bwd(a.m, n_w, ga.count, a.k_w, a.sm_count);
+    if (a.workspace == nullptr || a.workspace_bytes < pl.ws_bytes) {
+        *why = "small-M backward: workspace too small";
+        return cudaErrorInvalidValue;
+    }
+    GemvParams p = {};
+    p.n_prob = ga.count;
+    p.m = (int)a.m; p.k_w = (int)a.k_w;
+    p.planes = static_cast<float*>(a.workspace);
+    p.ldp = pl.ldp;
+    p.rows_per_slab = pl.rows_per_slab;
+    for (int i = 0; i < ga.count; ++i) {
+        fill_problem(p.prob[i], ga.item[i]);
+        p.prob[i].first = pl.first[i];
+    }
+    for (int i = ga.count; i < GV_MAXP; ++i) p.prob[i] = p.prob[0];
+    cudaError_t e = launch_pdl(nf4_gemv_bwd_kernel<GB_WARPS_PER_CTA>,
+                               dim3((unsigned)(a.k_w / 64), (unsigned)pl.slabs), dim3(GB_WARPS_PER_CTA * 32),
+                               0, stream, p);
+    if (e != cudaSuccess) { *why = "small-M backward kernel launch"; return e; }
+    e = launch_splitk_reduce(p.planes, a.m, a.k_w, pl.ldp, pl.slabs, nullptr, a.out, a.ld_out,
+                             a.sm_count, stream);
+    if (e != cudaSuccess) *why = "small-M backward reduce launch";
+    return e;
 }
 
 }  // namespace nf4

@@ -198,9 +198,25 @@ struct CeArgs {
 };
 cudaError_t launch_ce(const CeArgs& a, cudaStream_t stream);
 
-// Weight-streaming forward kernel for M <= 64 (gemv.cu); launch_gemm* route eligible calls to it.
+// Weight-streaming kernels for a handful of token rows (gemv.cu); launch_gemm* route eligible
+// calls to them: forward for M <= 64 (a whole group in one launch), backward for M <= 16.
 bool gemv_eligible(const GemmArgs& a);
+bool gemv_bwd_eligible(const GemmArgs& a);
 cudaError_t launch_gemv(const GemmArgs& a, cudaStream_t stream);
+cudaError_t launch_gemv_group(const GemmGroupArgs& ga, cudaStream_t stream);
+cudaError_t launch_gemv_bwd_group(const GemmGroupArgs& ga, cudaStream_t stream, const char** why);
+// Row slabs of the streaming backward and the fp32 planes they need as scratch.
+struct StreamBwdPlan {
+    int rows_per_slab, slabs;
+    int first[GEMM_MAX_GROUP];   // first slab of each member
+    long long ldp;
+    size_t ws_bytes;
+};
+StreamBwdPlan plan_stream_bwd(long long m, const long long* n_w, int count, long long k_w, int sm_count);
+// out[m, n_out] = fp16(sum of `splits` fp32 planes [m][ldp] (+ bias)): the split-K reduction (gemm.cu).
+cudaError_t launch_splitk_reduce(const float* planes, long long m, long long n_out, long long ldp,
+                                 int splits, const __half* bias, __half* out, long long ld_out,
+                                 int sm_count, cudaStream_t stream);
 
 struct LoraDownArgs {
     const __half* in;

@@ -126,3 +126,58 @@ def test_code_ring_hand_back_under_load(cuda_lib, nested):
             finally:
                 nf4.PREPARED_SCALES = True
     assert cuda_lib.device_status() == 0
+
+
+@pytest.mark.parametrize("m", [1, 4, 5, 16])
+@pytest.mark.parametrize("n,k", [(1536, 1536), (256, 1536), (1536, 8960), (8960, 1536), (48, 64)])
+def test_small_m_backward_vs_oracle(cuda_lib, m, n, k):
+    """dX = dY . W for up to 16 token rows: the weight-streaming backward kernel (row slabs summed
+    as fp32 planes) against the oracle, twice (the scratch needs no clearing between calls)."""
+    from hackaton_b200.nf4 import linear_backward_dx
+
+    packed, state = synthetic_weight(n, k, True, seed=n + 3 * m, device="cuda")
+    w = oracle_weight(packed, state)
+    g = torch.Generator().manual_seed(m)
+    dy = torch.randn(m, n, generator=g).half()
+    want = nf4_oracle.linear_bwd(dy, w)
+    for _ in range(2):
+        dx = linear_backward_dx(dy.cuda(), packed, state)
+        assert nf4_oracle.max_rel_err(dx.cpu(), want) <= TOL
+    assert cuda_lib.device_status() == 0
+
+
+@pytest.mark.parametrize("m", [1, 7, 16, 40])
+def test_small_m_group_with_lora(cuda_lib, m):
+    """q/k/v sharing one input at decode-like token counts: one streaming launch forward (three
+    outputs, LoRA on q and v), one backward (summed dX with both LoRA shares), through autograd."""
+    from hackaton_b200 import Projection, nf4_linear_group
+
+    k = 1536
+    g = torch.Generator().manual_seed(11 + m)
+    x = torch.randn(m, k, generator=g).half()
+    projs, refs, grads = [], [], []
+    for i, n in enumerate((1536, 256, 256)):
+        packed, state = synthetic_weight(n, k, True, seed=50 + i, device="cuda")
+        w = oracle_weight(packed, state)
+        a = b = None
+        if i != 1:
+            a = ((torch.rand(16, k, generator=g) * 2 - 1) / k ** 0.5).half()
+            b = (torch.randn(n, 16, generator=g) * 0.1).half()
+        projs.append(Projection(packed, state, None, None if a is None else a.cuda().requires_grad_(),
+                                None if b is None else b.cuda().requires_grad_(), 2.0))
+        refs.append((w, a, b))
+        grads.append(torch.randn(m, n, generator=g).half())
+    xg = x.cuda().requires_grad_()
+    ys = nf4_linear_group(xg, projs)
+    torch.autograd.backward(list(ys), [d.cuda() for d in grads])
+    dx_ref = torch.zeros(m, k)
+    for y, (w, a, b), dy in zip(ys, refs, grads):
+        if a is None:
+            want = nf4_oracle.linear_fwd(x, w)
+            dx_ref += nf4_oracle.linear_bwd(dy, w).float()
+        else:
+            want, _ = nf4_oracle.lora_fwd(x, w, a, b, 2.0)
+            dx_ref += nf4_oracle.lora_bwd(dy, x, w, a, b, 2.0)[0].float()
+        assert nf4_oracle.max_rel_err(y.detach().cpu(), want) <= TOL
+    assert nf4_oracle.max_rel_err(xg.grad.cpu(), dx_ref) <= TOL
+    assert cuda_lib.device_status() == 0
