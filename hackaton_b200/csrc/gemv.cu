@@ -23,8 +23,9 @@
 // one column) is a byte-permute of two of its own decoded words. A (the upstream gradient,
 // row-major over the contraction) is loaded as plain fragments. A thread ends up with 16
 // consecutive output columns of tokens g and g + 8. Row slabs are summed in two steps: the
-// warps of a CTA through shared memory, the CTAs of a k-block as fp32 planes that the split-K
-// reduction kernel adds in slab order (deterministic).
+// warps of a CTA through shared memory, the CTAs of a k-block as fp32 planes in caller-provided
+// scratch, which the last CTA of the k-block to finish (a ticket counter) adds in slab order
+// (deterministic) and writes out as fp16.
 //
 // Both kernels ask for their slab of codes to be brought into L2 before they wait for the
 // previous kernel of the stream (programmatic dependent launch): a prefetch reads no values, so
@@ -35,6 +36,8 @@
 // N % 16 == 0; other calls take the tcgen05 kernel.
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "decode.cuh"
 #include "kernels.h"
 #include "ptx.cuh"
@@ -42,7 +45,10 @@
 namespace nf4 {
 
 constexpr int GV_ROWS = 16;
-constexpr int GV_BATCH = 4;
+#ifndef GV_BATCH_N
+#define GV_BATCH_N 4
+#endif
+constexpr int GV_BATCH = GV_BATCH_N;
 constexpr int GV_MAXP = GEMM_MAX_GROUP;
 
 struct GemvProblem {
@@ -67,6 +73,8 @@ struct GemvParams {
     long long ldp;
     int n_prob, m, k_w;
     int rows_per_slab;       // backward: weight rows per CTA (multiple of 16 * warps)
+    int ticket_base;         // backward: first ticket of this launch, or -1 (reduction by a second kernel)
+    int n_slabs;
     int prefetch;            // codes are 16-byte aligned: bulk L2 prefetch is legal
 };
 
@@ -128,7 +136,15 @@ nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
     const int nkb = p.k_w >> 6;
+#ifdef GV_INTERLEAVE
+    // warps take the k-blocks in turn: at any moment the warps of a CTA read neighbouring 32-byte
+    // pieces of the same 128-byte lines
+    const int kb_begin = warp, kb_end = nkb;
+    constexpr int KB_STEP = GV_WARPS;
+#else
     const int kb_begin = nkb * warp / GV_WARPS, kb_end = nkb * (warp + 1) / GV_WARPS;
+    constexpr int KB_STEP = 1;
+#endif
     const uint8_t* c_lo = pr.codes + (size_t)r_lo * row_bytes + t * 8;
     const uint8_t* c_hi = pr.codes + (size_t)r_hi * row_bytes + t * 8;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
@@ -142,7 +158,7 @@ nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
     auto issue = [&](int kb0) {
 #pragma unroll
         for (int b = 0; b < GV_BATCH; ++b) {
-            const int kb = min(kb0 + b, kb_end - 1);  // (tail: re-reads the last block, unused)
+            const int kb = min(kb0 + b * KB_STEP, kb_end - 1);  // (tail: re-reads the last block, unused)
             // this thread's 16 weights of rows r_lo and r_hi: k = kb*64 + 16t .. + 15
             q_lo[b] = __ldg(reinterpret_cast<const uint2*>(c_lo + (size_t)kb * 32));
             q_hi[b] = __ldg(reinterpret_cast<const uint2*>(c_hi + (size_t)kb * 32));
@@ -153,11 +169,11 @@ nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
     if (kb_begin < kb_end) issue(kb_begin);
     const RegLut lut = load_reg_lut(pr.code16);
 
-    for (int kb0 = kb_begin; kb0 < kb_end; kb0 += GV_BATCH) {
+    for (int kb0 = kb_begin; kb0 < kb_end; kb0 += GV_BATCH * KB_STEP) {
         if (kb0 != kb_begin) issue(kb0);
 #pragma unroll
         for (int b = 0; b < GV_BATCH; ++b) {
-            const int kb = kb0 + b;
+            const int kb = kb0 + b * KB_STEP;
             if (kb >= kb_end) break;
             uint32_t wl[8], wh[8];
             {
@@ -225,6 +241,13 @@ nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
 // ------------------------------------------------------------------------------------ backward
 
 constexpr int GB_BATCH = 4;   // 16-row steps whose loads are in flight together
+
+// One ticket per k-block of a launch in flight: the CTA that takes the last ticket of its k-block
+// adds the slabs' planes and writes the result, so small problems need no second kernel. The
+// tickets start at zero (module load) and the last arriver puts its ticket back to zero. Launches
+// get their span of tickets in turn; TICKET_LAUNCHES launches may be in flight at once.
+constexpr int TICKET_LAUNCHES = 64, TICKET_SPAN = 512;
+__device__ unsigned g_gemv_tickets[TICKET_LAUNCHES * TICKET_SPAN];
 
 // grid = (k-blocks, row slabs over the whole group); a CTA's warps take the 16-row steps of its
 // slab in turn. The slab's sums go to an fp32 plane; the split-K reduction kernel adds the planes.
@@ -307,7 +330,8 @@ nf4_gemv_bwd_kernel(const __grid_constant__ GemvParams p) {
         red[warp][g + 8][16 * t + 8 + c] = acc[c][3];
     }
     __syncthreads();
-    float* plane = p.planes + (size_t)slab * ((size_t)p.m * (size_t)p.ldp);
+    const size_t plane_elems = (size_t)p.m * (size_t)p.ldp;
+    float* plane = p.planes + (size_t)slab * plane_elems;
     for (int e = threadIdx.x; e < 16 * 64; e += GB_WARPS * 32) {
         const int token = e >> 6, col = e & 63;
         if (token >= p.m) continue;
@@ -323,7 +347,31 @@ nf4_gemv_bwd_kernel(const __grid_constant__ GemvParams p) {
                          __half2float(__ldg(pr.ext_b + (long long)r * p.k_w + kcol)), s);
             v += s;
         }
-        plane[(size_t)token * p.ldp + kcol] = v;
+        __stcg(plane + (size_t)token * p.ldp + kcol, v);
+    }
+    if (p.ticket_base < 0) return;   // a reduction kernel follows
+    // Last arriver of this k-block: every thread makes its plane writes visible device-wide, then
+    // one thread takes the ticket.
+    __shared__ int is_last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* ticket = g_gemv_tickets + p.ticket_base + kb;
+        const unsigned old = atomicAdd(ticket, 1u);
+        is_last = old == (unsigned)(p.n_slabs - 1) ? 1 : 0;
+        if (is_last) *ticket = 0u;   // (nobody else touches it any more in this launch)
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    __half* out = p.prob[0].out;
+    for (int e = threadIdx.x; e < 16 * 64; e += GB_WARPS * 32) {
+        const int token = e >> 6, col = e & 63;
+        if (token >= p.m) continue;
+        const size_t off = (size_t)token * p.ldp + (size_t)(kb * 64 + col);
+        float v = 0.f;
+        for (int z = 0; z < p.n_slabs; ++z) v += __ldcg(p.planes + (size_t)z * plane_elems + off);
+        out[(long long)token * p.prob[0].ld_out + kb * 64 + col] = __float2half_rn(v);
     }
 }
 
@@ -444,6 +492,12 @@ cudaError_t launch_gemv_bwd_group(const GemmGroupArgs& ga, cudaStream_t stream, 
     p.planes = static_cast<float*>(a.workspace);
     p.ldp = pl.ldp;
     p.rows_per_slab = pl.rows_per_slab;
+    p.n_slabs = pl.slabs;
+    const long long nkb = a.k_w / 64;
+    static std::atomic<unsigned> cursor{0};
+    p.ticket_base = nkb <= TICKET_SPAN
+        ? (int)((cursor.fetch_add(1u, std::memory_order_relaxed) % TICKET_LAUNCHES) * TICKET_SPAN)
+        : -1;
     for (int i = 0; i < ga.count; ++i) {
         fill_problem(p.prob[i], ga.item[i]);
         p.prob[i].first = pl.first[i];
@@ -453,6 +507,7 @@ cudaError_t launch_gemv_bwd_group(const GemmGroupArgs& ga, cudaStream_t stream, 
                                dim3((unsigned)(a.k_w / 64), (unsigned)pl.slabs), dim3(GB_WARPS_PER_CTA * 32),
                                0, stream, p);
     if (e != cudaSuccess) { *why = "small-M backward kernel launch"; return e; }
+    if (p.ticket_base >= 0) return e;
     e = launch_splitk_reduce(p.planes, a.m, a.k_w, pl.ldp, pl.slabs, nullptr, a.out, a.ld_out,
                              a.sm_count, stream);
     if (e != cudaSuccess) *why = "small-M backward reduce launch";
