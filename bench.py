@@ -873,6 +873,30 @@ def run_single(args):
         ce[key] = {"us": us, "gbs": gbs, "frac_of_hbm": gbs / pk["hbm_gbs"], "bytes_per_element": bytes_per_elem}
     del ce_logits, ce_grad_out
 
+    # ---- the lm_head products of one chunk of the chunked loss (256 rows against the 151,936 x
+    # 1536 fp16 table: 467 MB, re-read from HBM by every launch) through the library's kernel,
+    # with torch's library GEMM timed beside them
+    from hackaton_b200.dense import fp16_linear
+    lm_rows, lm_hidden = 256, 1536
+    lm_w = torch.randn(ce_vocab, lm_hidden, device=device, dtype=torch.float16)
+    lm_w *= 0.02
+    lm_h = [torch.randn(lm_rows, lm_hidden, device=device, dtype=torch.float16) for _ in range(2)]
+    lm_g = [torch.randn(lm_rows, ce_vocab, device=device, dtype=torch.float16) for _ in range(2)]
+    lm_flops = 2.0 * lm_rows * ce_vocab * lm_hidden
+    lm_bytes = 2.0 * (ce_vocab * lm_hidden + lm_rows * ce_vocab + lm_rows * lm_hidden)
+    lm = {"rows": lm_rows, "vocab": ce_vocab, "hidden": lm_hidden, "tensor_peak_tflops": pk["tflops_burst"],
+          "hbm_peak_gbs": pk["hbm_gbs"]}
+    for key, fn in (
+            ("logits", lambda i: fp16_linear(lm_h[i % 2], lm_w)),
+            ("d_hidden", lambda i: fp16_linear(lm_g[i % 2], lm_w, transposed=True)),
+            ("logits_library_gemm", lambda i: torch.nn.functional.linear(lm_h[i % 2], lm_w)),
+            ("d_hidden_library_gemm", lambda i: torch.mm(lm_g[i % 2], lm_w))):
+        us = time_kernel(fn) * 1e3
+        lm[key] = {"us": us, "tflops": lm_flops / (us * 1e-6) / 1e12,
+                   "frac_of_tensor_peak": lm_flops / (us * 1e-6) / 1e12 / pk["tflops_burst"],
+                   "frac_of_hbm": lm_bytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"]}
+    del lm_w, lm_h, lm_g
+
     # ---- standalone decode (codes + two-level scales -> fp16 weights), HBM bound:
     # 0.515869 B read + 2 B written per weight, rotating over the 28 layers' weights
     from hackaton_b200.nf4 import dequantize_nf4
@@ -1027,7 +1051,7 @@ def run_single(args):
         "frac_of_sustained_tensor_peak": value / pk["tflops_sustained"],
         "ms_per_28_layer_step": total_ms / args.steps * N_LAYERS,
         "peak_hbm_mib": peak_mem, "cuda_graphs": use_graphs, "dequant": dq, "small_m": small,
-        "packed_varlen": varlen, "sustained": step_sustained, "swiglu": sw, "rmsnorm": rn, "rope": rp, "cross_entropy": ce,
+        "packed_varlen": varlen, "sustained": step_sustained, "swiglu": sw, "rmsnorm": rn, "rope": rp, "cross_entropy": ce, "lm_head": lm,
         "step_ms_min_med_max": [min(per_step), statistics.median(per_step), max(per_step)],
         "roofline": roofline, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,

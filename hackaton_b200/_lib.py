@@ -22,7 +22,7 @@ EXPORTS = (
     "nf4b200_set_sm_limit", "nf4b200_gate_up_swiglu_fwd", "nf4b200_gate_up_swiglu_workspace_bytes",
     "nf4b200_swiglu_fwd", "nf4b200_swiglu_bwd", "nf4b200_linear_bwd_dx_swiglu",
     "nf4b200_linear_bwd_dx_swiglu_workspace_bytes", "nf4b200_rmsnorm_fwd", "nf4b200_rmsnorm_bwd",
-    "nf4b200_qkv_rotate", "nf4b200_ce_stats", "nf4b200_ce_grad", "nf4b200_selftest_wait",
+    "nf4b200_qkv_rotate", "nf4b200_ce_stats", "nf4b200_ce_grad", "nf4b200_selftest_wait", "nf4b200_fp16_linear",
 )
 
 F16, BF16, F32 = 0, 1, 2
@@ -68,6 +68,9 @@ def lib() -> ctypes.CDLL:
     handle.nf4b200_query.argtypes = [c_int, POINTER(Props)]
     handle.nf4b200_device_status.argtypes = [POINTER(c_int)]
     handle.nf4b200_selftest_wait.argtypes = [c_int64, c_void_p]
+    handle.nf4b200_fp16_linear.argtypes = [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64,
+                                           c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p,
+                                           c_size_t, c_void_p]
     handle.nf4b200_dequant.argtypes = [POINTER(Weight), c_void_p, c_int, c_void_p]
     handle.nf4b200_linear_fwd.argtypes = [POINTER(Weight), c_void_p, c_int64, c_int64, c_void_p,
                                           c_void_p, c_void_p, c_void_p, c_int64, c_void_p,

@@ -149,6 +149,8 @@ void fill_gemm(nf4::GemmArgs& g, const nf4b200_weight* w, int sms) {
     g.offset = w->offset;
     g.code16 = w->code16;
     g.scales16 = static_cast<const __half*>(w->scales16);
+    g.dense_w = nullptr;
+    g.ld_w = 0;
     g.n_w = w->n_rows;
     g.k_w = w->n_cols;
     g.nested = w->nested ? 1 : 0;
@@ -327,6 +329,44 @@ int nf4b200_linear_fwd(const nf4b200_weight* w, const void* x, int64_t m, int64_
     cudaError_t e = nf4::launch_gemm(g, static_cast<cudaStream_t>(stream), &why);
     if (e != cudaSuccess)
         return fail(NF4B200_ECUDA, "linear_fwd: %s: %s", why, cudaGetErrorString(e));
+    return NF4B200_OK;
+}
+
+int nf4b200_fp16_linear(const void* weight, int64_t n_rows, int64_t n_cols, int64_t ldw,
+                        const void* x, int64_t m, int64_t ldx, int transposed, const void* bias,
+                        void* y, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (!weight || !aligned16(weight)) return fail(NF4B200_EINVAL, "fp16_linear: weight is NULL or not 16-byte aligned");
+    if (n_rows <= 0 || n_cols <= 0 || n_rows > 0x7FFFFFFF || n_cols > 0x7FFFFFFF)
+        return fail(NF4B200_EINVAL, "fp16_linear: weight shape %lld x %lld", (long long)n_rows, (long long)n_cols);
+    if (ldw < n_cols || ldw % 8 != 0)
+        return fail(NF4B200_EINVAL, "fp16_linear: weight row stride %lld (needs >= %lld columns, multiple of 8)",
+                    (long long)ldw, (long long)n_cols);
+    if (n_cols % 8 != 0 || n_rows % 8 != 0)
+        return fail(NF4B200_EINVAL, "fp16_linear: weight dimensions must be multiples of 8");
+    const int64_t in_cols = transposed ? n_rows : n_cols, out_cols = transposed ? n_cols : n_rows;
+    if ((rc = check_act("x", x, m, ldx, in_cols)) != NF4B200_OK) return rc;
+    if (!y) return fail(NF4B200_EINVAL, "y is NULL");
+    if (ldy < out_cols) return fail(NF4B200_EINVAL, "y: row stride %lld < %lld columns", (long long)ldy,
+                                    (long long)out_cols);
+    if (transposed && bias) return fail(NF4B200_EINVAL, "fp16_linear: bias only with transposed = 0");
+    nf4::GemmArgs g = {};
+    g.dense_w = static_cast<const __half*>(weight);
+    g.ld_w = ldw;
+    g.n_w = n_rows; g.k_w = n_cols;
+    g.nested_blocksize = 1;
+    g.sm_count = gemm_sms(d);
+    g.act = static_cast<const __half*>(x); g.m = m; g.ld_act = ldx;
+    g.out = static_cast<__half*>(y); g.ld_out = ldy;
+    g.bias = static_cast<const __half*>(bias);
+    g.trans_w = transposed != 0;
+    if ((rc = set_workspace(g, workspace, workspace_bytes)) != NF4B200_OK) return rc;
+    const char* why = "";
+    cudaError_t e = nf4::launch_gemm(g, static_cast<cudaStream_t>(stream), &why);
+    if (e != cudaSuccess)
+        return fail(NF4B200_ECUDA, "fp16_linear: %s: %s", why, cudaGetErrorString(e));
     return NF4B200_OK;
 }
 

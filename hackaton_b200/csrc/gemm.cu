@@ -130,7 +130,10 @@ struct GemmMaps {
     CUtensorMap scales[MAXP]; // fp16 block scales [K_w / 64][N_w] (only when `prepared`)
 };
 
-template <int CG, int NACC, int STAGES, int TABLES_>
+// DENSE_ (plain fp16 weights brought by TMA, no decoding): the TMA warp runs ahead into the next
+// unit's weight slots while the epilogue is still staging, so the staging areas get a region of
+// their own (4 KB per producer warp) instead of borrowing the weight slots.
+template <int CG, int NACC, int STAGES, int TABLES_, bool DENSE_ = false>
 struct SmemLayout {
     static constexpr int NB = BN / CG;                 // weight-tile columns decoded by one CTA
     static constexpr int A_BYTES = NACC * 128 * BK * 2;
@@ -141,19 +144,21 @@ struct SmemLayout {
     static constexpr int TABLES = TABLES_;  // second-level tables kept in shared memory
     // Whatever the operand ring leaves free holds a second, deeper ring of packed codes and
     // ready-made block scales, so that their HBM latency stays out of the operand ring's cycle.
-    static constexpr int FIXED_BYTES = STAGES * STAGE_BYTES + 64 + 1024 * TABLES + 512 + 1024;
-    static constexpr int NC_FIT = (232448 - FIXED_BYTES) / (C_BYTES + S_BYTES);
-    static constexpr int NC = NC_FIT > 8 ? 8 : NC_FIT;
+    static constexpr int STAGING_BYTES = DENSE_ ? PRODUCER_WARPS * 4096 : 0;
+    static constexpr int FIXED_BYTES = STAGES * STAGE_BYTES + 64 + 1024 * TABLES + 512 + 1024 + STAGING_BYTES;
+    static constexpr int NC_FIT = DENSE_ ? 2 : (232448 - FIXED_BYTES) / (C_BYTES + S_BYTES);
+    static constexpr int NC = DENSE_ ? 2 : (NC_FIT > 8 ? 8 : NC_FIT);   // (dense: ring unused)
     static constexpr int CODES_OFF = STAGES * STAGE_BYTES;
-    static constexpr int SCALE_OFF = CODES_OFF + NC * C_BYTES;
-    static constexpr int META_OFF = SCALE_OFF + NC * S_BYTES;
+    static constexpr int SCALE_OFF = CODES_OFF + (DENSE_ ? 0 : NC * C_BYTES);
+    static constexpr int META_OFF = SCALE_OFF + (DENSE_ ? 0 : NC * S_BYTES);
     static constexpr int TABLE2_OFF = META_OFF + 64;
     static constexpr int BAR_OFF = TABLE2_OFF + 1024 * TABLES;
-    static constexpr int TOTAL = BAR_OFF + 512;
+    static constexpr int STAGING_OFF = BAR_OFF + 512;
+    static constexpr int TOTAL = STAGING_OFF + STAGING_BYTES;
     static constexpr int DYNAMIC_BYTES = TOTAL + 1024;  // slack for 1024-byte alignment
-    static_assert(NC >= 2, "no room for the code ring");
+    static_assert(NC_FIT >= 2, "no room for the code ring");
     static constexpr int WARPS_PER_W_SLOT = W_BYTES / 4096;  // 4 KB epilogue staging per warp
-    static_assert(STAGES * WARPS_PER_W_SLOT >= PRODUCER_WARPS, "staging needs more weight slots");
+    static_assert(DENSE_ || STAGES * WARPS_PER_W_SLOT >= PRODUCER_WARPS, "staging needs more weight slots");
     static_assert(DYNAMIC_BYTES <= 232448, "exceeds the 227 KB of shared memory per CTA");
 };
 
@@ -314,11 +319,15 @@ __device__ __forceinline__ int ext_problem(const GemmParams& p, int e) {
 
 // PREP = true: every problem comes with its scale table (known at compile time, so the hot loops
 // carry no trace of the gather path); PREP = false decides at run time from p.prepared.
-template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP, int EPI = 0>
+// DENSE: the weight is plain fp16 [n_w, k_w] (maps.codes[] describe it): its tiles arrive by TMA
+// in the very layout the decoding warps would have written, next to the activation tiles; the code
+// ring and the decoding loop are idle and the producer warps only run the epilogue.
+template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP, int EPI = 0,
+          bool DENSE = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmParams p) {
     const bool prepared = PREP || p.prepared != 0;
-    using L = SmemLayout<CG, NACC, STAGES, TABLES>;
+    using L = SmemLayout<CG, NACC, STAGES, TABLES, DENSE>;
     constexpr int NB = L::NB;
     // The 16 producer warps form 16 / DW groups of DW warps that take the k-blocks in turn (all 16
     // drain the accumulators): while one group publishes its tile (fence, barriers), the other is
@@ -337,7 +346,8 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
     // "operands ready" arrivals: the decoding warps of both CTAs, plus one from the peer CTA that
     // vouches for its activation tile
     // plus the leader's own TMA (its expect_tx arrive), so the issuers watch a single barrier
-    constexpr uint32_t W_ARRIVALS = CG * DW + (CG == 2 ? 1 : 0) + 1;
+    constexpr uint32_t W_ARRIVALS = (DENSE ? 0 : CG * DW) + (CG == 2 ? 1 : 0) + 1;
+    static_assert(!DENSE || EPI == 0, "dense weights: plain epilogue only");
     constexpr int NC = L::NC;
     // With two accumulators each has its own issuing thread (warps 17 and 19, different
     // schedulers): the tensor pipe queues only a couple of MMAs, so the barrier checks one
@@ -469,11 +479,24 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                         const int pi = TRANS_W ? find_problem(p, kbg) : w.prob;
                         const int kb = TRANS_W ? kbg - p.prob[pi].first : kbg;
                         const uint32_t landed = rank == 0 ? bar_full_w(s) : bar_full_tma(s);
-                        mbar_arrive_expect_tx(landed, L::A_BYTES);
+                        mbar_arrive_expect_tx(landed, L::A_BYTES + (DENSE ? L::W_BYTES : 0));
 #pragma unroll
                         for (int a = 0; a < NACC; ++a)
                             tma_load_2d(sa + a * (128 * BK * 2), &maps.act[TRANS_W ? pi : 0], kb * BK,
                                         w.m0 + a * (128 * CG) + (int)rank * 128, landed);
+                        if (DENSE) {
+                            // this CTA's half of the weight tile, as the decoding warps lay it out:
+                            // forward NB rows of n_w x 64 k_w; backward NB / 64 blocks of 64 n_w x 64 k_w
+                            const int nb0 = w.n0 + (int)rank * NB;
+                            const uint32_t wa = sa + L::A_BYTES;
+                            if (!TRANS_W) {
+                                tma_load_2d(wa, &maps.codes[pi], kb * BK, nb0, landed);
+                            } else {
+#pragma unroll
+                                for (int cb = 0; cb < NB / 64; ++cb)
+                                    tma_load_2d(wa + cb * 8192, &maps.codes[pi], nb0 + cb * 64, kb * BK, landed);
+                            }
+                        }
                     } else {
                         // extension step: the producers bring the operands
                         mbar_arrive(rank == 0 ? bar_full_w(s) : bar_full_tma(s));
@@ -578,6 +601,8 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                 }
             }
         }
+    } else if (warp == AUX_WARP && DENSE) {
+        // (dense weights: nothing to feed)
     } else if (warp == AUX_WARP) {
         // ------------------------------------------------------------------ codes + block scales
         // Walks the weight k-blocks of this CTA's units in execution order, up to NC k-blocks
@@ -687,6 +712,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         float off_val = 0.f;
         uint32_t tab_off = 0, ab_low = 0;
         auto load_lut = [&](int pi) {
+            if (DENSE) return;
             const GemmProblem& pr = p.prob[pi];
             uint16_t bits[16];
 #pragma unroll
@@ -750,8 +776,10 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         const int q = warp & 3;
         const int grp = warp >> 2;
         constexpr int CHUNKS_PER_GRP = NACC * (BN / 32) / 4;
-        const uint32_t staging = smem_base + (uint32_t)(warp / L::WARPS_PER_W_SLOT) * L::STAGE_BYTES +
-                                 L::A_BYTES + (uint32_t)(warp % L::WARPS_PER_W_SLOT) * 4096u;
+        const uint32_t staging = DENSE
+            ? smem_base + L::STAGING_OFF + (uint32_t)warp * 4096u
+            : smem_base + (uint32_t)(warp / L::WARPS_PER_W_SLOT) * L::STAGE_BYTES +
+                  L::A_BYTES + (uint32_t)(warp % L::WARPS_PER_W_SLOT) * 4096u;
         const bool split = p.splits > 1;
 
         uint32_t g = 0;   // position in the operand ring
@@ -768,7 +796,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                 ? (uint32_t)row * (uint32_t)blocks_per_row + (uint32_t)((nb0 + klocal) >> 6)
                 : (uint32_t)(nb0 + row) * (uint32_t)blocks_per_row + (uint32_t)w.kb_begin;
 
-            for (int it = 0; it < w.n_iter && !fail; ++it, ++g) {
+            for (int it = 0; it < (DENSE ? 0 : w.n_iter) && !fail; ++it, ++g) {
                 const uint32_t c = cslot;  // code-ring slot and phase of this step (weight steps)
                 const uint32_t cph = cphase;
                 if (it < w.nkb && ++cslot == NC) { cslot = 0; cphase ^= 1u; }
@@ -1373,11 +1401,12 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
     return plan_gemm_group(m, &n_w, 1, k_w, trans_w, sm_count);
 }
 
-template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP = false, int EPI = 0>
+template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP = false, int EPI = 0,
+          bool DENSE = false>
 static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaStream_t stream,
                               const char** why, const SwigluArgs* epi = nullptr) {
-    using L = SmemLayout<CG, NACC, STAGES, TABLES>;
-    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW, TABLES, PREP, EPI>;
+    using L = SmemLayout<CG, NACC, STAGES, TABLES, DENSE>;
+    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW, TABLES, PREP, EPI, DENSE>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::DYNAMIC_BYTES);
     if (e != cudaSuccess) { *why = "cudaFuncSetAttribute(shared memory)"; return e; }
@@ -1400,7 +1429,11 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
                 return cudaErrorInvalidValue;
             }
         }
-        const bool ok = TRANS_W
+        const bool ok = DENSE
+            ? make_map_2d(&maps.codes[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a.dense_w, (uint64_t)k_w,
+                          (uint64_t)a.n_w, (uint64_t)a.ld_w * 2, BK, TRANS_W ? 64 : L::NB,
+                          CU_TENSOR_MAP_SWIZZLE_128B)
+            : TRANS_W
             ? make_map_2d(&maps.codes[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, a.codes, (uint64_t)k_w / 2,
                           (uint64_t)a.n_w, (uint64_t)k_w / 2, L::NB / 2, BK,
                           CG == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)
@@ -1409,7 +1442,7 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
                           CU_TENSOR_MAP_SWIZZLE_NONE);
         if (!ok) { *why = "cuTensorMapEncodeTiled(codes)"; return cudaErrorInvalidValue; }
         if (a.scales16 == nullptr) prepared = false;
-        if (a.scales16 != nullptr) {
+        if (a.scales16 != nullptr && !DENSE) {
             // table [K_w / 64][N_w] fp16: forward box = NB rows of one column block, backward box =
             // 64 rows x the CTA's column blocks
             const bool oks = TRANS_W
@@ -1575,12 +1608,29 @@ cudaError_t launch_bwd_dx_swiglu(const GemmArgs& a, const SwigluArgs& epi, cudaS
     return launch_cfg<2, 2, true, 4, 8, MAXP, false, 2>(ga, pl, stream, why, &epi);
 }
 
+// Plain fp16 weight [n_w, k_w] (row pitch ld_w): the same pipeline with the weight tiles brought by
+// TMA instead of decoded. One weight per call, no rank-16 term.
+static cudaError_t launch_dense(const GemmGroupArgs& ga, cudaStream_t stream, const char** why) {
+    const GemmArgs& a = ga.item[0];
+    if (ga.count != 1 || a.ext_a != nullptr) { *why = "dense weight: one weight, no rank-16 term"; return cudaErrorInvalidValue; }
+    const GemmPlan pl = plan_gemm(a.m, a.n_w, a.k_w, a.trans_w, a.sm_count);
+    if (pl.cg == 2 && pl.nacc == 2)
+        return a.trans_w ? launch_cfg<2, 2, true, 3, 8, 1, false, 0, true>(ga, pl, stream, why)
+                         : launch_cfg<2, 2, false, 3, 8, 1, false, 0, true>(ga, pl, stream, why);
+    if (pl.cg == 2)
+        return a.trans_w ? launch_cfg<2, 1, true, 4, 16, 1, false, 0, true>(ga, pl, stream, why)
+                         : launch_cfg<2, 1, false, 4, 16, 1, false, 0, true>(ga, pl, stream, why);
+    return a.trans_w ? launch_cfg<1, 1, true, 3, 16, 1, false, 0, true>(ga, pl, stream, why)
+                     : launch_cfg<1, 1, false, 3, 16, 1, false, 0, true>(ga, pl, stream, why);
+}
+
 cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, const char** why) {
     *why = "";
     if (ga.count < 1 || ga.count > GEMM_MAX_GROUP) { *why = "group size"; return cudaErrorInvalidValue; }
     long long n_w[GEMM_MAX_GROUP];
     for (int i = 0; i < ga.count; ++i) n_w[i] = ga.item[i].n_w;
     const GemmArgs& a = ga.item[0];
+    if (a.dense_w != nullptr) return launch_dense(ga, stream, why);
     // A handful of token rows: stream the weights through the small-M kernels, the whole group in
     // one launch (NF4B200_DEBUG bit 7 keeps them on the tensor-core kernel, for comparison).
     if (a.m <= 64 && !(debug_flags() & 128)) {

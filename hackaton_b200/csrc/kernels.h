@@ -64,6 +64,8 @@ struct GemmArgs {
     const float* offset;
     const float* code16;
     const __half* scales16;  // optional ready-made block scales [k_w / 64][n_w] (fp16), or null
+    const __half* dense_w;   // instead of the NF4 fields: a plain fp16 weight [n_w, k_w], or null
+    long long ld_w;          // its row pitch in elements
     long long n_w, k_w;
     int nested;
     int nested_blocksize;

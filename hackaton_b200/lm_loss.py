@@ -2,7 +2,9 @@
 
 Same surface as the reference's `ce_stats` / `ce_grad` / `fused_cross_entropy`
 (solution/kernels.py:173-238) and `linear_cross_entropy` (solution/lm_loss.py:27-67). The
-statistics pass and the gradient pass are this library's kernels (csrc/cross_entropy.cu).
+statistics pass and the gradient pass are this library's kernels (csrc/cross_entropy.cu), and so
+are the two fp16 matrix products of a chunk (`dense.fp16_linear`: the tcgen05 kernel of the NF4
+projections with the weight tiles brought by TMA).
 """
 
 from __future__ import annotations
@@ -11,6 +13,7 @@ import torch
 
 from . import _lib
 from ._autograd import call
+from .dense import fp16_linear
 from .nf4 import _stream_ptr
 
 CHUNK_ROWS = 256      # rows of logits alive at a time (solution/lm_loss.py:27)
@@ -86,9 +89,16 @@ def fused_cross_entropy(logits, targets, denom, inplace_grad=False):
     return call(_LossFromLogits(bool(inplace_grad)), logits.contiguous(), targets, denom)
 
 
-def _head_chunk(hidden_rows, weight):
-    """Logits of one chunk of rows: hidden_rows . weightᵀ, fp16 in and out."""
-    return torch.nn.functional.linear(hidden_rows, weight)
+def _head_products(hidden_rows, weight):
+    """The two matrix products of one chunk: logits = hidden_rows . weightᵀ, and, once the logits
+    have been turned into their gradient, d_hidden = d_logits . weight. fp16 weights (the model's
+    own lm_head) go through this library's tcgen05 kernel; other dtypes (a test in fp32) use
+    torch's matmul."""
+    if hidden_rows.dtype == torch.float16 and weight.dtype == torch.float16:
+        return (fp16_linear(hidden_rows, weight),
+                lambda d_logits, out: fp16_linear(d_logits, weight, transposed=True, out=out))
+    return (torch.nn.functional.linear(hidden_rows, weight),
+            lambda d_logits, out: torch.mm(d_logits, weight, out=out))
 
 
 class _HeadAndLoss:
@@ -108,11 +118,11 @@ class _HeadAndLoss:
         with torch.autocast("cuda", enabled=False):
             for lo in range(0, rows, CHUNK_ROWS):
                 rs = slice(lo, min(lo + CHUNK_ROWS, rows))
-                logits = _head_chunk(hidden[rs], weight)
+                logits, back = _head_products(hidden[rs], weight)
                 ce_stats(logits, targets[rs], True,
                          out=(stats["lse"][rs], stats["loss"][rs], stats["entropy"][rs], argmax[rs]))
                 ce_grad(logits, targets[rs], stats["lse"][rs], unit, logits)
-                torch.mm(logits, weight, out=d_hidden[rs])
+                back(logits, d_hidden[rs])
         keep(d_hidden, denom)
         keep.constant(stats["loss"], stats["entropy"], argmax)
         return stats["loss"].sum() / denom, stats["loss"], stats["entropy"], argmax

@@ -150,6 +150,21 @@ int nf4b200_linear_fwd_static(const nf4b200_weight* w, const void* x, int64_t m,
                               int64_t ldy, void* stream);
 
 /*
+ * Linear with a plain fp16 weight [n_rows, n_cols] (row stride ldw elements), through the same
+ * tcgen05 / TMEM pipeline as the NF4 linear with the weight tiles brought by TMA instead of
+ * decoded: the lm_head products of the chunked loss, which the reference leaves to cuBLAS
+ * (solution/lm_loss.py:31-40: F.linear(hidden, weight) and torch.mm(grad_logits, weight)).
+ *   transposed == 0:  y[m, n_rows] = x[m, n_cols] . W^T (+ bias)
+ *   transposed != 0:  y[m, n_cols] = x[m, n_rows] . W
+ * fp16 in, fp32 accumulate, fp16 out; n_rows and n_cols multiples of 8, rows of x / y / W 16-byte
+ * aligned. workspace: nf4b200_workspace_bytes(n_rows, n_cols, m, transposed) bytes or NULL, as for
+ * nf4b200_linear_fwd.
+ */
+int nf4b200_fp16_linear(const void* weight, int64_t n_rows, int64_t n_cols, int64_t ldw,
+                        const void* x, int64_t m, int64_t ldx, int transposed, const void* bias,
+                        void* y, int64_t ldy, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Input gradient of the same linear, decode fused:
  *   dx[m, n_cols] = dy[m, n_rows] . W (+ u[m, rank] . lora_a[rank, n_cols])
  * Replaces NF4Linear.backward (solution/nf4.py:94-99): a second dequantize_nf4 + torch.matmul.
