@@ -1157,7 +1157,12 @@ def run_multi(args):
     comm_sms = args.comm_sms
     if comm_sms > 0:
         os.environ.setdefault("NCCL_MAX_CTAS", str(comm_sms))
-    dist.init_process_group("nccl", device_id=device)
+    pg_options = None
+    if args.nccl_high_priority:
+        # the collectives' kernels get SMs ahead of the next GEMM's CTAs when a GEMM ends
+        pg_options = dist.ProcessGroupNCCL.Options()
+        pg_options.is_high_priority_stream = True
+    dist.init_process_group("nccl", device_id=device, pg_options=pg_options)
     if comm_sms > 0:
         from hackaton_b200.sharded import reserve_comm_sms
         reserve_comm_sms(comm_sms)
@@ -1348,6 +1353,8 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--comm-sms", type=int, default=0,
                     help="multi-GPU: SMs kept free of the GEMM grids for NCCL kernels")
+    ap.add_argument("--nccl-high-priority", action="store_true",
+                    help="multi-GPU: run NCCL's kernels on a high-priority stream")
     ap.add_argument("--layout", default="paired", choices=["paired", "gathered"],
                     help="multi-GPU: paired = o/down sharded along input features (four all-reduces "
                          "per step); gathered = every weight sharded along output features "
