@@ -35,6 +35,7 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 constexpr int LD_WARPS = 8;
 constexpr int LD_ROWS = 16;
 constexpr int LD_THREADS = LD_WARPS * 32;
+constexpr int LD_BATCH = 3;   // chunks in flight per warp (16 registers each; two blocks per SM)
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                          uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -60,32 +61,41 @@ __device__ __forceinline__ void lora_down_block(const __half* __restrict__ in, l
     const long long chunks = (c + 31) / 32;   // c % 8 == 0 on this path
     const long long ch_begin = chunks * warp / LD_WARPS, ch_end = chunks * (warp + 1) / LD_WARPS;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (long long ch = ch_begin; ch < ch_end; ++ch) {
-        const long long col = ch * 32 + t * 8;
-        const bool col_ok = col < c;
-        uint4 a_lo = zero, a_hi = zero, b_lo = zero, b_hi = zero;
-        if (col_ok) {
-            if (r_lo < m) a_lo = __ldg(reinterpret_cast<const uint4*>(in + r_lo * ld_in + col));
-            if (r_hi < m) a_hi = __ldg(reinterpret_cast<const uint4*>(in + r_hi * ld_in + col));
-            if (RANK_MAJOR) {
-                b_lo = __ldg(reinterpret_cast<const uint4*>(p + (long long)g * c + col));
-                b_hi = __ldg(reinterpret_cast<const uint4*>(p + (long long)(g + 8) * c + col));
-            } else {
-                __half lo[8], hi[8];
+    // LD_BATCH chunks per round: every load of the round is issued before the first MMA, so a
+    // warp pays one memory round trip per round instead of one per chunk.
+    for (long long ch0 = ch_begin; ch0 < ch_end; ch0 += LD_BATCH) {
+        uint4 a_lo[LD_BATCH], a_hi[LD_BATCH], b_lo[LD_BATCH], b_hi[LD_BATCH];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    lo[e] = __ldg(p + (col + e) * 16 + g);
-                    hi[e] = __ldg(p + (col + e) * 16 + g + 8);
+        for (int q = 0; q < LD_BATCH; ++q) {
+            const long long col = (ch0 + q) * 32 + t * 8;
+            const bool col_ok = ch0 + q < ch_end && col < c;
+            a_lo[q] = a_hi[q] = b_lo[q] = b_hi[q] = zero;
+            if (col_ok) {
+                if (r_lo < m) a_lo[q] = __ldg(reinterpret_cast<const uint4*>(in + r_lo * ld_in + col));
+                if (r_hi < m) a_hi[q] = __ldg(reinterpret_cast<const uint4*>(in + r_hi * ld_in + col));
+                if (RANK_MAJOR) {
+                    b_lo[q] = __ldg(reinterpret_cast<const uint4*>(p + (long long)g * c + col));
+                    b_hi[q] = __ldg(reinterpret_cast<const uint4*>(p + (long long)(g + 8) * c + col));
+                } else {
+                    __half lo[8], hi[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        lo[e] = __ldg(p + (col + e) * 16 + g);
+                        hi[e] = __ldg(p + (col + e) * 16 + g + 8);
+                    }
+                    b_lo[q] = *reinterpret_cast<const uint4*>(lo);
+                    b_hi[q] = *reinterpret_cast<const uint4*>(hi);
                 }
-                b_lo = *reinterpret_cast<const uint4*>(lo);
-                b_hi = *reinterpret_cast<const uint4*>(hi);
             }
         }
-        // k16 step 0: halves 0,1 | 2,3 ; step 1: halves 4,5 | 6,7
-        mma16816(d0, a_lo.x, a_hi.x, a_lo.y, a_hi.y, b_lo.x, b_lo.y);
-        mma16816(d1, a_lo.x, a_hi.x, a_lo.y, a_hi.y, b_hi.x, b_hi.y);
-        mma16816(d0, a_lo.z, a_hi.z, a_lo.w, a_hi.w, b_lo.z, b_lo.w);
-        mma16816(d1, a_lo.z, a_hi.z, a_lo.w, a_hi.w, b_hi.z, b_hi.w);
+#pragma unroll
+        for (int q = 0; q < LD_BATCH; ++q) {
+            // k16 step 0: halves 0,1 | 2,3 ; step 1: halves 4,5 | 6,7
+            mma16816(d0, a_lo[q].x, a_hi[q].x, a_lo[q].y, a_hi[q].y, b_lo[q].x, b_lo[q].y);
+            mma16816(d1, a_lo[q].x, a_hi[q].x, a_lo[q].y, a_hi[q].y, b_hi[q].x, b_hi[q].y);
+            mma16816(d0, a_lo[q].z, a_hi[q].z, a_lo[q].w, a_hi[q].w, b_lo[q].z, b_lo[q].w);
+            mma16816(d1, a_lo[q].z, a_hi[q].z, a_lo[q].w, a_hi[q].w, b_hi[q].z, b_hi[q].w);
+        }
     }
     // accumulator layout: d[0],d[1] -> (row g, cols 2t, 2t+1); d[2],d[3] -> (row g+8, same cols)
     part[warp][g][2 * t] = d0[0];         part[warp][g][2 * t + 1] = d0[1];

@@ -164,3 +164,44 @@ def test_gathered_layout_shards(cuda_lib, world):
             assert _rel(y[rows_dev].cpu(), nf4_oracle.linear_fwd(x[rows_dev].cpu(), w)) <= TOL
             assert _rel(dx[rows_dev].cpu(), nf4_oracle.linear_bwd(dy[rows_dev].cpu(), w)) <= TOL
     assert cuda_lib.device_status() == 0
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_qkv_shards_with_lora(cuda_lib, world):
+    """LoRA on the sharded q and v (A replicated, B split with W): one rank's grouped forward,
+    grouped dX with both rank-16 shares, and the factors' gradients, at the shard shapes of 2 and
+    8 GPUs (v: 256 and 64 rows), against the oracle. 2048 token rows keep the CPU side short."""
+    from hackaton_b200.sharded import ShardedNF4Linear, backward_dx_group, forward_local_group, lora_weight_grads
+
+    m, scaling = 2048, 2.0
+    g = torch.Generator(device="cuda").manual_seed(40 + world)
+    x = torch.randn(m, HIDDEN, generator=g, device="cuda").half()
+    mods, refs, grads = [], [], []
+    for i, n in enumerate((HIDDEN // world, KV // world, KV // world)):
+        packed, state = _weight(n, HIDDEN, 400 + world * 10 + i)
+        a = b = None
+        if i != 1:
+            a = ((torch.rand(16, HIDDEN, generator=g, device="cuda") * 2 - 1) / HIDDEN ** 0.5).half()
+            b = (torch.randn(n, 16, generator=g, device="cuda") * 0.05).half()
+        mods.append(ShardedNF4Linear(packed, state, n, lora_a=a, lora_b=b, scaling=scaling))
+        refs.append((oracle_weight(packed, state), a, b))
+        grads.append(torch.randn(m, n, generator=g, device="cuda").half())
+    ys, xas = forward_local_group(mods, x, return_lora_inputs=True)
+    dx, work, us = backward_dx_group(mods, grads, return_lora_inputs=True)
+    wgrads, works = lora_weight_grads(mods, x, grads, xas, us)
+    assert work is None and works == [] and sorted(wgrads) == [0, 2]
+    x_cpu = x.cpu()
+    dx_ref = torch.zeros(m, HIDDEN)
+    for i, (y, (w, a, b), dy) in enumerate(zip(ys, refs, grads)):
+        if a is None:
+            assert _rel(y.cpu(), nf4_oracle.linear_fwd(x_cpu, w)) <= TOL
+            dx_ref += nf4_oracle.linear_bwd(dy.cpu(), w).float()
+            continue
+        y_ref, _ = nf4_oracle.lora_fwd(x_cpu, w, a.cpu(), b.cpu(), scaling)
+        d_ref, da_ref, db_ref = nf4_oracle.lora_bwd(dy.cpu(), x_cpu, w, a.cpu(), b.cpu(), scaling)
+        dx_ref += d_ref.float()
+        assert _rel(y.cpu(), y_ref) <= TOL
+        assert _rel(wgrads[i][0].cpu(), da_ref) <= TOL
+        assert _rel(wgrads[i][1].cpu(), db_ref) <= TOL
+    assert _rel(dx.cpu(), dx_ref) <= TOL
+    assert cuda_lib.device_status() == 0
