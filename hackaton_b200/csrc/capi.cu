@@ -589,7 +589,7 @@ int64_t nf4b200_linear_bwd_dx_swiglu_workspace_bytes(int64_t n_rows, int64_t n_c
     if (n_rows <= 0 || n_cols <= 0 || m <= 0)
         return fail(NF4B200_EINVAL, "linear_bwd_dx_swiglu_workspace_bytes: bad shape");
     const nf4::GemmPlan pl = nf4::plan_gemm(m, n_rows, n_cols, true, gemm_sms(d));
-    if (pl.cg == 2 && pl.nacc == 2 && pl.splits == 1 && n_cols % 8 == 0) return 0;
+    if (pl.cg == 2 && pl.nacc == 2 && pl.splits == 1 && pl.bn == 256 && n_cols % 8 == 0) return 0;
     return (int64_t)((pl.ws_bytes + 255) / 256 * 256 + swiglu_tmp_bytes(m, n_cols));
 }
 

@@ -133,9 +133,9 @@ struct GemmMaps {
 // DENSE_ (plain fp16 weights brought by TMA, no decoding): the TMA warp runs ahead into the next
 // unit's weight slots while the epilogue is still staging, so the staging areas get a region of
 // their own (4 KB per producer warp) instead of borrowing the weight slots.
-template <int CG, int NACC, int STAGES, int TABLES_, bool DENSE_ = false>
+template <int CG, int NACC, int STAGES, int TABLES_, bool DENSE_ = false, int BN_ = BN>
 struct SmemLayout {
-    static constexpr int NB = BN / CG;                 // weight-tile columns decoded by one CTA
+    static constexpr int NB = BN_ / CG;                // weight-tile columns decoded by one CTA
     static constexpr int A_BYTES = NACC * 128 * BK * 2;
     static constexpr int W_BYTES = NB * BK * 2;
     static constexpr int C_BYTES = NB * BK / 2;
@@ -158,7 +158,12 @@ struct SmemLayout {
     static constexpr int DYNAMIC_BYTES = TOTAL + 1024;  // slack for 1024-byte alignment
     static_assert(NC_FIT >= 2, "no room for the code ring");
     static constexpr int WARPS_PER_W_SLOT = W_BYTES / 4096;  // 4 KB epilogue staging per warp
-    static_assert(DENSE_ || STAGES * WARPS_PER_W_SLOT >= PRODUCER_WARPS, "staging needs more weight slots");
+    // Narrow tiles: the weight slots are too small for 16 staging areas, which then sit in the
+    // activation slots; the TMA warp holds the next unit's tiles back until they have been read.
+    static constexpr bool STAGING_IN_A = !DENSE_ && STAGES * WARPS_PER_W_SLOT < PRODUCER_WARPS;
+    static constexpr int WARPS_PER_A_SLOT = A_BYTES / 4096;
+    static_assert(DENSE_ || !STAGING_IN_A || STAGES * WARPS_PER_A_SLOT >= PRODUCER_WARPS,
+                  "staging needs more operand slots");
     static_assert(DYNAMIC_BYTES <= 232448, "exceeds the 227 KB of shared memory per CTA");
 };
 
@@ -279,8 +284,9 @@ __device__ __forceinline__ int find_problem(const GemmParams& p, int idx) {
 // CTA 0 of the pair expands those rows of the gate weight (problem 0), CTA 1 the same rows of the
 // up weight (problem 1), so every token row finds gate in accumulator columns 0..127 and up in
 // 128..255. `prob` and `n0` are then per CTA: n0 + rank * 128 is the first weight row either way.
-template <bool TRANS_W, int EPI>
+template <bool TRANS_W, int EPI, int BN_ = 256>
 __device__ __forceinline__ Unit make_unit(int u, const GemmParams& p, int rows_per_tile, int rank) {
+    constexpr int BN = BN_;  // (the tile width of this instantiation)
     Unit w;
     const int tile = u / p.splits;
     w.slice = u % p.splits;
@@ -323,11 +329,14 @@ __device__ __forceinline__ int ext_problem(const GemmParams& p, int e) {
 // in the very layout the decoding warps would have written, next to the activation tiles; the code
 // ring and the decoding loop are idle and the producer warps only run the epilogue.
 template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP, int EPI = 0,
-          bool DENSE = false>
+          bool DENSE = false, int BN_ = 256>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ GemmParams p) {
     const bool prepared = PREP || p.prepared != 0;
-    using L = SmemLayout<CG, NACC, STAGES, TABLES, DENSE>;
+    constexpr int BN = BN_;  // output-tile width of this instantiation (hides the default above)
+    static_assert(BN_ == 256 || (BN_ == 128 && CG == 2 && NACC == 2 && EPI == 0 && !DENSE),
+                  "128-wide tiles: pair kernel with two accumulators, plain epilogue");
+    using L = SmemLayout<CG, NACC, STAGES, TABLES, DENSE, BN_>;
     constexpr int NB = L::NB;
     // The 16 producer warps form 16 / DW groups of DW warps that take the k-blocks in turn (all 16
     // drain the accumulators): while one group publishes its tile (fence, barriers), the other is
@@ -367,7 +376,8 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
     const uint32_t bar_tmem_empty = bar_base + 8u * (3 * STAGES + 1);
     auto bar_full_c = [&](int c) { return bar_base + 8u * (3 * STAGES + 2 + c); };
     auto bar_empty_c = [&](int c) { return bar_base + 8u * (3 * STAGES + 2 + NC + c); };
-    constexpr int BAR_COUNT = 3 * STAGES + 2 + 2 * NC;
+    const uint32_t bar_epi_done = bar_base + 8u * (3 * STAGES + 2 + 2 * NC);  // (STAGING_IN_A only)
+    constexpr int BAR_COUNT = 3 * STAGES + 3 + 2 * NC;
     static_assert(8 * BAR_COUNT + 8 <= 512, "barrier area");
     volatile uint32_t* tmem_slot =
         reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFF + 8 * BAR_COUNT);
@@ -394,6 +404,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         }
         mbar_init(bar_tmem_full, ISSUERS);
         mbar_init(bar_tmem_empty, ARRIVALS);
+        mbar_init(bar_epi_done, 1);
         *abort_flag = 0;
         fence_barrier_init();
     }
@@ -429,35 +440,11 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
 
     int fail = 0;
 
-    // Warp-wide waits: one lane polls the barrier, the others sleep at the warp vote. Keeps the
-    // shared-memory pipe free of 31 redundant polls per warp.
-    constexpr uint32_t WAIT_SLEEP_NS = 64u;
+    // Warp-wide waits (all lanes wait on the barrier themselves).
     auto warp_wait = [&](uint32_t bar, uint32_t parity) -> bool {
-        if (mbar_try_wait(bar, parity)) return true;
-        const unsigned long long t0 = globaltimer_ns();
-        uint32_t polls = 0;
-        while (!mbar_try_wait(bar, parity)) {
-            __nanosleep(WAIT_SLEEP_NS);
-            if ((++polls & 63u) == 0u) {
-                if (*abort_flag) return false;
-                if (globaltimer_ns() - t0 > WAIT_TIMEOUT_NS) { *abort_flag = 1; return false; }
-            }
-        }
-        return true;
+        return mbar_wait(bar, parity, abort_flag);
     };
-    auto warp_wait_commit = [&](uint32_t bar, uint32_t parity) -> bool {
-        if (mbar_test_wait_cluster(bar, parity)) return true;
-        const unsigned long long t0 = globaltimer_ns();
-        uint32_t polls = 0;
-        while (!mbar_test_wait_cluster(bar, parity)) {
-            __nanosleep(WAIT_SLEEP_NS);
-            if ((++polls & 63u) == 0u) {
-                if (*abort_flag) return false;
-                if (globaltimer_ns() - t0 > WAIT_TIMEOUT_NS) { *abort_flag = 1; return false; }
-            }
-        }
-        return true;
-    };
+    auto warp_wait_commit = warp_wait;  // (barriers completed by a tcgen05.commit)
 
     if (warp == TMA_WARP) {
         // ------------------------------------------------------------------ TMA producer
@@ -465,7 +452,11 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
             uint32_t g = 0;  // ring position, running across units
             uint32_t unit_iter2 = 0;
             for (int u = pair; u < total_units && !fail; u += n_pairs, ++unit_iter2) {
-                const Unit w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
+                const Unit w = make_unit<TRANS_W, EPI, BN_>(u, p, ROWS_PER_TILE, (int)rank);
+                if (L::STAGING_IN_A && unit_iter2 > 0) {
+                    // the previous unit's epilogue stages its output in the activation slots
+                    if (!mbar_wait(bar_epi_done, (unit_iter2 - 1u) & 1u, abort_flag)) { fail = 1; break; }
+                }
                 for (int it = 0; it < w.n_iter; ++it, ++g) {
                     const int s = (int)(g % STAGES);
                     const uint32_t ph = (g / STAGES) & 1u;
@@ -533,7 +524,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
             w.nkb = w.n_iter = 0;
             int it = 0;
             if (have) {
-                w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
+                w = make_unit<TRANS_W, EPI, BN_>(u, p, ROWS_PER_TILE, (int)rank);
                 tc_fence_after_sync();
             }
             uint32_t ph = 0;
@@ -575,7 +566,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                         u += n_pairs;
                         have = u < total_units;
                         if (have) {
-                            w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
+                            w = make_unit<TRANS_W, EPI, BN_>(u, p, ROWS_PER_TILE, (int)rank);
                             it = 0;
                             // the accumulators must have been drained (in both CTAs)
                             if (!mbar_wait_cluster(bar_tmem_empty, unit_iter & 1u, abort_flag)) {
@@ -593,7 +584,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
             // Peer CTA: tell the leader when this CTA's activation tile of a step has landed.
             uint32_t g = 0;
             for (int u = pair; u < total_units && !fail; u += n_pairs) {
-                const Unit w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
+                const Unit w = make_unit<TRANS_W, EPI, BN_>(u, p, ROWS_PER_TILE, (int)rank);
                 for (int it = 0; it < w.n_iter; ++it, ++g) {
                     const int s = (int)(g % STAGES);
                     if (!mbar_wait(bar_full_tma(s), (g / STAGES) & 1u, abort_flag)) { fail = 8; break; }
@@ -620,7 +611,7 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         int c = 0;          // slot of the code ring
         uint32_t cph = 0;   // its phase
         for (int u = pair; u < total_units && !fail; u += n_pairs) {
-            const Unit w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
+            const Unit w = make_unit<TRANS_W, EPI, BN_>(u, p, ROWS_PER_TILE, (int)rank);
             const int nb0 = w.n0 + (int)rank * NB;
             int cur_prob = -1, n_w_cur = 0, first_cur = 0, sh = 0;
             bool nested_cur = false;
@@ -751,11 +742,13 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                 const int e = (pt >> 3) % PPR;
                 klocal = e * 8 * WORDS;
                 const int byte = e * 4 * WORDS;              // offset of the piece inside its row
-                if (CG == 1)
+                if (NB / 2 == 128)
                     src_off = (uint32_t)row * 128u + (uint32_t)(((byte >> 4) ^ (row & 7)) << 4);
-                else
+                else if (NB / 2 == 64)
                     src_off = (uint32_t)row * 64u +
                               (uint32_t)((((byte >> 4) ^ ((row >> 1) & 3)) << 4) + (byte & 15));
+                else  // 32-byte rows, not swizzled: a warp reads 8 whole rows, no bank conflicts
+                    src_off = (uint32_t)row * 32u + (uint32_t)byte;
                 dst = (uint32_t)(klocal >> 6) * 8192u + (uint32_t)(row >> 3) * 1024u +
                       (uint32_t)(row & 7) * 128u;
                 chunk0 = (klocal & 63) >> 3;
@@ -778,15 +771,20 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
         constexpr int CHUNKS_PER_GRP = NACC * (BN / 32) / 4;
         const uint32_t staging = DENSE
             ? smem_base + L::STAGING_OFF + (uint32_t)warp * 4096u
+            : L::STAGING_IN_A
+            ? smem_base + (uint32_t)(warp / L::WARPS_PER_A_SLOT) * L::STAGE_BYTES +
+                  (uint32_t)(warp % L::WARPS_PER_A_SLOT) * 4096u
             : smem_base + (uint32_t)(warp / L::WARPS_PER_W_SLOT) * L::STAGE_BYTES +
                   L::A_BYTES + (uint32_t)(warp % L::WARPS_PER_W_SLOT) * 4096u;
         const bool split = p.splits > 1;
 
-        uint32_t g = 0;   // position in the operand ring
+        uint32_t g = 0;                  // steps taken in the operand ring
+        uint32_t sslot = 0, sphase = 0;  // ... as slot and phase
         uint32_t cslot = 0, cphase = 0;  // position in the code ring
+        const bool multi_table = L::TABLES > 1 && p.n_prob > 1;
         uint32_t unit_iter = 0;
         for (int u = pair; u < total_units; u += n_pairs, ++unit_iter) {
-            const Unit w = make_unit<TRANS_W, EPI>(u, p, ROWS_PER_TILE, (int)rank);
+            const Unit w = make_unit<TRANS_W, EPI, BN_>(u, p, ROWS_PER_TILE, (int)rank);
             NF4_TRACE(0);
             const int nb0 = w.n0 + (int)rank * NB;  // first weight-tile column of this CTA
             // Byte of the copied absmax word that holds this thread's first-level entry: block
@@ -800,22 +798,19 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                 const uint32_t c = cslot;  // code-ring slot and phase of this step (weight steps)
                 const uint32_t cph = cphase;
                 if (it < w.nkb && ++cslot == NC) { cslot = 0; cphase ^= 1u; }
+                const uint32_t s = sslot;  // operand-ring slot and phase of this step
+                const uint32_t ph = sphase;
+                if (++sslot == (uint32_t)STAGES) { sslot = 0; sphase ^= 1u; }
                 if (GROUPS > 1 && (int)(g % GROUPS) != group) continue;
-                const int s = (int)(g % STAGES);
-                const uint32_t ph = (g / STAGES) & 1u;
-                const uint32_t stage_off = (uint32_t)s * L::STAGE_BYTES;
+                const uint32_t stage_off = s * L::STAGE_BYTES;
                 if (it < w.nkb) {
-                    // codes and scale of this k-block from the code ring; expand into registers,
-                    // hand the ring slot back, then wait for the operand slot to be free
+                    // codes and scale of this k-block from the code ring
                     if (!warp_wait(bar_full_c(c), cph)) { fail = 4; break; }
                     if (pt == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(1, it); }
-                    // codes and scale go into registers and the code-ring slot goes back at once;
-                    // the expansion itself waits for the operand slot (holding the expanded tile
-                    // in registers across that wait costs spills under the 96-register cap)
                     uint32_t cw[WORDS];
                     __half2 scale2 = __half2half2(__ushort_as_half((unsigned short)0));
                     if (!NF4_TUNE(1)) {
-                        if (L::TABLES > 1 && p.n_prob > 1) {
+                        if (multi_table) {
                             const int pi = (int)lds32(smem_base + L::META_OFF + 4u * c);
                             if (pi != lut_prob) load_lut(pi);
                         }
@@ -844,31 +839,18 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                             cw[0] = q.x; cw[1] = q.y;
                         }
                     }
-                    // Hand the code-ring slot back. The slot was read through the generic proxy
-                    // (ld.shared) and will be re-filled by TMA, i.e. through the async proxy. An
-                    // mbarrier arrive alone does not order the two: it can be performed while this
-                    // warp's loads are still queued in the (saturated) shared-memory pipe, the
-                    // feeding warp then sees a free slot, and the TMA write can land before some
-                    // of the loads' wavefronts are served, which then return the next k-block's
-                    // codes for part of the warp's lanes. fence.proxy.async makes the loads
-                    // complete before anything the async proxy does after the arrive; it is the
-                    // ordering the PTX memory model asks for between the two proxies.
-#ifdef NF4B200_HANDBACK_EARLY  // test builds: hand back before the operand slot is awaited
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_empty_c(c));
+                    // Expand into registers before the operand slot is awaited: the arithmetic
+                    // overlaps the wait, and one fence per k-block serves both hand-overs below.
+                    uint4 vals[WORDS];
+                    if (!NF4_TUNE(1)) {
+#pragma unroll
+                        for (int i = 0; i < WORDS; ++i) vals[i] = decode_word_reg(cw[i], lut, scale2);
+                    }
                     if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
-#else
-                    if (!warp_wait_commit(bar_empty(s), ph ^ 1u)) { fail = 4; break; }
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_empty_c(c));
-#endif
                     if (pt == 0) { const uint32_t unit_iter2 = unit_iter; NF4_TRACE2(7, it); }
                     if (!NF4_TUNE(1)) {
 #pragma unroll
-                        for (int i = 0; i < WORDS; ++i)
-                            sts128(dst_off[i] + stage_off, decode_word_reg(cw[i], lut, scale2));
+                        for (int i = 0; i < WORDS; ++i) sts128(dst_off[i] + stage_off, vals[i]);
                     }
                 } else {
                     // K extension operands, unswizzled core-matrix layout (see the MMA branch).
@@ -910,10 +892,20 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
                         }
                     }
                 }
-                // publish: every lane fences its writes towards the async proxy, one lane arrives
+                // Publish: every lane fences towards the async proxy, one lane arrives. The same
+                // fence hands the code-ring slot back. That slot was read through the generic
+                // proxy (ld.shared) and will be re-filled by TMA, i.e. through the async proxy. An
+                // mbarrier arrive alone does not order the two: it can be performed while this
+                // warp's loads are still queued in the (saturated) shared-memory pipe, the feeding
+                // warp then sees a free slot, and the TMA write can land before some of the loads'
+                // wavefronts are served, which then return the next k-block's codes for part of
+                // the warp's lanes. fence.proxy.async makes the loads complete before anything the
+                // async proxy does after the arrive; it is the ordering the PTX memory model asks
+                // for between the two proxies.
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
+                    if (it < w.nkb) mbar_arrive(bar_empty_c(c));
                     if (CG == 2) mbar_arrive_cluster(lead_full_w0 + 8u * s);
                     else         mbar_arrive(bar_full_w(s));
                 }
@@ -1156,7 +1148,9 @@ nf4_gemm_kernel(const __grid_constant__ GemmMaps maps, const __grid_constant__ G
             NF4_TRACE(3);
             // the staging areas live in weight slots: nobody may decode the next unit into them
             // before every warp has read its staging back
+            if (L::STAGING_IN_A) fence_proxy_async_smem();  // (reads here, then TMA writes: two proxies)
             named_bar_sync(1, PRODUCER_THREADS);
+            if (L::STAGING_IN_A && threadIdx.x == 0) mbar_arrive(bar_epi_done);
             NF4_TRACE(4);
         }
     }
@@ -1323,10 +1317,16 @@ static ForcedPlan forced_plan() {
 static constexpr int debug_flags() { return 0; }
 #endif
 
+#ifndef NF4B200_NARROW_MAX_KB
+#define NF4B200_NARROW_MAX_KB 40
+#endif
+constexpr int NARROW_MAX_KB = NF4B200_NARROW_MAX_KB;  // longest contraction the 128-wide tiles take
+
 // Tiling and split-K plan shared by the launcher and the workspace-size query.
 GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long k_w, bool trans_w,
-                         int sm_count) {
+                         int sm_count, bool narrow_ok) {
     GemmPlan pl;
+    pl.bn = BN;
     if (m <= 128)      { pl.cg = 1; pl.nacc = 1; }
     else if (m <= 256) { pl.cg = 2; pl.nacc = 1; }
     else               { pl.cg = 2; pl.nacc = 2; }
@@ -1343,25 +1343,51 @@ GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long
 #endif
     int n_tiles = 0, nkb = 0;
     size_t ws_floats = 0;
-    for (int i = 0; i < count; ++i) {
-        if (trans_w) {
-            pl.first[i] = nkb;                          // first k-block of problem i
-            nkb += (int)((n_w[i] + BK - 1) / BK);
-        } else {
-            pl.first[i] = n_tiles;                      // first n-tile of problem i
-            n_tiles += (int)((n_w[i] + BN - 1) / BN);
-            pl.ldp[i] = (n_w[i] + 3) / 4 * 4;
+    auto lay_out = [&](int bn) {  // n-tiles of width bn, k-blocks, first[] per problem
+        n_tiles = 0;
+        nkb = 0;
+        for (int i = 0; i < count; ++i) {
+            if (trans_w) {
+                pl.first[i] = nkb;                          // first k-block of problem i
+                nkb += (int)((n_w[i] + BK - 1) / BK);
+            } else {
+                pl.first[i] = n_tiles;                      // first n-tile of problem i
+                n_tiles += (int)((n_w[i] + bn - 1) / bn);
+                pl.ldp[i] = (n_w[i] + 3) / 4 * 4;
+            }
         }
-    }
-    if (trans_w) {
-        n_tiles = (int)((k_w + BN - 1) / BN);
-        pl.ldp[0] = (k_w + 3) / 4 * 4;
-    } else {
-        nkb = (int)((k_w + BK - 1) / BK);
+        if (trans_w) {
+            n_tiles = (int)((k_w + bn - 1) / bn);
+            pl.ldp[0] = (k_w + 3) / 4 * 4;
+        } else {
+            nkb = (int)((k_w + BK - 1) / BK);
+        }
+    };
+    lay_out(BN);
+    const int slots = sm_count / pl.cg;  // units that run at the same time
+    // Few wide tiles (q/k/v and o at 2048 tokens): 512-row tiles of half the width in a single
+    // wave. Against the 256-row tiles below, every decoded weight meets twice as many token rows,
+    // and no K-slices or reduction pass are needed. Needs every weight's scale table (the caller
+    // falls back with narrow_ok = false otherwise), so the scratch is sized for the fallback too.
+    if (!forced && narrow_ok && pl.cg == 2 && pl.nacc == 2 && nkb <= NARROW_MAX_KB) {
+        const long long wide = ((m + 511) / 512) * n_tiles;
+        lay_out(BN / 2);
+        const long long narrow = ((m + 511) / 512) * n_tiles;
+        if (wide * 2 <= slots && narrow <= slots) {
+            pl.bn = BN / 2;
+            pl.n_tiles = n_tiles;
+            pl.nkb = nkb;
+            pl.m_tiles = (int)((m + 511) / 512);
+            pl.splits = 1;
+            pl.kb_per_split = nkb;
+            for (int i = 0; i < count; ++i) pl.ws_off[i] = 0;
+            pl.ws_bytes = plan_gemm_group(m, n_w, count, k_w, trans_w, sm_count, false).ws_bytes;
+            return pl;
+        }
+        lay_out(BN);
     }
     pl.n_tiles = n_tiles;
     pl.nkb = nkb;
-    const int slots = sm_count / pl.cg;  // units that run at the same time
     // Short contractions whose 512-row tiles would fill less than half of the pairs (q/k/v and o
     // at 2048 tokens): 256-row tiles in a single wave, no split-K and no reduction pass, measured
     // 2 to 8 us faster than slices + reduce up to 24 k-blocks; longer contractions keep the slices.
@@ -1402,11 +1428,12 @@ GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int 
 }
 
 template <int CG, int NACC, bool TRANS_W, int STAGES, int DW, int TABLES, bool PREP = false, int EPI = 0,
-          bool DENSE = false>
+          bool DENSE = false, int BN_ = BN>
 static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaStream_t stream,
                               const char** why, const SwigluArgs* epi = nullptr) {
-    using L = SmemLayout<CG, NACC, STAGES, TABLES, DENSE>;
-    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW, TABLES, PREP, EPI, DENSE>;
+    using L = SmemLayout<CG, NACC, STAGES, TABLES, DENSE, BN_>;
+    auto kernel = nf4_gemm_kernel<CG, NACC, TRANS_W, STAGES, DW, TABLES, PREP, EPI, DENSE, BN_>;
+    if (pl.bn != BN_) { *why = "plan and kernel disagree on the tile width"; return cudaErrorInvalidValue; }
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          L::DYNAMIC_BYTES);
     if (e != cudaSuccess) { *why = "cudaFuncSetAttribute(shared memory)"; return e; }
@@ -1436,7 +1463,8 @@ static cudaError_t launch_cfg(const GemmGroupArgs& ga, const GemmPlan& pl, cudaS
             : TRANS_W
             ? make_map_2d(&maps.codes[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, a.codes, (uint64_t)k_w / 2,
                           (uint64_t)a.n_w, (uint64_t)k_w / 2, L::NB / 2, BK,
-                          CG == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)
+                          L::NB / 2 == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : L::NB / 2 == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE)
             : make_map_2d(&maps.codes[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, a.codes, (uint64_t)k_w / 2,
                           (uint64_t)a.n_w, (uint64_t)k_w / 2, BK / 2, L::NB,
                           CU_TENSOR_MAP_SWIZZLE_NONE);
@@ -1572,6 +1600,7 @@ cudaError_t launch_gate_up_swiglu(const GemmGroupArgs& ga, __half* hidden, long 
     GemmPlan pl = {};
     pl.cg = 2;
     pl.nacc = 2;
+    pl.bn = BN;
     pl.m_tiles = (int)((a.m + 511) / 512);
     pl.n_tiles = (int)((a.n_w + BN / 2 - 1) / (BN / 2));
     pl.nkb = (int)((a.k_w + BK - 1) / BK);
@@ -1591,7 +1620,7 @@ cudaError_t launch_gate_up_swiglu(const GemmGroupArgs& ga, __half* hidden, long 
 bool swiglu_bwd_fused_eligible(const GemmArgs& a) {
     if (!a.trans_w || a.ext_a != nullptr || a.k_w % 8 != 0 || (debug_flags() & 16)) return false;
     const GemmPlan pl = plan_gemm(a.m, a.n_w, a.k_w, true, a.sm_count);
-    return pl.cg == 2 && pl.nacc == 2 && pl.splits == 1;
+    return pl.cg == 2 && pl.nacc == 2 && pl.splits == 1 && pl.bn == BN;
 }
 
 cudaError_t launch_bwd_dx_swiglu(const GemmArgs& a, const SwigluArgs& epi, cudaStream_t stream,
@@ -1613,7 +1642,7 @@ cudaError_t launch_bwd_dx_swiglu(const GemmArgs& a, const SwigluArgs& epi, cudaS
 static cudaError_t launch_dense(const GemmGroupArgs& ga, cudaStream_t stream, const char** why) {
     const GemmArgs& a = ga.item[0];
     if (ga.count != 1 || a.ext_a != nullptr) { *why = "dense weight: one weight, no rank-16 term"; return cudaErrorInvalidValue; }
-    const GemmPlan pl = plan_gemm(a.m, a.n_w, a.k_w, a.trans_w, a.sm_count);
+    const GemmPlan pl = plan_gemm_group(a.m, &a.n_w, 1, a.k_w, a.trans_w, a.sm_count, false);
     if (pl.cg == 2 && pl.nacc == 2)
         return a.trans_w ? launch_cfg<2, 2, true, 3, 8, 1, false, 0, true>(ga, pl, stream, why)
                          : launch_cfg<2, 2, false, 3, 8, 1, false, 0, true>(ga, pl, stream, why);
@@ -1653,13 +1682,16 @@ cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, cons
             return e;
         }
     }
-    const GemmPlan pl = plan_gemm_group(a.m, n_w, ga.count, a.k_w, a.trans_w, a.sm_count);
     // Pair kernels: two alternating groups of 8 decoding warps for the 512-row tiles (measured
     // faster than one group of 16 in both directions), one group of 16 for the 256-row tiles; each
     // in a variant specialised for "every weight brings its scale table".
     bool prep = true;
     for (int i = 0; i < ga.count; ++i)
         if (ga.item[i].scales16 == nullptr) prep = false;
+    const GemmPlan pl = plan_gemm_group(a.m, n_w, ga.count, a.k_w, a.trans_w, a.sm_count, prep);
+    if (pl.bn == BN / 2)
+        return a.trans_w ? launch_cfg<2, 2, true, 5, 8, MAXP, true, 0, false, BN / 2>(ga, pl, stream, why)
+                         : launch_cfg<2, 2, false, 5, 8, MAXP, true, 0, false, BN / 2>(ga, pl, stream, why);
     if (pl.cg == 2 && pl.nacc == 2) {
         if (prep)
             return a.trans_w ? launch_cfg<2, 2, true, 4, 8, MAXP, true>(ga, pl, stream, why)

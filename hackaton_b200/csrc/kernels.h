@@ -88,6 +88,7 @@ constexpr int GEMM_MAX_GROUP = 4;  // weights that one grouped launch can take
 struct GemmPlan {
     int cg;            // CTAs cooperating on one tile (1, or 2 = CTA pair)
     int nacc;          // 128-row accumulators per CTA (1 or 2)
+    int bn;            // output-tile width: 256, or 128 (pair kernel with two accumulators only)
     int m_tiles, n_tiles;
     int splits;        // units sharing one tile along K
     int kb_per_split;  // 64-deep k-blocks per unit
@@ -102,8 +103,9 @@ struct GemmArgs;
 // A group of up to GEMM_MAX_GROUP weights with the same number of columns. Forward: shared
 // activations (item[0].act), one output per item. Backward: one dY per item (item[i].act), the
 // products are summed into item[0].out. m, trans_w, sm_count and the workspace come from item[0].
+// narrow_ok = false keeps the 128-wide tiles out of the plan (they need every weight's scale table).
 GemmPlan plan_gemm_group(long long m, const long long* n_w, int count, long long k_w, bool trans_w,
-                         int sm_count);
+                         int sm_count, bool narrow_ok = true);
 GemmPlan plan_gemm(long long m, long long n_w, long long k_w, bool trans_w, int sm_count);
 
 struct GemmGroupArgs {

@@ -47,16 +47,19 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                  : "memory");
 }
 
+// One blocking attempt: the hardware suspends the thread until the phase completes or the
+// hinted time has passed, so a waiting warp takes no issue slots from the working ones.
+constexpr uint32_t TRY_WAIT_HINT_NS = 100000u;
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(done)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(TRY_WAIT_HINT_NS)
         : "memory");
     return done;
 }
@@ -66,18 +69,12 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           unsigned long long limit_ns = WAIT_TIMEOUT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t0 = 0;
-    uint32_t polls = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if ((++polls & 31u) == 0u) {
-            if (*abort_flag) return false;
-            unsigned long long now = globaltimer_ns();
-            if (t0 == 0) {
-                t0 = now;
-            } else if (now - t0 > limit_ns) {
-                *abort_flag = 1;
-                return false;
-            }
+    const unsigned long long t0 = globaltimer_ns();
+    while (!mbar_try_wait(bar, parity)) {  // (each attempt blocks for up to TRY_WAIT_HINT_NS)
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > limit_ns) {
+            *abort_flag = 1;
+            return false;
         }
     }
     return true;
@@ -233,41 +230,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
-// Non-blocking phase test, used to poll the barriers that the peer CTA signals (remote arrives,
-// multicast tcgen05.commit).
-__device__ __forceinline__ uint32_t mbar_test_wait_cluster(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done;
-}
-
-// Bounded polling wait for a barrier signalled from the peer CTA.
+// Barriers that the peer CTA signals (remote arrives, multicast tcgen05.commit) are waited on
+// like any other: the arrival completes the phase in this CTA's shared memory and wakes the
+// suspended thread.
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag) {
-    if (mbar_test_wait_cluster(bar, parity)) return true;
-    unsigned long long t0 = 0;
-    uint32_t polls = 0;
-    while (!mbar_test_wait_cluster(bar, parity)) {
-        if ((++polls & 1023u) == 0u) {
-            if (*abort_flag) return false;
-            unsigned long long now = globaltimer_ns();
-            if (t0 == 0) {
-                t0 = now;
-            } else if (now - t0 > WAIT_TIMEOUT_NS) {
-                *abort_flag = 1;
-                return false;
-            }
-        }
-    }
-    return true;
+    return mbar_wait(bar, parity, abort_flag);
 }
 
 // All threads of both CTAs meet (used once after set-up and once before tear-down).
