@@ -79,12 +79,18 @@ def test_both_paths_same_bits(m, rows, cols, nested):
             out[prepared] = (y, dx)
         finally:
             nf4.PREPARED_SCALES = True
-    if m > 64:
-        assert torch.equal(out[True][0], out[False][0])
-    else:  # with a table, M <= 64 forward calls take the weight-streaming kernel: other sum order
-        diff = (out[True][0].float() - out[False][0].float()).abs().max()
-        assert diff <= 2e-3 * out[False][0].float().abs().max()
-    assert torch.equal(out[True][1], out[False][1])
+    # Same bits wherever both paths add the k-blocks in the same order. Two cases do not: with a
+    # table, M <= 64 forward calls take the weight-streaming kernel; and the small 300-row problem
+    # runs as 128-wide tiles without K-slices when it has a table, as two K-slices otherwise.
+    same_order_fwd = m > 64 and m != 300
+    same_order_bwd = m != 300
+    for same, a, b in ((same_order_fwd, out[True][0], out[False][0]),
+                       (same_order_bwd, out[True][1], out[False][1])):
+        if same:
+            assert torch.equal(a, b)
+        else:
+            diff = (a.float() - b.float()).abs().max()
+            assert diff <= 2e-3 * b.float().abs().max()
 
 
 def test_gather_path_vs_oracle(gather_only):
