@@ -280,8 +280,8 @@ def layer_backward(layer, acts):
 
 def kernels_per_step(shapes, m):
     """Kernels of this library that one step launches: a fused GEMM per group and direction, one
-    split-K reduction per output wherever the library's plan slices the contraction (it does when
-    the call needs scratch), and lora_down / lora_grad twice each per LoRA projection."""
+    split-K reduction per output wherever the library's plan slices the contraction (the library
+    is asked), and lora_down / lora_grad twice each per LoRA projection."""
     import ctypes
 
     from hackaton_b200 import _lib
@@ -292,8 +292,10 @@ def kernels_per_step(shapes, m):
         cols = shapes[group[0]][1]
         arr = (ctypes.c_int64 * len(rows))(*rows)
         for backward in (0, 1):
-            need = int(_lib.lib().nf4b200_workspace_bytes_group(len(rows), arr, cols, m, backward))
-            n += 1 + (0 if need <= 0 else (1 if backward else len(rows)))
+            launches = int(_lib.lib().nf4b200_launches_group(len(rows), arr, cols, m, backward, 1))
+            if launches < 1:
+                raise RuntimeError(f"nf4b200_launches_group: {launches}")
+            n += launches
     # lora_down: one batched launch per group and direction; lora_grad: one per group
     groups_with_lora = sum(1 for group in GROUPS if any(g in LORA_ON for g in group))
     return n + 3 * groups_with_lora
@@ -626,6 +628,18 @@ def run_leg(args):
             e = layers[i % n_layers]["down"]
             linear_forward(acts["x_down"], e["packed"], None, e["state"])
             launches += 2
+    elif args.only == "attn_proj":     # the 512 x 128 tiles: o forward/backward, q/k/v backward
+        from hackaton_b200.group import linear_backward_dx_group
+        from hackaton_b200.nf4 import linear_backward_dx
+
+        acts = make_activations(shapes, args.tokens or 2048, device)
+        for i in range(reps * n_layers):
+            lay = layers[i % n_layers]
+            linear_forward(acts["x_o"], lay["o"]["packed"], None, lay["o"]["state"])
+            linear_backward_dx(acts["dy_o"], lay["o"]["packed"], lay["o"]["state"])
+            linear_backward_dx_group([acts["dy_" + n] for n in "qkv"],
+                                     [(lay[n]["packed"], lay[n]["state"]) for n in "qkv"])
+            launches += 3
     elif args.only == "lora":
         acts = make_activations(shapes, args.tokens or 2048, device)
         for i in range(reps * n_layers):
@@ -1361,7 +1375,7 @@ def main():
                          "(all-gather of outputs, all-reduce of dX)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--only", default=None,
-                    choices=["dequant", "small_m", "small_m_bwd", "down_fwd", "lora"],
+                    choices=["dequant", "small_m", "small_m_bwd", "down_fwd", "attn_proj", "lora"],
                     help="run a few eager launches of one kernel family and nothing else (the "
                          "command profiler captures are taken from)")
     ap.add_argument("--tokens", type=int, default=0, help="with --only: token rows")

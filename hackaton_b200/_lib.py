@@ -17,7 +17,7 @@ EXPORTS = (
     "nf4b200_query", "nf4b200_last_error", "nf4b200_device_status", "nf4b200_dequant",
     "nf4b200_linear_fwd", "nf4b200_linear_bwd_dx", "nf4b200_lora_down", "nf4b200_lora_grad",
     "nf4b200_workspace_bytes", "nf4b200_linear_fwd_static", "nf4b200_linear_fwd_group",
-    "nf4b200_linear_bwd_dx_group", "nf4b200_workspace_bytes_group", "nf4b200_scales16_bytes",
+    "nf4b200_linear_bwd_dx_group", "nf4b200_workspace_bytes_group", "nf4b200_launches_group", "nf4b200_scales16_bytes",
     "nf4b200_prepare_scales", "nf4b200_lora_down_batch", "nf4b200_lora_grad_batch",
     "nf4b200_set_sm_limit", "nf4b200_gate_up_swiglu_fwd", "nf4b200_gate_up_swiglu_workspace_bytes",
     "nf4b200_swiglu_fwd", "nf4b200_swiglu_bwd", "nf4b200_linear_bwd_dx_swiglu",
@@ -93,6 +93,8 @@ def lib() -> ctypes.CDLL:
                                                    c_int64, c_void_p, c_size_t, c_void_p]
     handle.nf4b200_workspace_bytes_group.argtypes = [c_int, pi64, c_int64, c_int64, c_int]
     handle.nf4b200_workspace_bytes_group.restype = c_int64
+    handle.nf4b200_launches_group.argtypes = [c_int, pi64, c_int64, c_int64, c_int, c_int]
+    handle.nf4b200_launches_group.restype = c_int
     pf = POINTER(c_float)
     handle.nf4b200_lora_down_batch.argtypes = [c_int, pv, c_int64, pi64, pi64, pv, pi64, pi64, pf,
                                                pv, c_void_p]

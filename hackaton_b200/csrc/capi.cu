@@ -504,6 +504,24 @@ int64_t nf4b200_workspace_bytes_group(int count, const int64_t* n_rows, int64_t 
     return (int64_t)pl.ws_bytes;
 }
 
+int nf4b200_launches_group(int count, const int64_t* n_rows, int64_t n_cols, int64_t m, int backward,
+                           int with_scale_tables) {
+    DeviceInfo* d = nullptr;
+    int rc = require_sm100(&d);
+    if (rc != NF4B200_OK) return rc;
+    if (count < 1 || count > nf4::GEMM_MAX_GROUP || !n_rows || n_cols <= 0 || m <= 0)
+        return fail(NF4B200_EINVAL, "launches_group: bad arguments");
+    long long rows[nf4::GEMM_MAX_GROUP];
+    for (int i = 0; i < count; ++i) {
+        if (n_rows[i] <= 0) return fail(NF4B200_EINVAL, "launches_group: bad shape");
+        rows[i] = n_rows[i];
+    }
+    const nf4::GemmPlan pl = nf4::plan_gemm_group(m, rows, count, n_cols, backward != 0, gemm_sms(d),
+                                                  with_scale_tables != 0);
+    // one GEMM; with K-slices, one reduction per output (forward: per weight; backward: one dX)
+    return 1 + (pl.splits > 1 ? (backward ? 1 : count) : 0);
+}
+
 // Bytes of one temporary [m, n_rows] fp16 array, rounded so that the next one stays aligned.
 static size_t swiglu_tmp_bytes(int64_t m, int64_t n_rows) {
     return ((size_t)m * (size_t)n_rows * 2 + 255) / 256 * 256;

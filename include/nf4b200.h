@@ -206,6 +206,15 @@ int nf4b200_linear_bwd_dx_group(int count, const nf4b200_weight* const* w, const
                                 size_t workspace_bytes, void* stream);
 int64_t nf4b200_workspace_bytes_group(int count, const int64_t* n_rows, int64_t n_cols, int64_t m,
                                       int backward);
+/*
+ * Kernels that one nf4b200_linear_fwd_group / nf4b200_linear_bwd_dx_group call of this shape
+ * launches with more than 64 token rows: the fused GEMM, plus one reduction per output when the
+ * plan cuts the contraction into K-slices. with_scale_tables: every weight of the group carries
+ * the table of nf4b200_prepare_scales (the 128-wide tiles need it). Negative: an error code.
+ * (No counterpart in the reference; a benchmark's launch count reads it instead of guessing.)
+ */
+int nf4b200_launches_group(int count, const int64_t* n_rows, int64_t n_cols, int64_t m, int backward,
+                           int with_scale_tables);
 
 /*
  * SwiGLU, the step that follows the gate / up projections in the MLP (the reference's
