@@ -1701,14 +1701,8 @@ cudaError_t launch_gemm_group(const GemmGroupArgs& ga, cudaStream_t stream, cons
     }
     if (pl.cg == 2) {
         if (prep)
-#ifndef NF4B200_N1_DW
-#define NF4B200_N1_DW 16
-#endif
-#ifndef NF4B200_N1_STAGES
-#define NF4B200_N1_STAGES 6
-#endif
-            return a.trans_w ? launch_cfg<2, 1, true, NF4B200_N1_STAGES, NF4B200_N1_DW, MAXP, true>(ga, pl, stream, why)
-                             : launch_cfg<2, 1, false, NF4B200_N1_STAGES, NF4B200_N1_DW, MAXP, true>(ga, pl, stream, why);
+            return a.trans_w ? launch_cfg<2, 1, true, 6, 16, MAXP, true>(ga, pl, stream, why)
+                             : launch_cfg<2, 1, false, 6, 16, MAXP, true>(ga, pl, stream, why);
         return a.trans_w ? launch_cfg<2, 1, true, 6, 16, MAXP>(ga, pl, stream, why)
                          : launch_cfg<2, 1, false, 6, 16, MAXP>(ga, pl, stream, why);
     }
