@@ -1202,8 +1202,42 @@ def run_multi(args):
             dist.destroy_process_group()
             raise SystemExit(1)
 
-    def run(i):
+    # One CUDA graph per rotating layer, collectives included: with eight ranks on one host the
+    # Python side of a step (a dozen launches and four collectives) takes longer than the GPU
+    # needs for an eighth of the work. Capture runs in thread-local mode because the process
+    # group's watchdog thread polls events meanwhile. All ranks replay graphs, or none does.
+    for i in range(max(args.warmup, 3)):
         step_fn(layers[i % n_rot], acts)
+    torch.cuda.synchronize()
+    graphs = None
+    if not args.no_graphs:
+        captured = 1
+        try:
+            graphs = []
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for j in range(n_rot):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+                        keep = step_fn(layers[j], acts)
+                    graphs.append((g, keep))
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+        except Exception as exc:                      # noqa: BLE001
+            print(f"[bench] rank {rank}: CUDA graph capture of the step failed ({exc!r}); "
+                  "timing eager launches", file=sys.stderr)
+            captured = 0
+        flag = torch.tensor([captured], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            graphs = None
+
+    def run(i):
+        if graphs is not None:
+            graphs[i % n_rot][0].replay()
+        else:
+            step_fn(layers[i % n_rot], acts)
 
     for i in range(args.warmup):
         run(i)
@@ -1236,9 +1270,29 @@ def run_multi(args):
 
     for i in range(3):
         run_local(i)
+    local_graphs = None
+    if graphs is not None:
+        try:
+            local_graphs = []
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for j in range(n_rot):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+                        run_local(j)
+                    local_graphs.append(g)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+        except Exception as exc:                      # noqa: BLE001
+            print(f"[bench] rank {rank}: capture of the local step failed ({exc!r})", file=sys.stderr)
+            local_graphs = None
     n_local = max(3, args.steps // 2)
-    local_ms, _, _ = timed_steps(run_local, n_local, barrier=dist.barrier)
+    local_ms, _, _ = timed_steps(
+        (lambda i: local_graphs[i % n_rot].replay()) if local_graphs is not None else run_local,
+        n_local, barrier=dist.barrier)
     local_ms = max_over_ranks(local_ms / n_local)
+    del local_graphs
 
     # ---- the other layout, for the record (a few steps outside the main timed region): the
     # all-gather-of-outputs layout when the main run is paired, and the other way round
@@ -1330,6 +1384,7 @@ def run_multi(args):
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": workload_config(world, layout=args.layout, multi_gpu_workload=True),
             "verified": verified, "verify_max_rel_err": verify_err,
+            "cuda_graphs": graphs is not None,
             "frac_of_tensor_peak": value / (pk["tflops_burst"] * world),
             "frac_of_sustained_tensor_peak": value / (pk["tflops_sustained"] * world),
             "gemm_only_ms_per_step": local_ms,
@@ -1354,7 +1409,16 @@ def run_multi(args):
             "gpu_launches": (14 if paired else 26) * args.steps, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    torch.cuda.synchronize()
     dist.barrier()
+    if graphs is not None:
+        # With graphs that hold captured collectives the process group's teardown did not return
+        # (observed with two ranks: the line above printed, then both processes sat in the
+        # teardown until they were killed). Every rank has passed the barrier, nothing is in
+        # flight: leave without it.
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     dist.destroy_process_group()
 
 
