@@ -154,3 +154,25 @@ def test_sibling_modules_share_one_launch(cuda_lib):
     for a, r in zip(grads, grads_ref):
         assert nf4_oracle.max_rel_err(a.cpu(), r.cpu()) <= 1e-2
     cuda_lib.device_status()
+
+
+def test_launch_count_query(cuda_lib):
+    """nf4b200_launches_group: one GEMM, plus one reduction per output where the plan cuts the
+    contraction into K-slices (1.5B shapes at 2048 tokens)."""
+    import ctypes
+
+    lib = cuda_lib.lib()
+
+    def launches(rows, cols, m, backward, tables=1):
+        arr = (ctypes.c_int64 * len(rows))(*rows)
+        return int(lib.nf4b200_launches_group(len(rows), arr, cols, m, backward, tables))
+
+    qkv, gate_up = (1536, 256, 256), (8960, 8960)
+    assert launches(qkv, 1536, 2048, 0) == 1          # 512 x 128 tiles, one wave
+    assert launches(qkv, 1536, 2048, 1) == 1          # ... also for the chained backward
+    assert launches(qkv, 1536, 2048, 1, tables=0) == 2   # without scale tables: K-slices + reduction
+    assert launches(gate_up, 1536, 2048, 0) == 1
+    assert launches(gate_up, 1536, 2048, 1) == 2      # 280 k-blocks over 24 tiles: three K-slices
+    assert launches((1536,), 8960, 2048, 0) == 2      # down forward
+    assert launches((1536,), 8960, 2048, 1) == 1
+    assert launches((0,), 8960, 2048, 1) < 0          # bad shape: an error code
