@@ -7,7 +7,8 @@
 // epilogue would dominate. So: no shared-memory ring, no TMEM. Warps stream the codes straight
 // from global memory, expand them in registers with the same byte-permute table look-up as the
 // big kernel (same rounding: fp16(table) * fp16(scale)) and multiply with warp-level mma.sync
-// (m16n8k16, fp32 accumulate).
+// (m16n8k16, fp32 accumulate). Forward with up to 8 token rows: a byte -> fp16-pair table in
+// shared memory instead, and the block scale applied to each k-block's fp32 sums.
 //
 // Forward: a CTA owns 16 weight rows of one member of the group, its warps split the 64-deep
 // k-blocks. The contraction index is visited in a permuted order that A (weights) and B (tokens)
@@ -87,6 +88,34 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The same with a zero accumulator going in (first step of a k-block whose sums are scaled
+// afterwards).
+__device__ __forceinline__ void mma_16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                uint32_t a3, uint32_t b0, uint32_t b1) {
+    const float z = 0.f;
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%10,%10,%10,%10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z));
+}
+
+__device__ __forceinline__ uint32_t gv_lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+// Forward decode by byte: a 256-entry table in shared memory maps a byte of codes to its two
+// unscaled fp16 table values (first weight = high nibble in the low half), kept in PAIR_COPIES
+// copies (lane l reads copy l % PAIR_COPIES) so that a warp's look-ups spread over the banks.
+// One look-up per two weights instead of 27 register instructions per eight; the block scale
+// is applied to the k-block's fp32 sums instead of to every weight (one rounding less). Used for
+// up to 8 token rows (one token block): measured at M = 1 per layer 26.2 -> 23.7 us forward, while
+// with two token blocks (M = 16) the per-block scaling costs more than the look-ups save
+// (gate/up 14.8 -> 19.0 us), so those keep the register look-up.
+constexpr int PAIR_COPIES = 8;
+
 __device__ __forceinline__ RegLut load_reg_lut(const float* code16) {
     uint16_t bits[16];
 #pragma unroll
@@ -112,8 +141,10 @@ __device__ __forceinline__ void prefetch_span(const uint8_t* ptr, long long byte
     }
 }
 
+// (the 4-warp instantiation for one token block is capped at 64 registers: eight CTAs per SM, so
+// the 1120 CTAs of a gate/up group are one wave)
 template <int NT, int GV_WARPS>  // token blocks of 8 (M <= 8 * NT); warps that split K
-__global__ void __launch_bounds__(GV_WARPS * 32)
+__global__ void __launch_bounds__(GV_WARPS * 32, (GV_WARPS == 4 && NT == 1) ? 8 : 1)
 nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
     constexpr int GV_THREADS = GV_WARPS * 32;
     const int pi = gemv_find(p, (int)blockIdx.x);
@@ -127,6 +158,8 @@ nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
     grid_dep_wait();
     grid_dep_launch();
     __shared__ float red[GV_WARPS][NT * 8][GV_ROWS + 1];
+    constexpr bool PAIR = NT == 1;
+    __shared__ uint32_t pair_table[PAIR ? 256 * PAIR_COPIES : 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int r_lo = r0 + g, r_hi = r0 + g + 8;  // n_w % 16 == 0: both inside the weight
@@ -167,7 +200,28 @@ nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
         }
     };
     if (kb_begin < kb_end) issue(kb_begin);
-    const RegLut lut = load_reg_lut(pr.code16);
+    RegLut lut = {};
+    uint32_t pair_base = 0;
+    if constexpr (PAIR) {
+        // (red is free until the fold: it holds the 16 fp16 table values while the pairs are built)
+        unsigned short* t16 = reinterpret_cast<unsigned short*>(&red[0][0][0]);
+        if (threadIdx.x < 16)
+            t16[threadIdx.x] = __half_as_ushort(__float2half_rn(__ldg(pr.code16 + threadIdx.x)));
+        __syncthreads();
+        for (int i = threadIdx.x; i < 256 * PAIR_COPIES; i += GV_THREADS) {
+            const int e = i / PAIR_COPIES;
+            pair_table[i] = (uint32_t)t16[e >> 4] | ((uint32_t)t16[e & 15] << 16);
+        }
+        __syncthreads();
+        pair_base = (uint32_t)__cvta_generic_to_shared(pair_table) + (lane % PAIR_COPIES) * 4;
+    } else {
+        lut = load_reg_lut(pr.code16);
+    }
+    auto pairs = [&](uint32_t w, uint32_t (&o)[8], int at) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            o[at + i] = gv_lds32(pair_base + ((w >> (8 * i)) & 0xFFu) * (4u * PAIR_COPIES));
+    };
 
     for (int kb0 = kb_begin; kb0 < kb_end; kb0 += GV_BATCH * KB_STEP) {
         if (kb0 != kb_begin) issue(kb0);
@@ -176,7 +230,11 @@ nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
             const int kb = kb0 + b * KB_STEP;
             if (kb >= kb_end) break;
             uint32_t wl[8], wh[8];
-            {
+            const float f_lo = __half2float(s_lo[b]), f_hi = __half2float(s_hi[b]);
+            if constexpr (PAIR) {
+                pairs(q_lo[b].x, wl, 0); pairs(q_lo[b].y, wl, 4);
+                pairs(q_hi[b].x, wh, 0); pairs(q_hi[b].y, wh, 4);
+            } else {
                 const uint4 a = decode_word_reg(q_lo[b].x, lut, __half2half2(s_lo[b]));
                 const uint4 c = decode_word_reg(q_lo[b].y, lut, __half2half2(s_lo[b]));
                 wl[0] = a.x; wl[1] = a.y; wl[2] = a.z; wl[3] = a.w;
@@ -198,13 +256,27 @@ nf4_gemv_kernel(const __grid_constant__ GemvParams p) {
                     x0 = __ldg(xp);
                     x1 = __ldg(xp + 1);
                 }
+                if constexpr (PAIR) {
+                // unscaled sums of this k-block, then the rows' block scales (d0, d1: row g; d2, d3: g + 8)
+                float blk[4];
+                mma_16816_first(blk, wl[0], wh[0], wl[1], wh[1], x0.x, x0.y);
+                mma_16816(blk, wl[2], wh[2], wl[3], wh[3], x0.z, x0.w);
+                mma_16816(blk, wl[4], wh[4], wl[5], wh[5], x1.x, x1.y);
+                mma_16816(blk, wl[6], wh[6], wl[7], wh[7], x1.z, x1.w);
+                acc[nt][0] = fmaf(f_lo, blk[0], acc[nt][0]);
+                acc[nt][1] = fmaf(f_lo, blk[1], acc[nt][1]);
+                acc[nt][2] = fmaf(f_hi, blk[2], acc[nt][2]);
+                acc[nt][3] = fmaf(f_hi, blk[3], acc[nt][3]);
+                } else {
                 mma_16816(acc[nt], wl[0], wh[0], wl[1], wh[1], x0.x, x0.y);
                 mma_16816(acc[nt], wl[2], wh[2], wl[3], wh[3], x0.z, x0.w);
                 mma_16816(acc[nt], wl[4], wh[4], wl[5], wh[5], x1.x, x1.y);
                 mma_16816(acc[nt], wl[6], wh[6], wl[7], wh[7], x1.z, x1.w);
+                }
             }
         }
     }
+    __syncthreads();   // (the pair table build used `red`; every warp is past its look-ups)
 
     // accumulator fragment: d0,d1 -> (weight row g, tokens 2t, 2t+1); d2,d3 -> (row g+8, same)
 #pragma unroll
