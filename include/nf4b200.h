@@ -109,6 +109,12 @@ int nf4b200_selftest_wait(int64_t limit_ns, void* stream);
  * Replaces nf4_dequant_kernel / dequantize_nf4 (solution/nf4.py:28-44, 67-77) and, for nested
  * weights, the scale pre-pass _flatten_quant_states (solution/packed.py:57-79).
  * Needs n_rows * n_cols % 8 == 0 and blocksize % 8 == 0 (as solution/nf4.py:61-63).
+ * Stream order: the kernel is launched as a programmatic dependent of its predecessor in the
+ * stream and reads the weight's arrays (codes, absmax, code2, absmax2, offset, table) before it
+ * waits for that predecessor; `out` is written after the wait. This is ordinary stream order
+ * unless the predecessor is itself a kernel that releases its dependents early
+ * (cudaTriggerProgrammaticLaunchCompletion) and is what writes those arrays: such a producer must
+ * be separated from this call by another kernel or an event. No kernel of this library writes them.
  */
 int nf4b200_dequant(const nf4b200_weight* w, void* out, int out_dtype, void* stream);
 
