@@ -78,7 +78,7 @@ __device__ __forceinline__ void bulk_store_wait_read() {
     asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
-// STAGED (16-bit outputs into a 16-byte aligned buffer): a tile is expanded into 32 KB of shared
+// STAGED (16-bit outputs): a tile is expanded into 32 KB of shared
 // memory and leaves as one bulk copy, so all that is left to do after the dependency wait is one
 // instruction per CTA.
 template <typename T, bool NESTED, bool SHIFTS, bool STAGED>
@@ -227,12 +227,10 @@ static cudaError_t launch_t(const DequantArgs& a, cudaStream_t stream) {
 }
 
 cudaError_t launch_dequant(const DequantArgs& a, cudaStream_t stream) {
-    // bulk copies want 16-byte aligned addresses on both sides
-    const bool staged = (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
+    // (the C entry point has checked that `out` is 16-byte aligned, which the bulk copies need)
     switch (a.out_dtype) {
-        case 0: return staged ? launch_t<__half, true>(a, stream) : launch_t<__half, false>(a, stream);
-        case 1: return staged ? launch_t<__nv_bfloat16, true>(a, stream)
-                              : launch_t<__nv_bfloat16, false>(a, stream);
+        case 0: return launch_t<__half, true>(a, stream);
+        case 1: return launch_t<__nv_bfloat16, true>(a, stream);
         case 2: return launch_t<float, false>(a, stream);
         default: return cudaErrorInvalidValue;
     }

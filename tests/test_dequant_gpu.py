@@ -95,3 +95,27 @@ def test_rejects_what_it_cannot_decode(cuda_lib):
         dequantize_nf4(packed, state)
     state.quant_type = "nf4"
     assert not can_dequantize(packed.cpu(), state)
+
+
+@pytest.mark.parametrize("nested", [True, False])
+def test_store_routes_and_grid_stride(cuda_lib, nested):
+    """16-bit outputs leave through a staging area and one bulk copy per tile, fp32 outputs with
+    per-thread stores; a weight with more tiles than resident CTAs (18944 x 3584: 4145 tiles for
+    888 CTAs) makes every CTA reuse its staging area. The fp32 result rounded to fp16 is the fp16
+    result (one product, one rounding), and both ends of the walk equal the oracle."""
+    import copy
+
+    from hackaton_b200 import dequantize_nf4
+    from tests.util import oracle_weight, synthetic_weight
+
+    rows, cols = 18944, 3584
+    packed, state = synthetic_weight(rows, cols, nested, seed=21, device="cuda")
+    half = dequantize_nf4(packed, state)
+    state32 = copy.copy(state)
+    state32.dtype = torch.float32
+    full = dequantize_nf4(packed, state32)
+    assert full.dtype == torch.float32 and torch.equal(full.half(), half)
+    want = oracle_weight(packed, state)
+    for sl in (slice(0, 64), slice(rows - 64, rows)):
+        assert torch.equal(half[sl].cpu(), want[sl])
+    assert cuda_lib.device_status() == 0
