@@ -111,9 +111,9 @@ __device__ __forceinline__ uint32_t gv_lds32(uint32_t addr) {
 // copies (lane l reads copy l % PAIR_COPIES) so that a warp's look-ups spread over the banks.
 // One look-up per two weights instead of 27 register instructions per eight; the block scale
 // is applied to the k-block's fp32 sums instead of to every weight (one rounding less). Used for
-// up to 8 token rows (one token block): measured at M = 1 per layer 26.2 -> 23.7 us forward, while
-// with two token blocks (M = 16) the per-block scaling costs more than the look-ups save
-// (gate/up 14.8 -> 19.0 us), so those keep the register look-up.
+// up to 8 token rows (one token block): measured at M = 1, each group timed alone, 26.2 -> 24.0 us
+// per layer forward, while with two token blocks (M = 16) the per-block scaling costs more than
+// the look-ups save (gate/up 14.8 -> 19.0 us), so those keep the register look-up.
 constexpr int PAIR_COPIES = 8;
 
 __device__ __forceinline__ RegLut load_reg_lut(const float* code16) {
